@@ -1,0 +1,664 @@
+// Causal grouped-query attention over the paged cache, for prompt portions and single decoded
+// tokens in one batch.
+//
+// Every request r of the step brings q_len[r] = q_start[r+1] - q_start[r] new tokens whose keys
+// and values are already in the cache; kv_len[r] counts them too.  The query at offset j of
+// request r sits at position kv_len[r] - q_len[r] + j and sees keys 0..position (or the last
+// `window` of them).  Query head h reads kv head h / (n_q / n_kv).
+//
+// Cache layout (one K and one V array per layer): [page][kv head][slot in page][d]; the key at
+// position i of request r lives in page block_table[r][i / P], slot i % P.
+//
+// Work is cut into (query tile, kv head [, head chunk], kv split).  A query tile packs
+// (token, head-in-group) pairs as rows so that the heads of a group share the K/V they read.
+// Key tiles are anchored at absolute positions (tile k = keys [k*KT, (k+1)*KT)); a request with
+// nsplit[r] > 1 spreads its key tiles over that many blocks, which write unnormalised partial
+// sums to scratch memory; msgl_attention_combine merges them in split order.
+//
+// Three kernels:
+//   attn_mma_kernel<D, false>   bfloat16, tensor cores (mma.sync m16n8k16), 64 rows per block,
+//                               each warp owns 16 rows and walks all keys of a tile
+//   attn_mma_kernel<D, true>    bfloat16, 16 rows per block (decode), each warp owns 16 of the
+//                               tile's 64 keys; the four warps are merged at the end
+//   attn_simt_kernel<T>         any head size up to 512, float32 arithmetic throughout; this is
+//                               the true 32-bit path and the fallback for odd head sizes
+// Scores, softmax and the accumulation are float32 in all of them.
+#include "common.cuh"
+#include <math.h>
+
+#ifndef MSGL_HEAD_DIM
+#define MSGL_HEAD_DIM 128
+#endif
+
+struct AttnParams {
+    const void* q;            // [T, n_q, d]
+    void* out;                // [T, n_q, d]
+    const void* k_cache;
+    const void* v_cache;
+    const int* q_start;       // [B + 1]
+    const int* kv_len;        // [B]
+    const int* block_table;   // [B, bt_stride]
+    const int* nsplit;        // [B] or null (1 everywhere)
+    float* part_o;            // [(split * T + token) * n_q + head][d]
+    float* part_ml;           // [(split * T + token) * n_q + head][2]  (max in log2 units, sum)
+    int B, T, n_q, n_kv, d, page_size, bt_stride, window, max_split;
+    float scale;
+    int qlen_min, qlen_max;   // this launch takes the requests with qlen_min <= q_len <= qlen_max
+    int uniform_decode;       // every request has exactly one token: tile index == request index
+};
+
+struct TileInfo {
+    int req, t0, n_tok;       // request, first token of the tile within the request, tokens in the tile
+    int q_len, kv_len, q_base;
+};
+
+// Map blockIdx.x to (request, tile) by walking the per-request tile counts with one warp.
+__device__ __forceinline__ bool find_tile(const AttnParams& p, int tile_tokens, TileInfo& ti, int* sh /* >= 4 ints */) {
+    if (p.uniform_decode) {
+        const int r = blockIdx.x;
+        if (r >= p.B) return false;
+        ti.req = r; ti.t0 = 0; ti.n_tok = 1; ti.q_len = 1; ti.kv_len = p.kv_len[r]; ti.q_base = p.q_start[r];
+        return true;
+    }
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int base = 0, found_req = -1, found_t0 = 0;
+        for (int r0 = 0; r0 < p.B && found_req < 0; r0 += 32) {
+            const int r = r0 + lane;
+            int nt = 0;
+            if (r < p.B) {
+                const int ql = p.q_start[r + 1] - p.q_start[r];
+                if (ql >= p.qlen_min && ql <= p.qlen_max) nt = (ql + tile_tokens - 1) / tile_tokens;
+            }
+            int inc = nt;  // inclusive scan
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += v;
+            }
+            const int target = (int)blockIdx.x - base;
+            const unsigned hit = __ballot_sync(0xffffffffu, target < inc);
+            if (hit) {
+                const int src = __ffs(hit) - 1;
+                const int inc_src = __shfl_sync(0xffffffffu, inc, src);
+                const int nt_src = __shfl_sync(0xffffffffu, nt, src);
+                found_req = r0 + src;
+                found_t0 = (target - (inc_src - nt_src)) * tile_tokens;
+            }
+            base += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) { sh[0] = found_req; sh[1] = found_t0; }
+    }
+    __syncthreads();
+    ti.req = sh[0];
+    ti.t0 = sh[1];
+    if (ti.req < 0) return false;
+    ti.q_base = p.q_start[ti.req];
+    ti.q_len = p.q_start[ti.req + 1] - ti.q_base;
+    ti.kv_len = p.kv_len[ti.req];
+    ti.n_tok = min(tile_tokens, ti.q_len - ti.t0);
+    return true;
+}
+
+// Which key tiles a block walks: the tiles that hold keys [k_lo, p_max], cut into ns splits.
+__device__ __forceinline__ void key_tile_range(const AttnParams& p, const TileInfo& ti, int KT, int split, int ns,
+                                               int& p_min, int& p_max, int& kt_begin, int& kt_end) {
+    p_min = ti.kv_len - ti.q_len + ti.t0;
+    p_max = p_min + ti.n_tok - 1;
+    int k_lo = 0;
+    if (p.window > 0) k_lo = max(0, p_min - p.window + 1);
+    const int first = k_lo / KT, last = p_max / KT;
+    const int n_t = last - first + 1;
+    const int per = (n_t + ns - 1) / ns;
+    kt_begin = first + split * per;
+    kt_end = min(first + (split + 1) * per, last + 1);
+    if (kt_begin > kt_end) kt_begin = kt_end;
+}
+
+// ---------------------------------------------------------------------------------------
+// bfloat16 tensor-core kernel
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+constexpr int MMA_KT = 64;        // keys per tile
+constexpr int MMA_WARPS = 4;
+constexpr int MMA_THREADS = MMA_WARPS * 32;
+
+template <int D, bool KEY_SPLIT>
+__global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams p) {
+    constexpr int R = KEY_SPLIT ? 16 : 64;          // rows per block
+    constexpr int LDS = D + 8;                      // padded row of a shared-memory tile (elements)
+    constexpr int WK = KEY_SPLIT ? 16 : 64;         // keys of a tile that one warp handles
+    constexpr int NKB = WK / 8;                     // 8-key blocks per warp
+    constexpr int NDB = D / 8;                      // 8-wide output column blocks
+    constexpr int CH = D / 8;                       // 16-byte chunks per row
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* KVs = Qs + R * LDS;              // [stage][K|V][MMA_KT][LDS]
+    __shared__ int sh_tile[4];
+
+    const int G = p.n_q / p.n_kv;
+    const int Gc = G <= R ? G : R;
+    const int n_chunks = G <= R ? 1 : (G + R - 1) / R;
+    const int QT = G <= R ? R / G : 1;
+    const int kvh = blockIdx.y / n_chunks;
+    const int chunk = blockIdx.y - kvh * n_chunks;
+
+    TileInfo ti;
+    if (!find_tile(p, QT, ti, sh_tile)) return;
+    const int ns = p.nsplit ? min(max(p.nsplit[ti.req], 1), p.max_split) : 1;
+    const int split = blockIdx.z;
+    if (split >= ns) return;
+
+    int p_min, p_max, kt_begin, kt_end;
+    key_tile_range(p, ti, MMA_KT, split, ns, p_min, p_max, kt_begin, kt_end);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(p.q);
+    const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(p.k_cache);
+    const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(p.v_cache);
+    const int* bt = p.block_table + (size_t)ti.req * p.bt_stride;
+
+    // ---- Q rows into shared memory (zero rows where the tile has no token/head)
+    for (int idx = tid; idx < R * CH; idx += MMA_THREADS) {
+        const int r = idx / CH, c = idx - r * CH;
+        const int tl = r / Gc, hl = r - tl * Gc;
+        const int hg = chunk * R + hl;
+        const bool valid = tl < ti.n_tok && hg < G && tl < QT;
+        const size_t tok = (size_t)(ti.q_base + ti.t0 + (valid ? tl : 0));
+        const __nv_bfloat16* src = qg + (tok * p.n_q + (size_t)kvh * G + (valid ? hg : 0)) * D + c * 8;
+        cp_async16(Qs + r * LDS + c * 8, valid ? (const void*)src : (const void*)qg, valid);
+    }
+
+    auto load_kv = [&](int stage, int kt) {
+        __nv_bfloat16* Ks = KVs + (size_t)stage * 2 * MMA_KT * LDS;
+        __nv_bfloat16* Vs = Ks + MMA_KT * LDS;
+        const int key0 = kt * MMA_KT;
+        for (int idx = tid; idx < MMA_KT * CH; idx += MMA_THREADS) {
+            const int kl = idx / CH, c = idx - kl * CH;
+            const int key = key0 + kl;
+            const bool valid = key <= p_max;
+            size_t off = 0;
+            if (valid) {
+                const int pg = bt[key / p.page_size];
+                const int sl = key % p.page_size;
+                off = (((size_t)pg * p.n_kv + kvh) * p.page_size + sl) * D + c * 8;
+            }
+            cp_async16(Ks + kl * LDS + c * 8, kc + off, valid);
+            cp_async16(Vs + kl * LDS + c * 8, vc + off, valid);
+        }
+    };
+
+    // per-thread rows: g = lane / 4 (and g + 8) of this warp's 16 rows
+    const int row_base = KEY_SPLIT ? 0 : warp * 16;
+    const int key_base = KEY_SPLIT ? warp * 16 : 0;
+    const int r_lo = row_base + (lane >> 2), r_hi = r_lo + 8;
+    const int pos_lo = p_min + r_lo / Gc, pos_hi = p_min + r_hi / Gc;   // position of each row's query
+    const float sc = p.scale * 1.4426950408889634f;                     // scores in log2 units
+
+    float o[NDB][4];
+#pragma unroll
+    for (int i = 0; i < NDB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+    const int n_tiles = kt_end - kt_begin;
+    if (n_tiles > 0) load_kv(0, kt_begin);
+    cp_async_commit();
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int kt = kt_begin + it;
+        if (it + 1 < n_tiles) {
+            load_kv((it + 1) & 1, kt + 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const __nv_bfloat16* Ks = KVs + (size_t)(it & 1) * 2 * MMA_KT * LDS;
+        const __nv_bfloat16* Vs = Ks + MMA_KT * LDS;
+
+        // ---- S = Q K^T
+        float s[NKB][4];
+#pragma unroll
+        for (int i = 0; i < NKB; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            unsigned a[4];
+            ldmatrix_x4(a, Qs + (row_base + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nb2 = 0; nb2 < NKB / 2; ++nb2) {
+                unsigned b[4];
+                const int key = key_base + nb2 * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
+                ldmatrix_x4(b, Ks + key * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16_16816(s[2 * nb2], a, b[0], b[1]);
+                mma_bf16_16816(s[2 * nb2 + 1], a, b[2], b[3]);
+            }
+        }
+
+        // ---- scale, mask, online softmax
+        const int key0 = kt * MMA_KT + key_base;
+        const bool need_mask = (kt * MMA_KT + MMA_KT - 1 > p_min) ||
+                               (p.window > 0 && kt * MMA_KT <= p_max - p.window);
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < NKB; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = s[nb][e] * sc;
+                if (need_mask) {
+                    const int key = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+                    const int pos = (e < 2) ? pos_lo : pos_hi;
+                    bool ok = key <= pos;
+                    if (p.window > 0) ok = ok && (key > pos - p.window);
+                    if (!ok) v = -INFINITY;
+                }
+                s[nb][e] = v;
+                if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+            }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float mu_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, mu_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
+        const float al_lo = exp2f(m_lo - mu_lo), al_hi = exp2f(m_hi - mu_hi);
+        m_lo = mn_lo; m_hi = mn_hi;
+        l_lo *= al_lo; l_hi *= al_hi;
+#pragma unroll
+        for (int nb = 0; nb < NKB; ++nb) {
+            s[nb][0] = exp2f(s[nb][0] - mu_lo); s[nb][1] = exp2f(s[nb][1] - mu_lo);
+            s[nb][2] = exp2f(s[nb][2] - mu_hi); s[nb][3] = exp2f(s[nb][3] - mu_hi);
+            l_lo += s[nb][0] + s[nb][1];
+            l_hi += s[nb][2] + s[nb][3];
+        }
+#pragma unroll
+        for (int i = 0; i < NDB; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+
+        // ---- O += P V
+#pragma unroll
+        for (int j = 0; j < NKB / 2; ++j) {
+            unsigned a[4];
+            a[0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
+            a[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
+            a[2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
+            a[3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+#pragma unroll
+            for (int nd2 = 0; nd2 < D / 16; ++nd2) {
+                unsigned b[4];
+                const int key = key_base + j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4_trans(b, Vs + key * LDS + nd2 * 16 + ((lane >> 4) & 1) * 8);
+                mma_bf16_16816(o[2 * nd2], a, b[0], b[1]);
+                mma_bf16_16816(o[2 * nd2 + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+    // row sums over the four threads that share a row
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+    __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(p.out);
+    const bool direct = ns == 1;
+
+    if (!KEY_SPLIT) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = half ? r_hi : r_lo;
+            const int tl = r / Gc, hl = r - tl * Gc, hg = chunk * R + hl;
+            if (!(tl < ti.n_tok && hg < G && tl < QT)) continue;
+            const size_t tok = (size_t)(ti.q_base + ti.t0 + tl);
+            const int head = kvh * G + hg;
+            const float l = half ? l_hi : l_lo, m = half ? m_hi : m_lo;
+            if (direct) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                __nv_bfloat16* dst = og + (tok * p.n_q + head) * D;
+#pragma unroll
+                for (int nd = 0; nd < NDB; ++nd) {
+                    const int col = nd * 8 + (lane & 3) * 2;
+                    *reinterpret_cast<__nv_bfloat162*>(dst + col) =
+                        __floats2bfloat162_rn(o[nd][half * 2] * inv, o[nd][half * 2 + 1] * inv);
+                }
+            } else {
+                const size_t prow = ((size_t)split * p.T + tok) * p.n_q + head;
+                float* dst = p.part_o + prow * D;
+#pragma unroll
+                for (int nd = 0; nd < NDB; ++nd) {
+                    const int col = nd * 8 + (lane & 3) * 2;
+                    *reinterpret_cast<float2*>(dst + col) = make_float2(o[nd][half * 2], o[nd][half * 2 + 1]);
+                }
+                if ((lane & 3) == 0) { p.part_ml[prow * 2] = m; p.part_ml[prow * 2 + 1] = l; }
+            }
+        }
+    } else {
+        // merge the four warps (same rows, disjoint keys) through shared memory
+        float* Om = reinterpret_cast<float*>(KVs);              // [4][16][D]
+        float* Mm = Om + MMA_WARPS * 16 * D;                    // [4][16]
+        float* Lm = Mm + MMA_WARPS * 16;                        // [4][16]
+        __syncthreads();
+#pragma unroll
+        for (int nd = 0; nd < NDB; ++nd) {
+            const int col = nd * 8 + (lane & 3) * 2;
+            float* d0 = Om + ((size_t)warp * 16 + (lane >> 2)) * D + col;
+            float* d1 = d0 + 8 * D;
+            d0[0] = o[nd][0]; d0[1] = o[nd][1];
+            d1[0] = o[nd][2]; d1[1] = o[nd][3];
+        }
+        if ((lane & 3) == 0) {
+            Mm[warp * 16 + (lane >> 2)] = m_lo; Mm[warp * 16 + (lane >> 2) + 8] = m_hi;
+            Lm[warp * 16 + (lane >> 2)] = l_lo; Lm[warp * 16 + (lane >> 2) + 8] = l_hi;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < 16 * D; idx += MMA_THREADS) {
+            const int r = idx / D, col = idx - r * D;
+            const int tl = r / Gc, hl = r - tl * Gc, hg = chunk * R + hl;
+            if (!(tl < ti.n_tok && hg < G && tl < QT)) continue;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < MMA_WARPS; ++w) M = fmaxf(M, Mm[w * 16 + r]);
+            const float Mu = (M == -INFINITY) ? 0.f : M;
+            float acc = 0.f, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < MMA_WARPS; ++w) {
+                const float f = exp2f(Mm[w * 16 + r] - Mu);
+                acc += f * Om[((size_t)w * 16 + r) * D + col];
+                L += f * Lm[w * 16 + r];
+            }
+            const size_t tok = (size_t)(ti.q_base + ti.t0 + tl);
+            const int head = kvh * G + hg;
+            if (direct) {
+                og[(tok * p.n_q + head) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            } else {
+                const size_t prow = ((size_t)split * p.T + tok) * p.n_q + head;
+                p.part_o[prow * D + col] = acc;
+                if (col == 0) { p.part_ml[prow * 2] = M; p.part_ml[prow * 2 + 1] = L; }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// float32-arithmetic kernel for any head size (the true 32-bit path; also takes bfloat16 data)
+// ---------------------------------------------------------------------------------------
+constexpr int SIMT_R = 16;        // rows per block
+constexpr int SIMT_KT = 32;       // keys per tile
+constexpr int SIMT_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(SIMT_THREADS) attn_simt_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int D = p.d;
+    float* Qs = reinterpret_cast<float*>(smem_raw);          // [R][D]
+    float* Os = Qs + SIMT_R * D;                             // [R][D]
+    float* Ks = Os + SIMT_R * D;                             // [KT][D + 1]
+    float* Vs = Ks + SIMT_KT * (D + 1);                      // [KT][D]
+    float* Ss = Vs + SIMT_KT * D;                            // [R][KT]
+    float* Ms = Ss + SIMT_R * SIMT_KT;                       // [R]
+    float* Ls = Ms + SIMT_R;                                 // [R]
+    float* As = Ls + SIMT_R;                                 // [R]
+    __shared__ int sh_tile[4];
+
+    constexpr int R = SIMT_R;
+    const int G = p.n_q / p.n_kv;
+    const int Gc = G <= R ? G : R;
+    const int n_chunks = G <= R ? 1 : (G + R - 1) / R;
+    const int QT = G <= R ? R / G : 1;
+    const int kvh = blockIdx.y / n_chunks;
+    const int chunk = blockIdx.y - kvh * n_chunks;
+
+    TileInfo ti;
+    if (!find_tile(p, QT, ti, sh_tile)) return;
+    const int ns = p.nsplit ? min(max(p.nsplit[ti.req], 1), p.max_split) : 1;
+    const int split = blockIdx.z;
+    if (split >= ns) return;
+    int p_min, p_max, kt_begin, kt_end;
+    key_tile_range(p, ti, SIMT_KT, split, ns, p_min, p_max, kt_begin, kt_end);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const T* qg = reinterpret_cast<const T*>(p.q);
+    const T* kc = reinterpret_cast<const T*>(p.k_cache);
+    const T* vc = reinterpret_cast<const T*>(p.v_cache);
+    const int* bt = p.block_table + (size_t)ti.req * p.bt_stride;
+    const float sc = p.scale * 1.4426950408889634f;
+
+    for (int idx = tid; idx < R * D; idx += SIMT_THREADS) {
+        const int r = idx / D, c = idx - r * D;
+        const int tl = r / Gc, hl = r - tl * Gc, hg = chunk * R + hl;
+        const bool valid = tl < ti.n_tok && hg < G && tl < QT;
+        float v = 0.f;
+        if (valid) v = to_f32<T>(qg[((size_t)(ti.q_base + ti.t0 + tl) * p.n_q + (size_t)kvh * G + hg) * D + c]);
+        Qs[idx] = v;
+        Os[idx] = 0.f;
+    }
+    if (tid < R) { Ms[tid] = -INFINITY; Ls[tid] = 0.f; As[tid] = 0.f; }
+    __syncthreads();
+
+    for (int kt = kt_begin; kt < kt_end; ++kt) {
+        const int key0 = kt * SIMT_KT;
+        for (int idx = tid; idx < SIMT_KT * D; idx += SIMT_THREADS) {
+            const int kl = idx / D, c = idx - kl * D;
+            const int key = key0 + kl;
+            float kv = 0.f, vv = 0.f;
+            if (key <= p_max) {
+                const int pg = bt[key / p.page_size];
+                const int sl = key % p.page_size;
+                const size_t off = (((size_t)pg * p.n_kv + kvh) * p.page_size + sl) * D + c;
+                kv = to_f32<T>(kc[off]);
+                vv = to_f32<T>(vc[off]);
+            }
+            Ks[kl * (D + 1) + c] = kv;
+            Vs[kl * D + c] = vv;
+        }
+        __syncthreads();
+        // scores: one (row, key) pair per thread and pass; a warp shares the row
+        for (int idx = tid; idx < R * SIMT_KT; idx += SIMT_THREADS) {
+            const int r = idx / SIMT_KT, kl = idx - r * SIMT_KT;
+            const float* qr = Qs + r * D;
+            const float* kr = Ks + kl * (D + 1);
+            float acc = 0.f;
+            for (int c = 0; c < D; ++c) acc = fmaf(qr[c], kr[c], acc);
+            const int key = key0 + kl;
+            const int pos = p_min + r / Gc;
+            bool ok = key <= pos && (r / Gc) < ti.n_tok;
+            if (p.window > 0) ok = ok && (key > pos - p.window);
+            Ss[idx] = ok ? acc * sc : -INFINITY;
+        }
+        __syncthreads();
+        // online softmax, one warp per row, one lane per key
+        for (int r = warp; r < R; r += SIMT_THREADS / 32) {
+            const float v = Ss[r * SIMT_KT + lane];
+            const float mx = warp_max(v);
+            const float m_old = Ms[r];
+            const float m_new = fmaxf(m_old, mx);
+            const float mu = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = exp2f(m_old - mu);
+            const float pv = exp2f(v - mu);
+            const float sum = warp_sum(pv);
+            Ss[r * SIMT_KT + lane] = pv;
+            if (lane == 0) { Ms[r] = m_new; Ls[r] = Ls[r] * alpha + sum; As[r] = alpha; }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < R * D; idx += SIMT_THREADS) {
+            const int r = idx / D, c = idx - r * D;
+            float acc = Os[idx] * As[r];
+            const float* pr = Ss + r * SIMT_KT;
+#pragma unroll 8
+            for (int kl = 0; kl < SIMT_KT; ++kl) acc = fmaf(pr[kl], Vs[kl * D + c], acc);
+            Os[idx] = acc;
+        }
+        __syncthreads();
+    }
+
+    T* og = reinterpret_cast<T*>(p.out);
+    for (int idx = tid; idx < R * D; idx += SIMT_THREADS) {
+        const int r = idx / D, c = idx - r * D;
+        const int tl = r / Gc, hl = r - tl * Gc, hg = chunk * R + hl;
+        if (!(tl < ti.n_tok && hg < G && tl < QT)) continue;
+        const size_t tok = (size_t)(ti.q_base + ti.t0 + tl);
+        const int head = kvh * G + hg;
+        if (ns == 1) {
+            const float l = Ls[r];
+            og[(tok * p.n_q + head) * D + c] = from_f32<T>(l > 0.f ? Os[idx] / l : 0.f);
+        } else {
+            const size_t prow = ((size_t)split * p.T + tok) * p.n_q + head;
+            p.part_o[prow * D + c] = Os[idx];
+            if (c == 0) { p.part_ml[prow * 2] = Ms[r]; p.part_ml[prow * 2 + 1] = Ls[r]; }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// merge of the kv splits, in split order: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    const int* __restrict__ token_req, const int* __restrict__ nsplit,
+                                    T* __restrict__ out, int T_, int n_q, int d, int max_split) {
+    const int tok = blockIdx.x;
+    const int req = token_req ? token_req[tok] : tok;
+    const int ns = min(max(nsplit[req], 1), max_split);
+    if (ns <= 1) return;
+    for (int idx = threadIdx.x; idx < n_q * d; idx += blockDim.x) {
+        const int h = idx / d, c = idx - h * d;
+        float M = -INFINITY;
+        for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[(((size_t)s * T_ + tok) * n_q + h) * 2]);
+        const float Mu = (M == -INFINITY) ? 0.f : M;
+        float acc = 0.f, L = 0.f;
+        for (int s = 0; s < ns; ++s) {
+            const size_t prow = ((size_t)s * T_ + tok) * n_q + h;
+            const float f = exp2f(part_ml[prow * 2] - Mu);
+            acc += f * part_o[prow * d + c];
+            L += f * part_ml[prow * 2 + 1];
+        }
+        out[((size_t)tok * n_q + h) * d + c] = from_f32<T>(L > 0.f ? acc / L : 0.f);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// C entry points
+// ---------------------------------------------------------------------------------------
+MSGL_API int msgl_attention_head_dim() { return MSGL_HEAD_DIM; }
+
+// rows per block and tokens per query tile of a variant, for the host's grid arithmetic
+// variant: 0 = simt, 1 = mma 64-row, 2 = mma key-split (16-row)
+MSGL_API int msgl_attention_tile_rows(int variant) { return variant == 1 ? 64 : 16; }
+
+static size_t simt_smem_bytes(int d) {
+    return sizeof(float) * ((size_t)2 * SIMT_R * d + (size_t)SIMT_KT * (2 * d + 1) + SIMT_R * SIMT_KT + 3 * SIMT_R);
+}
+
+template <int D, bool KS> static size_t mma_smem_bytes() {
+    constexpr int R = KS ? 16 : 64;
+    return sizeof(__nv_bfloat16) * ((size_t)R * (D + 8) + (size_t)4 * MMA_KT * (D + 8));
+}
+
+// grid_x: number of query tiles the launch has to cover (the host knows every q_len).
+MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const void* v_cache, const int* q_start,
+                            const int* kv_len, const int* block_table, const int* nsplit, float* part_o,
+                            float* part_ml, int B, int T_, int n_q, int n_kv, int d, int page_size, int bt_stride,
+                            int window, int max_split, float scale, int qlen_min, int qlen_max, int uniform_decode,
+                            int variant, int grid_x, int dtype, cudaStream_t stream) {
+    if (grid_x <= 0 || B <= 0) return MSGL_OK;
+    if (n_kv <= 0 || n_q % n_kv != 0 || d <= 0 || page_size <= 0 || max_split < 1) return MSGL_ERR_SIZE;
+    if (max_split > 1 && (part_o == nullptr || part_ml == nullptr || nsplit == nullptr)) return MSGL_ERR_SIZE;
+    AttnParams p;
+    p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len;
+    p.block_table = block_table; p.nsplit = nsplit; p.part_o = part_o; p.part_ml = part_ml;
+    p.B = B; p.T = T_; p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.page_size = page_size; p.bt_stride = bt_stride;
+    p.window = window; p.max_split = max_split; p.scale = scale; p.qlen_min = qlen_min; p.qlen_max = qlen_max;
+    p.uniform_decode = uniform_decode;
+    const int G = n_q / n_kv;
+    const int R = variant == 1 ? 64 : 16;
+    const int n_chunks = G <= R ? 1 : (G + R - 1) / R;
+    dim3 grid(grid_x, n_kv * n_chunks, max_split);
+    if (variant == 0) {
+        if (d > 512) return MSGL_ERR_SIZE;
+        const size_t smem = simt_smem_bytes(d);
+        if (smem > 227 * 1024) return MSGL_ERR_SIZE;
+        static size_t simt_attr[2] = {0, 0};   // largest size already granted per element type
+        if (dtype == MSGL_F32) {
+            if (smem > 48 * 1024 && smem > simt_attr[0]) {
+                cudaFuncSetAttribute(attn_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                simt_attr[0] = smem;
+            }
+            attn_simt_kernel<float><<<grid, SIMT_THREADS, smem, stream>>>(p);
+        } else if (dtype == MSGL_BF16) {
+            if (smem > 48 * 1024 && smem > simt_attr[1]) {
+                cudaFuncSetAttribute(attn_simt_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                simt_attr[1] = smem;
+            }
+            attn_simt_kernel<__nv_bfloat16><<<grid, SIMT_THREADS, smem, stream>>>(p);
+        } else {
+            return MSGL_ERR_DTYPE;
+        }
+        return msgl_check_launch();
+    }
+    if (dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    if (d != MSGL_HEAD_DIM) return MSGL_ERR_SIZE;
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
+    if (variant == 1) {
+        const size_t smem = mma_smem_bytes<MSGL_HEAD_DIM, false>();
+        static bool attr_set = false;   // set once, outside any stream capture (the first launch is never captured)
+        if (!attr_set) {
+            cudaFuncSetAttribute(attn_mma_kernel<MSGL_HEAD_DIM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attr_set = true;
+        }
+        attn_mma_kernel<MSGL_HEAD_DIM, false><<<grid, MMA_THREADS, smem, stream>>>(p);
+    } else if (variant == 2) {
+        const size_t smem = mma_smem_bytes<MSGL_HEAD_DIM, true>();
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaFuncSetAttribute(attn_mma_kernel<MSGL_HEAD_DIM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attr_set = true;
+        }
+        attn_mma_kernel<MSGL_HEAD_DIM, true><<<grid, MMA_THREADS, smem, stream>>>(p);
+    } else {
+        return MSGL_ERR_SIZE;
+    }
+    return msgl_check_launch();
+}
+
+MSGL_API int msgl_attention_combine(const float* part_o, const float* part_ml, const int* token_req,
+                                    const int* nsplit, void* out, int T_, int n_q, int d, int max_split, int dtype,
+                                    cudaStream_t stream) {
+    if (T_ <= 0 || max_split <= 1) return MSGL_OK;
+    const int threads = n_q * d >= 1024 ? 256 : 128;
+    if (dtype == MSGL_F32)
+        attn_combine_kernel<float><<<T_, threads, 0, stream>>>(part_o, part_ml, token_req, nsplit, (float*)out, T_, n_q, d, max_split);
+    else if (dtype == MSGL_BF16)
+        attn_combine_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(part_o, part_ml, token_req, nsplit,
+                                                                       (__nv_bfloat16*)out, T_, n_q, d, max_split);
+    else
+        return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}

@@ -1,0 +1,63 @@
+// Shared device helpers for the engine's sm_100a kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define MSGL_API extern "C" __attribute__((visibility("default")))
+
+// element type selector used by the C entry points: 0 = float32, 1 = bfloat16
+enum { MSGL_F32 = 0, MSGL_BF16 = 1 };
+
+// error codes returned by the C entry points (0 = launched)
+enum {
+    MSGL_OK = 0,
+    MSGL_ERR_DTYPE = 1,       // element type not handled by this kernel
+    MSGL_ERR_SIZE = 2,        // a size the kernel refuses (head size, row length, ...)
+    MSGL_ERR_LAUNCH = 3,      // cudaGetLastError() after the launch was not cudaSuccess
+    MSGL_ERR_ALIGN = 4,       // a pointer or stride not aligned as required
+};
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// weight that may be stored as float32 or as bfloat16, chosen at run time
+__device__ __forceinline__ float load_weight(const void* w, int i, int w_is_f32) {
+    return w_is_f32 ? reinterpret_cast<const float*>(w)[i]
+                    : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats of shared memory.
+// The order of the additions depends only on blockDim, never on the data or the batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int nwarps = (blockDim.x + 31) >> 5;
+    float r = (lane < nwarps) ? scratch[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+
+static inline int msgl_check_launch() {
+    return cudaGetLastError() == cudaSuccess ? MSGL_OK : MSGL_ERR_LAUNCH;
+}

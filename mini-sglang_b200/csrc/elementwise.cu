@@ -1,0 +1,304 @@
+// Memory-bound kernels of the decoder: embedding, RMSNorm with the residual sum fused in,
+// per-head q/k norm + rotary position encoding + cache write in one pass, SwiGLU.
+//
+// Conventions
+//  * activations are `T` (float or bfloat16); the residual stream is always float32, so the
+//    residual sum is computed and kept in 32-bit;
+//  * all arithmetic inside a kernel is float32; one rounding at the store;
+//  * every size is a run-time parameter (rows, widths, head counts, head size, page size);
+//    sizes a kernel cannot take are refused with MSGL_ERR_SIZE by the C entry point;
+//  * reductions are done in an order fixed by the launch shape only.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------
+// embedding: res[t, :] = float(E[ids[t], :])
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int H, int V) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * H;
+    if (id < 0 || id >= V) {  // host code validates ids; an id out of range yields zeros, never a wild read
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const T* row = table + (size_t)id * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32<T>(row[i]);
+}
+
+MSGL_API int msgl_embedding(const int* ids, const void* table, float* out, int T_, int H, int V,
+                            int dtype, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+    if (dtype == MSGL_F32)
+        embedding_kernel<float><<<T_, threads, 0, stream>>>(ids, (const float*)table, out, H, V);
+    else if (dtype == MSGL_BF16)
+        embedding_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, H, V);
+    else
+        return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm, optionally with the residual sum in front and a row gather:
+//   v      = (res_in ? res_in[src] : 0) + (x ? float(x[src]) : 0)        src = row_idx ? row_idx[r] : r
+//   res_out[r] = v                                                        (if res_out)
+//   y[r]   = T(v * rsqrt(mean(v^2) + eps) * w)
+// One block per row; the row is kept in shared memory between the two passes when it fits.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, const float* res_in, float* res_out,
+                               const int* __restrict__ row_idx, const void* __restrict__ w, int w_is_f32,
+                               float eps, T* __restrict__ y, int H, int cache_row) {
+    extern __shared__ float srow[];
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(row_idx ? row_idx[r] : r) * H;
+    const size_t dst = (size_t)r * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = 0.f;
+        if (res_in) v = res_in[src + i];
+        if (x) v += to_f32<T>(x[src + i]);
+        if (res_out) res_out[dst + i] = v;
+        if (cache_row) srow[i] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, red);
+    const float inv = rsqrtf(total / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v;
+        if (cache_row) {
+            v = srow[i];
+        } else {  // row too long for shared memory: recompute from the inputs
+            v = 0.f;
+            if (res_out) v = res_out[dst + i];
+            else {
+                if (res_in) v = res_in[src + i];
+                if (x) v += to_f32<T>(x[src + i]);
+            }
+        }
+        y[dst + i] = from_f32<T>(v * inv * load_weight(w, i, w_is_f32));
+    }
+}
+
+MSGL_API int msgl_rmsnorm(const void* x, const float* res_in, float* res_out, const int* row_idx,
+                          const void* w, int w_is_f32, float eps, void* y, int rows, int H,
+                          int dtype, cudaStream_t stream) {
+    if (rows <= 0) return MSGL_OK;
+    if (H <= 0) return MSGL_ERR_SIZE;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const int cache_row = (size_t)H * 4 <= 40 * 1024;
+    const size_t smem = cache_row ? (size_t)H * 4 : 0;
+    if (dtype == MSGL_F32)
+        rmsnorm_kernel<float><<<rows, threads, smem, stream>>>((const float*)x, res_in, res_out, row_idx, w, w_is_f32,
+                                                               eps, (float*)y, H, cache_row);
+    else if (dtype == MSGL_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<rows, threads, smem, stream>>>((const __nv_bfloat16*)x, res_in, res_out, row_idx,
+                                                                       w, w_is_f32, eps, (__nv_bfloat16*)y, H, cache_row);
+    else
+        return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// q/k per-head RMSNorm (optional) + rotary position encoding from a float32 table (optional)
+// + write of k and v into the paged cache + q to a dense buffer.  One warp per (token, head).
+//
+//   qkv row layout: [ q: n_q*d | k: n_kv*d | v: n_kv*d ],  row stride `qkv_stride` elements
+//   table: [max_pos, rot] float32 = cos(angles) | sin(angles), rot/2 each; halves of the
+//          first `rot` elements of a head are rotated against each other (NeoX style)
+//   cache layout per layer: [page][kv head][slot in page][d]; token slot s = page*P + offset
+// ---------------------------------------------------------------------------------------
+#define QKR_MAX_PER_LANE 16   // head sizes up to 512
+
+template <typename T>
+__global__ void qknorm_rope_kvwrite_kernel(const T* __restrict__ qkv, int qkv_stride,
+                                           const int* __restrict__ positions, const int* __restrict__ out_loc,
+                                           const void* __restrict__ qw, const void* __restrict__ kw, int w_is_f32,
+                                           float eps, const float* __restrict__ table, int rot, int max_pos,
+                                           T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                           int page_size, int n_q, int n_kv, int d) {
+    const int t = blockIdx.x;
+    const int warps = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int head = blockIdx.y * warps + (threadIdx.x >> 5);
+    const int n_heads = n_q + 2 * n_kv;
+    if (head >= n_heads) return;
+    const bool is_q = head < n_q;
+    const bool is_k = !is_q && head < n_q + n_kv;
+    const bool writes_cache = (k_cache != nullptr) && (out_loc != nullptr);
+    if (!is_q && !writes_cache) return;
+
+    const T* src = qkv + (size_t)t * qkv_stride + (size_t)head * d;
+    float v[QKR_MAX_PER_LANE];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < QKR_MAX_PER_LANE; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = (i < d) ? to_f32<T>(src[i]) : 0.f;
+        ss += v[j] * v[j];
+    }
+    const void* nw = is_q ? qw : (is_k ? kw : nullptr);
+    if (nw != nullptr) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+        for (int j = 0; j < QKR_MAX_PER_LANE; ++j) {
+            const int i = lane + 32 * j;
+            if (i < d) v[j] = v[j] * inv * load_weight(nw, i, w_is_f32);
+        }
+    }
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * n_q + head) * d;
+    } else {
+        const int slot = out_loc[t];
+        const int page = slot / page_size, off = slot - page * page_size;
+        const int kvh = is_k ? head - n_q : head - n_q - n_kv;
+        T* base = is_k ? k_cache : v_cache;
+        dst = base + (((size_t)page * n_kv + kvh) * page_size + off) * d;
+    }
+    if (table != nullptr && (is_q || is_k)) {
+        // rotate: element i < rot/2 pairs with i + rot/2.  The partner lives in another lane or
+        // register, so the head goes through shared memory once.
+        extern __shared__ float sh[];
+        float* hv = sh + (size_t)(threadIdx.x >> 5) * d;
+#pragma unroll
+        for (int j = 0; j < QKR_MAX_PER_LANE; ++j) {
+            const int i = lane + 32 * j;
+            if (i < d) hv[i] = v[j];
+        }
+        __syncwarp();
+        int pos = positions[t];
+        pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+        const float* cs = table + (size_t)pos * rot;
+        const int half = rot >> 1;
+        for (int i = lane; i < d; i += 32) {
+            float o;
+            if (i < half) {
+                o = hv[i] * cs[i] - hv[i + half] * cs[half + i];
+            } else if (i < rot) {
+                const int p = i - half;
+                o = hv[p] * cs[half + p] + hv[i] * cs[p];
+            } else {
+                o = hv[i];
+            }
+            dst[i] = from_f32<T>(o);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < QKR_MAX_PER_LANE; ++j) {
+            const int i = lane + 32 * j;
+            if (i < d) dst[i] = from_f32<T>(v[j]);
+        }
+    }
+}
+
+MSGL_API int msgl_qknorm_rope_kvwrite(const void* qkv, int qkv_stride, const int* positions, const int* out_loc,
+                                      const void* qw, const void* kw, int w_is_f32, float eps,
+                                      const float* table, int rot, int max_pos, void* q_out, void* k_cache,
+                                      void* v_cache, int page_size, int n_q, int n_kv, int d, int T_, int dtype,
+                                      cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (d <= 0 || d > 32 * QKR_MAX_PER_LANE || rot < 0 || rot > d || (rot & 1) || page_size <= 0) return MSGL_ERR_SIZE;
+    const int n_heads = n_q + 2 * n_kv;
+    const int warps = n_heads < 8 ? n_heads : 8;
+    dim3 grid(T_, (n_heads + warps - 1) / warps);
+    const size_t smem = table ? (size_t)warps * d * sizeof(float) : 0;
+    if (dtype == MSGL_F32)
+        qknorm_rope_kvwrite_kernel<float><<<grid, warps * 32, smem, stream>>>(
+            (const float*)qkv, qkv_stride, positions, out_loc, qw, kw, w_is_f32, eps, table, rot, max_pos,
+            (float*)q_out, (float*)k_cache, (float*)v_cache, page_size, n_q, n_kv, d);
+    else if (dtype == MSGL_BF16)
+        qknorm_rope_kvwrite_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(
+            (const __nv_bfloat16*)qkv, qkv_stride, positions, out_loc, qw, kw, w_is_f32, eps, table, rot, max_pos,
+            (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_size, n_q, n_kv, d);
+    else
+        return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// SwiGLU: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(a) = a / (1 + exp(-a)) in float32
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        const float a = to_f32<T>(gu[t * 2 * I + i]);
+        const float b = to_f32<T>(gu[t * 2 * I + I + i]);
+        out[idx] = from_f32<T>(a / (1.f + expf(-a)) * b);
+    }
+}
+
+// 8 bfloat16 per thread when the row width allows it
+__global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, int I8, size_t total8) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I8;
+        const int i = (int)(idx - t * I8);
+        uint4 a = gu[t * 2 * I8 + i];
+        uint4 b = gu[t * 2 * I8 + I8 + i];
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+        uint4 o;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 af = __bfloat1622float2(ap[k]);
+            const float2 bf = __bfloat1622float2(bp[k]);
+            op[k] = __floats2bfloat162_rn(af.x / (1.f + expf(-af.x)) * bf.x, af.y / (1.f + expf(-af.y)) * bf.y);
+        }
+        out[idx] = o;
+    }
+}
+
+MSGL_API int msgl_swiglu(const void* gu, void* out, int T_, int I, int dtype, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (I <= 0) return MSGL_ERR_SIZE;
+    const size_t total = (size_t)T_ * I;
+    const int threads = 256;
+    if (dtype == MSGL_BF16 && (I % 8) == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        const size_t total8 = total / 8;
+        size_t blocks = (total8 + threads - 1) / threads;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        swiglu_bf16x8_kernel<<<(unsigned)blocks, threads, 0, stream>>>((const uint4*)gu, (uint4*)out, I / 8, total8);
+        return msgl_check_launch();
+    }
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == MSGL_F32)
+        swiglu_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
+    else if (dtype == MSGL_BF16)
+        swiglu_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu,
+                                                                               (__nv_bfloat16*)out, I, total);
+    else
+        return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// float32 -> T conversion of rows (used where a float32 stream feeds a T consumer)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void cast_from_f32_kernel(const float* __restrict__ in, T* __restrict__ out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<T>(in[i]);
+}
+
+MSGL_API int msgl_cast_from_f32(const float* in, void* out, long long n, int dtype, cudaStream_t stream) {
+    if (n <= 0) return MSGL_OK;
+    size_t blocks = ((size_t)n + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == MSGL_F32)
+        cast_from_f32_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>(in, (float*)out, (size_t)n);
+    else if (dtype == MSGL_BF16)
+        cast_from_f32_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(in, (__nv_bfloat16*)out, (size_t)n);
+    else
+        return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}

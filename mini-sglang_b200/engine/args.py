@@ -1,0 +1,105 @@
+"""Options of the engine, with the names and meanings of the reference's ServerArgs where it has
+them (mini_sglang/managers/server_args.py:16-60) and its four environment tunables
+(mini_sglang/utils/global_vars.py:11-27).  Options of things this engine does not have (HTTP
+host/port, tensor parallel size, NCCL port, choice of attention backend, device) are left out;
+`tp_size` and `device` are accepted only with their single legal value."""
+
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import os
+import random
+from typing import List, Optional
+
+
+def _env(name: str, default: float) -> float:
+    return float(os.environ.get(name, default))
+
+
+@dataclasses.dataclass
+class EngineArgs:
+    model: str
+    page_size: int = 1
+    max_num_reqs: int = 1024
+    max_capture_bs: int = 128
+    schedule_policy: str = "lpm"
+    tp_size: int = 1
+    device: str = "cuda"
+    gpu_memory_utilization: float = 0.9
+    log_level: str = "INFO"
+    random_seed: Optional[int] = None
+    profile: bool = False
+    disable_radix_cache: bool = False
+    disable_cuda_graph: bool = False
+    schedule_conservativeness: float = 1.0
+    max_prefill_tokens: int = 16384
+    dummy_load: bool = False
+    # this engine's own
+    dtype: str = "bfloat16"                  # "bfloat16" | "float32" (true 32-bit everywhere)
+    num_pages: Optional[int] = None          # size of the cache in pages instead of a memory fraction
+    chunk_size: int = 8192                   # longest portion of one prompt in one step
+    max_context_len: Optional[int] = None    # default: the model's max_position_embeddings
+    init_new_token_ratio: float = dataclasses.field(default_factory=lambda: _env("SGLANG_INIT_NEW_TOKEN_RATIO", 0.7))
+    min_new_token_ratio_factor: float = dataclasses.field(default_factory=lambda: _env("SGLANG_MIN_NEW_TOKEN_RATIO_FACTOR", 0.14))
+    new_token_ratio_decay_steps: int = dataclasses.field(default_factory=lambda: int(_env("SGLANG_NEW_TOKEN_RATIO_DECAY_STEPS", 600)))
+    retract_decode_steps: int = dataclasses.field(default_factory=lambda: int(_env("SGLANG_RETRACT_DECODE_STEPS", 20)))
+
+    def __post_init__(self):
+        self.model = os.path.expanduser(self.model)
+        if not os.path.isdir(self.model):
+            raise ValueError(f"--model {self.model!r} is not a folder")
+        if self.random_seed is None:
+            self.random_seed = random.randint(0, 1 << 30)
+        if self.tp_size != 1:
+            raise ValueError("this engine runs on one GPU: tp_size must be 1")
+        if not str(self.device).startswith("cuda"):
+            raise ValueError("this engine runs on a CUDA device only")
+        if self.dtype not in ("bfloat16", "float32", "bf16", "fp32"):
+            raise ValueError("dtype must be bfloat16 or float32")
+        if self.schedule_policy not in ("fcfs", "lof", "random", "lpm", "dfs-weight"):
+            raise ValueError(f"unknown schedule policy {self.schedule_policy!r}")
+        if self.disable_radix_cache and self.schedule_policy not in ("fcfs", "lof", "random"):
+            raise ValueError(f"schedule policy {self.schedule_policy} needs the radix cache; with "
+                             "--disable_radix_cache choose from fcfs, lof, random")
+        if self.page_size < 1:
+            raise ValueError("page_size must be at least 1")
+
+    @staticmethod
+    def add_cli_args(parser: argparse.ArgumentParser) -> None:
+        d = EngineArgs
+        parser.add_argument("--model", type=str, required=True, help="Path to the model directory.")
+        parser.add_argument("--page_size", type=int, default=d.page_size, help="Page size for KV cache.")
+        parser.add_argument("--tp_size", type=int, default=1, help="Tensor parallelism degree (only 1).")
+        parser.add_argument("--device", type=str, default="cuda", help="Device to run the model on (cuda).")
+        parser.add_argument("--gpu_memory_utilization", type=float, default=d.gpu_memory_utilization,
+                            help="GPU memory utilization percentage.")
+        parser.add_argument("--max_num_reqs", type=int, default=d.max_num_reqs, help="Maximum number of requests to handle.")
+        parser.add_argument("--schedule_policy", type=str, default=d.schedule_policy,
+                            choices=["fcfs", "lof", "random", "lpm", "dfs-weight"], help="Scheduling policy to use.")
+        parser.add_argument("--log_level", type=str, default=d.log_level,
+                            choices=["DEBUG", "INFO", "WARNING", "ERROR", "CRITICAL"], help="Logging level.")
+        parser.add_argument("--random_seed", type=int, default=None, help="Random seed; random if not set.")
+        parser.add_argument("--profile", action="store_true", help="Record per-step timings.")
+        parser.add_argument("--disable_radix_cache", action="store_true", help="Disable the radix cache mechanism.")
+        parser.add_argument("--disable_cuda_graph", action="store_true", help="Disable the use of CUDA graphs.")
+        parser.add_argument("--max_capture_bs", type=int, default=d.max_capture_bs,
+                            help="Maximum batch size for CUDA graph capture.")
+        parser.add_argument("--schedule-conservativeness", type=float, default=d.schedule_conservativeness,
+                            help="A larger value means more conservative scheduling.")
+        parser.add_argument("--max_prefill_tokens", type=int, default=d.max_prefill_tokens,
+                            help="Maximum number of tokens in one step's batch.")
+        parser.add_argument("--dummy_load", action="store_true",
+                            help="Random weights for the configuration in --model instead of its checkpoint.")
+        parser.add_argument("--dtype", type=str, default=d.dtype, choices=["bfloat16", "float32"])
+        parser.add_argument("--num_pages", type=int, default=None, help="Cache size in pages (default: from memory).")
+        parser.add_argument("--chunk_size", type=int, default=d.chunk_size, help="Longest prompt portion per step.")
+        parser.add_argument("--max_context_len", type=int, default=None)
+
+    @classmethod
+    def from_cli_args(cls, ns: argparse.Namespace) -> "EngineArgs":
+        names = [f.name for f in dataclasses.fields(cls)]
+        return cls(**{n: getattr(ns, n) for n in names if hasattr(ns, n)})
+
+
+ServerArgs = EngineArgs      # the reference's name for the same thing

@@ -1,0 +1,460 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+finishes and frees.
+
+Every step is ONE batch for the step function: all running requests that have a single token
+to feed (decode) plus portions of prompts, as far as the step's token budget and the free pages
+allow.  Roles and rules follow the reference (mini_sglang/managers/scheduler.py:307-448,
+mini_sglang/managers/scheduler_policy.py:47-232, mini_sglang/managers/batch_info.py:349-441):
+
+  order       fcfs | lpm (longest cached prefix first; a request that shares its first 32 tokens
+              with an earlier waiting or still-prefilling request waits for that one to fill the
+              prefix cache) | lof (largest max_new_tokens first) | random
+  admission   need = tokens to prefill + (max_new - done) * new_token_ratio must fit into
+              free + evictable tokens minus what running and already admitted requests will need
+  budget      at most `max_step_tokens` tokens per step; a prompt is fed in portions of at most
+              `chunk_size` tokens (the reference prefills whole prompts only)
+  pages short evict unpinned prefix-cache pages first; if decoding still does not fit, retract:
+              the requests with the fewest generated tokens (ties: longest prompt) give back
+              everything they hold and return to the waiting queue with their tokens, until the
+              rest can decode `retract_decode_steps` more steps; they are prefilled again later.
+              If a single request is left and still does not fit, it is finished with reason abort.
+  ratio       new_token_ratio starts at 0.7 * conservativeness, decays to 0.14 of that over 600
+              decode steps, and is re-estimated after a retraction.
+
+The scheduler needs of its runner only `mgr` (a CacheManager), `step(entries) -> logits`, and of
+its sampler `sample(logits, temperatures, row_keys, steps) -> token ids`; tests drive it with
+stand-ins on the CPU.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import itertools
+import random
+import time
+from typing import Dict, List, Optional, Sequence, Tuple
+
+from ..cache import OutOfPages, PrefixTree
+from ..sampling import SamplingParams
+from .step import StepEntry
+
+IN_BATCH_PREFIX = 32      # tokens two requests must share for the later one to wait (scheduler_policy.py:18-19)
+
+
+@dataclasses.dataclass
+class FinishReason:
+    type: str                 # "length" | "stop" | "abort"
+    detail: object = None
+
+    def to_json(self):
+        if self.type == "length":
+            return {"type": "length", "length": self.detail}
+        if self.type == "stop":
+            return {"type": "stop", "matched": self.detail}
+        return {"type": "abort", "message": self.detail}
+
+
+class Req:
+    _keys = itertools.count(1)
+
+    def __init__(self, rid: str, prompt: Sequence[int], params: SamplingParams, eos_ids: Sequence[int] = ()):
+        if len(prompt) == 0:
+            raise ValueError("a request needs at least one prompt token")
+        self.rid = rid
+        self.tokens: List[int] = list(prompt)
+        self.n_prompt = len(self.tokens)
+        self.params = params
+        self.eos_ids = set(eos_ids) if params.eos_token_id == -1 else {params.eos_token_id}
+        self.slot: Optional[int] = None
+        self.node = None                      # pinned prefix-tree node
+        self.cached_tokens = 0                # prompt tokens taken from the prefix cache at first admission
+        self.finish_reason: Optional[FinishReason] = None
+        self.to_abort: Optional[str] = None
+        self.rng_key = params.seed if params.seed is not None else next(Req._keys)
+        self.retractions = 0
+        self.t_arrive = time.time()
+        self.t_first_token: Optional[float] = None
+        self.prompt_inserted = False
+
+    @property
+    def n_output(self) -> int:
+        return len(self.tokens) - self.n_prompt
+
+    @property
+    def output(self) -> List[int]:
+        return self.tokens[self.n_prompt:]
+
+    @property
+    def finished(self) -> bool:
+        return self.finish_reason is not None
+
+    def check_finished(self) -> bool:
+        """After a token was appended (mini_sglang/managers/req_info.py:123-140)."""
+        if self.finish_reason is not None:
+            return True
+        if self.to_abort is not None:
+            self.finish_reason = FinishReason("abort", self.to_abort)
+        elif self.n_output >= self.params.max_new_tokens:
+            self.finish_reason = FinishReason("length", self.n_output)
+        elif not self.params.ignore_eos and self.tokens[-1] in self.eos_ids:
+            self.finish_reason = FinishReason("stop", self.tokens[-1])
+        return self.finish_reason is not None
+
+
+@dataclasses.dataclass
+class StepOutput:
+    req: Req
+    token: Optional[int]       # the token sampled for the request in this step (None: aborted before one)
+    finished: bool
+
+
+class Scheduler:
+    def __init__(self, runner, sampler, *, max_num_reqs: int = 1024, max_step_tokens: int = 16384,
+                 chunk_size: int = 8192, policy: str = "lpm", conservativeness: float = 1.0,
+                 retract_decode_steps: int = 20, enable_prefix_cache: bool = True, eos_ids: Sequence[int] = (),
+                 init_new_token_ratio: float = 0.7, min_new_token_ratio_factor: float = 0.14,
+                 new_token_ratio_decay_steps: int = 600, seed: int = 0):
+        if policy == "dfs-weight":
+            raise ValueError("schedule policy dfs-weight is not implemented; choose lpm, fcfs, lof or random")
+        if policy not in ("lpm", "fcfs", "lof", "random"):
+            raise ValueError(f"unknown schedule policy {policy!r}")
+        self.runner, self.sampler = runner, sampler
+        self.mgr = runner.mgr
+        self.P = self.mgr.page_size
+        self.max_num_reqs = min(max_num_reqs, self.mgr.max_reqs)
+        self.max_step_tokens = max_step_tokens
+        self.chunk_size = max(1, chunk_size)
+        self.policy = policy
+        self.retract_decode_steps = retract_decode_steps
+        self.eos_ids = list(eos_ids)
+        can_share = len(self.mgr.groups) == 1 and self.mgr.groups[0].window is None and not self.mgr.state_ids
+        self.tree: Optional[PrefixTree] = PrefixTree(self.P) if (enable_prefix_cache and can_share) else None
+        if policy == "lpm" and self.tree is None:
+            self.policy = "fcfs"
+        self.init_ratio = min(init_new_token_ratio * conservativeness, 1.0)
+        self.min_ratio = min(self.init_ratio * min_new_token_ratio_factor, 1.0)
+        self.ratio_decay = (self.init_ratio - self.min_ratio) / new_token_ratio_decay_steps
+        self.new_token_ratio = self.init_ratio
+        self.waiting: List[Req] = []
+        self.running: List[Req] = []
+        self._rand = random.Random(seed)
+        self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "cached_tokens": 0, "retractions": 0,
+                      "evicted_pages": 0, "aborted": 0, "finished": 0}
+
+    # -- requests --------------------------------------------------------------------------
+    def add_request(self, req: Req) -> None:
+        limit = self.mgr.max_context_len
+        if req.n_prompt >= limit:
+            req.finish_reason = FinishReason("abort", f"prompt of {req.n_prompt} tokens does not fit the context of {limit}")
+            return
+        # the last generated token is never fed, so prompt + max_new - 1 tokens reach the cache
+        req.params.max_new_tokens = min(req.params.max_new_tokens, limit - req.n_prompt + 1)
+        self.waiting.append(req)
+
+    def abort(self, rid: str, message: str = "aborted") -> None:
+        for r in self.waiting + self.running:
+            if r.rid == rid:
+                r.to_abort = message
+
+    @property
+    def idle(self) -> bool:
+        return not self.waiting and not self.running
+
+    # -- accounting ------------------------------------------------------------------------
+    def _free_tokens(self) -> int:
+        ev = self.tree.evictable_pages if self.tree else 0
+        return (self.mgr.available_pages(0) + ev) * self.P
+
+    def _make_room(self, pages_per_group: Sequence[int]) -> bool:
+        """Evict prefix-cache pages until the pools can hand out `pages_per_group`."""
+        for gi, n in enumerate(pages_per_group):
+            pool = self.mgr.groups[gi].pool
+            if n > pool.available and gi == 0 and self.tree is not None:
+                freed = self.tree.evict(n - pool.available)
+                if freed:
+                    pool.free(freed)
+                    self.stats["evicted_pages"] += len(freed)
+            if n > pool.available:
+                return False
+        return True
+
+    def _pages_for(self, plan: Sequence[Tuple[Req, int]]) -> List[int]:
+        tot = [0] * len(self.mgr.groups)
+        for r, n in plan:
+            for gi, k in enumerate(self.mgr.pages_needed(r.slot, n)):
+                tot[gi] += k
+        return tot
+
+    def _release(self, req: Req, insert: bool) -> None:
+        """Give back what a request holds; with `insert`, its full pages go to the prefix cache."""
+        if req.slot is None:
+            return
+        if insert and self.tree is not None:
+            self._insert(req)
+        self.mgr.close(req.slot)
+        if req.node is not None:
+            self.tree.unlock(req.node)
+            req.node = None
+        req.slot = None
+
+    def _insert(self, req: Req) -> None:
+        """Offer the request's full pages to the prefix cache; afterwards the request borrows them."""
+        slot = req.slot
+        n_tok = int(self.mgr.length[slot])
+        n_full = n_tok // self.P
+        borrowed = int(self.mgr.borrowed[slot])
+        if n_full <= borrowed:
+            return
+        pages = [int(p) for p in self.mgr.block_table_row(0, slot)[:n_full]]
+        table, dup, node = self.tree.insert(req.tokens[:n_full * self.P], pages, owned_from=borrowed)
+        if dup:
+            self.mgr.groups[0].pool.free(dup)
+        self.mgr.replace_prefix(slot, table, n_full)
+        self.tree.lock(node)
+        if req.node is not None:
+            self.tree.unlock(req.node)
+        req.node = node
+
+    # -- ordering --------------------------------------------------------------------------
+    def _ordered_waiting(self) -> List[Tuple[Req, List[int], object]]:
+        """Waiting requests in policy order with their prefix match; requests that should wait for
+        another one to fill the prefix cache are left out of this step."""
+        matches = {}
+        for r in self.waiting:
+            if self.tree is not None:
+                pages, node = self.tree.match(r.tokens[:-1])
+            else:
+                pages, node = [], None
+            matches[r.rid] = (pages, node)
+        order = list(self.waiting)
+        if self.policy == "lpm":
+            order.sort(key=lambda r: -len(matches[r.rid][0]))          # stable: arrival order among equals
+        elif self.policy == "lof":
+            order.sort(key=lambda r: -r.params.max_new_tokens)
+        elif self.policy == "random":
+            self._rand.shuffle(order)
+        out = []
+        if self.tree is not None:
+            inflight = {tuple(r.tokens[:IN_BATCH_PREFIX]) for r in self.running
+                        if not r.prompt_inserted and r.n_prompt >= IN_BATCH_PREFIX}
+        else:
+            inflight = set()
+        seen = set()
+        for r in order:
+            pages, node = matches[r.rid]
+            if self.tree is not None and len(pages) * self.P < IN_BATCH_PREFIX and len(r.tokens) - 1 >= IN_BATCH_PREFIX:
+                key = tuple(r.tokens[:IN_BATCH_PREFIX])
+                if key in inflight or key in seen:
+                    continue
+                seen.add(key)
+            out.append((r, pages, node))
+        return out
+
+    # -- retraction ------------------------------------------------------------------------
+    def _decode_pages(self, reqs: Sequence[Req], turns: int) -> List[int]:
+        tot = [0] * len(self.mgr.groups)
+        for r in reqs:
+            for gi, k in enumerate(self.mgr.pages_needed(r.slot, turns)):
+                tot[gi] += k
+        return tot
+
+    def _retract(self, decoding: List[Req]) -> List[Req]:
+        """Retract until the rest can decode `retract_decode_steps` more steps
+        (mini_sglang/managers/batch_info.py:372-441)."""
+        keep = sorted(decoding, key=lambda r: (r.n_output - r.n_prompt), reverse=True)
+        retracted = []
+        while keep and not self._make_room(self._decode_pages(keep, self.retract_decode_steps)):
+            if len(keep) == 1:
+                # nothing left to take pages from: one more step still has to fit
+                if self._make_room(self._decode_pages(keep, 1)):
+                    break
+                r = keep.pop()
+                r.to_abort = "out of cache pages"
+                r.check_finished()
+                self._release(r, insert=False)
+                self.running.remove(r)
+                self.stats["aborted"] += 1
+                retracted.append(r)
+                break
+            r = keep.pop()
+            self._release(r, insert=False)
+            r.retractions += 1
+            r.prompt_inserted = False
+            self.running.remove(r)
+            self.waiting.append(r)
+            retracted.append(r)
+            self.stats["retractions"] += 1
+        if keep:
+            done = sum(r.n_output for r in keep)
+            total = sum(r.params.max_new_tokens for r in keep)
+            self.new_token_ratio = min((done + self.retract_decode_steps * len(keep)) / max(total, 1), 1.0)
+        return retracted
+
+    # -- one step ----------------------------------------------------------------------------
+    def step(self) -> List[StepOutput]:
+        outputs: List[StepOutput] = []
+        # aborted before running
+        for r in [r for r in self.waiting if r.to_abort is not None]:
+            self.waiting.remove(r)
+            r.check_finished()
+            outputs.append(StepOutput(r, None, True))
+            self.stats["aborted"] += 1
+
+        plan: List[Tuple[Req, int]] = []
+        budget = self.max_step_tokens
+
+        # 1. decode: every running request with exactly one token to feed
+        decoding = [r for r in self.running if len(r.tokens) - int(self.mgr.length[r.slot]) == 1]
+        retracted: List[Req] = []
+        if decoding:
+            if not self._make_room(self._decode_pages(decoding, 1)):
+                retracted = self._retract(decoding)
+                for r in retracted:
+                    if r.finished:
+                        outputs.append(StepOutput(r, None, True))
+                decoding = [r for r in decoding if r not in retracted]
+            else:
+                self.new_token_ratio = max(self.new_token_ratio - self.ratio_decay, self.min_ratio)
+            decoding = decoding[:budget]
+            plan.extend((r, 1) for r in decoding)
+            budget -= len(decoding)
+
+        # 2. prompts already under way
+        for r in self.running:
+            pending = len(r.tokens) - int(self.mgr.length[r.slot])
+            if pending <= 1 or budget <= 0 or r in retracted:
+                continue
+            n = min(pending, self.chunk_size, budget)
+            if self._make_room(self._pages_for(plan + [(r, n)])):
+                plan.append((r, n))
+                budget -= n
+
+        # 3. new requests (none in a step that had to retract)
+        if not retracted and budget > 0 and self.waiting:
+            ratio = self.new_token_ratio
+            used = sum((len(r.tokens) - int(self.mgr.length[r.slot])) + (r.params.max_new_tokens - r.n_output) * ratio
+                       for r in self.running)
+            for r, pages, node in self._ordered_waiting():
+                if len(self.running) >= self.max_num_reqs or budget <= 0 or self.mgr.free_slots == 0:
+                    break
+                prefix = len(pages) * self.P
+                extend = len(r.tokens) - prefix
+                need = extend + (r.params.max_new_tokens - r.n_output) * ratio
+                if node is not None:
+                    self.tree.lock(node)             # the matched pages are no longer evictable
+                if need > self._free_tokens() - used:
+                    if node is not None:
+                        self.tree.unlock(node)
+                    if not self.running and not plan:
+                        # alone and still too large for the whole pool: it can never run
+                        total_tokens = self.mgr.groups[0].pool.num_pages * self.P
+                        if len(r.tokens) + 1 > total_tokens:
+                            self.waiting.remove(r)
+                            r.to_abort = f"request of {len(r.tokens)} tokens does not fit the cache of {total_tokens} tokens"
+                            r.check_finished()
+                            outputs.append(StepOutput(r, None, True))
+                            self.stats["aborted"] += 1
+                            continue
+                    break
+                slot = self.mgr.open()
+                r.slot, r.node = slot, node
+                if pages:
+                    self.mgr.adopt_prefix(slot, pages)
+                n = min(extend, self.chunk_size, budget)
+                if not self._make_room(self._pages_for(plan + [(r, n)])):
+                    self._release(r, insert=False)
+                    break
+                if r.retractions == 0:
+                    r.cached_tokens = prefix
+                    self.stats["cached_tokens"] += prefix
+                self.waiting.remove(r)
+                self.running.append(r)
+                plan.append((r, n))
+                budget -= n
+                used += need
+
+        if not plan and self.running:
+            # nobody can move: prompts under way hold the pages and none of them can grow.  The one
+            # with the least in the cache gives everything back (or is finished if it is alone).
+            victim = min(self.running, key=lambda r: int(self.mgr.length[r.slot]))
+            self.running.remove(victim)
+            if self.running:
+                self._release(victim, insert=False)
+                victim.retractions += 1
+                victim.prompt_inserted = False
+                self.waiting.append(victim)
+                self.stats["retractions"] += 1
+            else:
+                victim.to_abort = "out of cache pages"
+                victim.check_finished()
+                self._release(victim, insert=False)
+                self.stats["aborted"] += 1
+                outputs.append(StepOutput(victim, None, True))
+            return outputs
+        if not plan:
+            return outputs
+
+        # 4. run the batch
+        entries, sampled = [], []
+        for r, n in plan:
+            start = int(self.mgr.length[r.slot])
+            last = start + n == len(r.tokens)
+            entries.append(StepEntry(r.slot, r.tokens[start:start + n], [n - 1] if last else []))
+            if last:
+                sampled.append(r)
+            if n == 1 and start >= r.n_prompt:
+                self.stats["decode_tokens"] += 1
+            else:
+                self.stats["prefill_tokens"] += n
+        logits = self.runner.step(entries)
+        self.stats["steps"] += 1
+        if sampled:
+            ids = self.sampler.sample(logits, [r.params.temperature for r in sampled],
+                                      [r.rng_key for r in sampled], [r.n_output for r in sampled])
+            ids = ids.tolist() if hasattr(ids, "tolist") else list(ids)
+        else:
+            ids = []
+
+        # 5. results
+        now = time.time()
+        for r, tok in zip(sampled, ids):
+            r.tokens.append(int(tok))
+            if r.t_first_token is None:
+                r.t_first_token = now
+            if r.check_finished():
+                self._release(r, insert=True)
+                self.running.remove(r)
+                self.stats["finished"] += 1
+                outputs.append(StepOutput(r, int(tok), True))
+            else:
+                if not r.prompt_inserted and self.tree is not None:
+                    self._insert(r)               # the prompt's pages become shareable
+                r.prompt_inserted = True
+                outputs.append(StepOutput(r, int(tok), False))
+        for r in [r for r in self.running if r.to_abort is not None and not r.finished]:
+            r.check_finished()
+            self._release(r, insert=False)
+            self.running.remove(r)
+            self.stats["aborted"] += 1
+            outputs.append(StepOutput(r, None, True))
+        return outputs
+
+    # -- maintenance -----------------------------------------------------------------------
+    def flush_cache(self) -> bool:
+        """Forget the prefix cache; only when idle (mini_sglang/managers/scheduler.py:236-255)."""
+        if not self.idle:
+            return False
+        if self.tree is not None:
+            pages = self.tree.reset()
+            if pages:
+                self.mgr.groups[0].pool.free(pages)
+        return True
+
+    def check_idle_invariants(self) -> None:
+        """No request in flight => every slot is free, every page is free or in the prefix cache, and
+        nothing is pinned (mini_sglang/managers/scheduler.py:257-272)."""
+        if not self.idle:
+            raise RuntimeError("check_idle_invariants called while requests are in flight")
+        if self.tree is not None and self.tree.protected_pages:
+            raise RuntimeError(f"leak: {self.tree.protected_pages} prefix-cache pages still pinned")
+        self.mgr.check_idle(self.tree.num_nodes if self.tree is not None else 0)

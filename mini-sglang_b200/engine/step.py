@@ -1,0 +1,416 @@
+"""The step function: one forward pass over a batch of (request, its next tokens).
+
+    runner.step([StepEntry(slot, tokens, want), ...]) -> float32 logits [wanted, vocab]
+
+Entries are portions of prompts of any length beside single decoded tokens, cut anywhere.  Only
+the tokens given are computed; everything earlier is read from the cache that previous steps
+left.  The logits come back for the wanted places only, in the order of the entries and of
+`want`.  The reference's counterpart is ModelRunner.forward_generate with
+BatchInfo.prepare_for_extend / prepare_for_decode (mini_sglang/managers/model_runner.py:193-229,
+mini_sglang/managers/batch_info.py:135-302), which runs either prompts or decoded tokens, never
+both, and returns the last position only.
+
+Per step the host writes ONE pinned int32 staging buffer (token ids, positions, request
+offsets and lengths, request slots, wanted rows, and per cache group the token slots, kv
+splits and block-table rows) and copies it to the device with one transfer.  Steps in which
+every request brings exactly one token replay a CUDA graph captured for that batch size.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache import CacheManager, OutOfPages, PagedKVNeed, StateNeed
+from ..config import ModelSpec, load_config
+from ..parts import BuildEnv, DecoderModel, GroupContext, KVCacheView, StateCacheView, StepContext, Workspace
+from ..weights import CheckpointSource, RandomSource
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+SM_COUNT = 148
+MAX_KV_SPLIT = 16
+MIN_KEYS_PER_SPLIT = 256
+
+
+@dataclasses.dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()          # places among `tokens` whose logits are wanted
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class _Layout:
+    """Offsets of the fields inside the int32 staging buffer of a step."""
+
+    def __init__(self, T: int, B: int, W: int, max_pages: Sequence[int]):
+        self.T, self.B, self.W, self.max_pages = T, B, W, list(max_pages)
+        off = 0
+
+        def take(n):
+            nonlocal off
+            o = off
+            off += _align4(max(n, 1))
+            return o
+
+        self.input_ids, self.positions, self.token_req = take(T), take(T), take(T)
+        self.q_start, self.kv_len, self.slots, self.want = take(B + 1), take(B), take(B), take(W)
+        self.out_loc, self.nsplit, self.table = [], [], []
+        for mp in max_pages:
+            self.out_loc.append(take(T))
+            self.nsplit.append(take(B))
+            self.table.append(take(B * mp))
+        self.size = off
+
+
+class CacheStorage:
+    """Device arrays behind the cache manager: per cache id K and V [pages + 1, kv heads, page,
+    head size] in the activation dtype, or a state array [max requests + 1, ...]."""
+
+    def __init__(self, mgr: CacheManager, dtype: torch.dtype, device):
+        self.kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self.state: Dict[int, torch.Tensor] = {}
+        for cid, need in mgr.needs.items():
+            if isinstance(need, PagedKVNeed):
+                g = mgr.groups[mgr.group_of_cache[cid]]
+                shape = (g.pool.num_pages + 1, need.n_kv_heads, mgr.page_size, need.head_dim)
+                self.kv[cid] = (torch.zeros(shape, dtype=dtype, device=device), torch.zeros(shape, dtype=dtype, device=device))
+            elif isinstance(need, StateNeed):
+                dt = {"float32": torch.float32, "compute": dtype, "int32": torch.int32}[need.dtype]
+                self.state[cid] = torch.zeros((mgr.max_reqs + 1, *need.shape), dtype=dt, device=device)
+        if self.state:
+            mgr.on_open.append(self._zero_slot)
+
+    def _zero_slot(self, slot: int) -> None:
+        for t in self.state.values():
+            t[slot].zero_()
+
+    def bytes(self) -> int:
+        n = sum(k.numel() * k.element_size() * 2 for k, _ in self.kv.values())
+        return n + sum(t.numel() * t.element_size() for t in self.state.values())
+
+
+def kv_bytes_per_page(needs: Dict[int, object], page_size: int, dtype: torch.dtype) -> int:
+    item = torch.empty((), dtype=dtype).element_size()
+    return sum(2 * page_size * n.n_kv_heads * n.head_dim * item for n in needs.values() if isinstance(n, PagedKVNeed))
+
+
+class _Graph:
+    def __init__(self):
+        self.graph = None
+        self.dev = None        # static device staging buffer
+        self.layout = None
+        self.logits = None
+        self.max_split = None
+
+
+class ModelRunner:
+    def __init__(self, spec: ModelSpec, source_factory, *, dtype: str = "bfloat16", page_size: int = 16,
+                 num_pages: Optional[int] = None, max_reqs: int = 64, max_context_len: Optional[int] = None,
+                 max_step_tokens: int = 8192, gpu_memory_utilization: float = 0.9, device: str = "cuda:0",
+                 use_cuda_graph: bool = True, max_capture_bs: int = 128):
+        self.device = self._init_device(device)
+        self.dtype = DTYPES[dtype]
+        if self.dtype == torch.float32:
+            ops.set_true_fp32()
+        self.spec = spec
+        self.page_size = page_size
+        self.max_context_len = min(max_context_len or spec.max_context_len, spec.max_context_len)
+        self.max_step_tokens = max_step_tokens
+        env = BuildEnv(dtype=self.dtype, device=self.device)
+        self.model = DecoderModel(spec, env)
+        head_dims = sorted({n.head_dim for n in self.model.cache_needs().values() if isinstance(n, PagedKVNeed)})
+        ops.warm_up(head_dims)
+        expected = self.model.tensors()
+        src = source_factory(expected, self.dtype, self.device)
+        try:
+            with torch.no_grad():
+                self.model.load(src)
+        finally:
+            src.close()
+        needs = self.model.cache_needs()
+        if num_pages is None:
+            torch.cuda.empty_cache()
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = int(total * gpu_memory_utilization) - (total - free)
+            per_page = max(kv_bytes_per_page(needs, page_size, self.dtype), 1)
+            num_pages = max(budget // per_page, 0)
+            num_pages = min(num_pages, max_reqs * (-(-self.max_context_len // page_size)))
+            if num_pages < 1:
+                raise RuntimeError("no memory left for the cache; lower gpu_memory_utilization's complement or the model size")
+        self.mgr = CacheManager(needs, page_size=page_size, num_pages=num_pages, max_reqs=max_reqs,
+                                max_context_len=self.max_context_len, max_step_tokens=max_step_tokens)
+        self.storage = CacheStorage(self.mgr, self.dtype, self.device)
+        self.workspace = Workspace(self.device)
+        self.vocab_size = spec.vocab_size
+        self._pinned = [None, None]
+        self._pinned_ev = [None, None]
+        self._flip = 0
+        self._dev_staging = None
+        self.use_cuda_graph = use_cuda_graph
+        self.max_capture_bs = max_capture_bs
+        self._graphs: Dict[Tuple[int, Tuple[int, ...]], _Graph] = {}
+        self._graph_pool = None
+        self.kernel_launches = 0
+        self._group_geom = []
+        for g in self.mgr.groups:
+            cid = g.cache_ids[0]
+            need = needs[cid]
+            G = max(need.q_heads // need.n_kv_heads, 1) if need.q_heads else 1
+            self._group_geom.append((need.n_kv_heads, G))
+
+    # -- device ------------------------------------------------------------------------------
+    def _init_device(self, device: str) -> torch.device:
+        if not torch.cuda.is_available():
+            raise RuntimeError("mini_sglang_b200 runs on a CUDA device (B200, sm_100a) only; none is visible")
+        dev = torch.device(device)
+        torch.cuda.set_device(dev)
+        return dev
+
+    def _alloc_pinned(self, n: int) -> torch.Tensor:
+        return torch.empty(n, dtype=torch.int32, pin_memory=True)
+
+    def _new_event(self):
+        return torch.cuda.Event()
+
+    # -- construction helpers ------------------------------------------------------------
+    @classmethod
+    def from_model_dir(cls, model_dir: str, **kw) -> "ModelRunner":
+        _, spec = load_config(model_dir)
+        return cls(spec, lambda exp, dt, dev: CheckpointSource(model_dir, exp, dt, dev), **kw)
+
+    @classmethod
+    def from_random(cls, spec: ModelSpec, seed: int, **kw) -> "ModelRunner":
+        return cls(spec, lambda exp, dt, dev: RandomSource(exp, seed, dt, dev), **kw)
+
+    # -- request slots -------------------------------------------------------------------
+    def open(self) -> int:
+        return self.mgr.open()
+
+    def close(self, slot: int) -> None:
+        self.mgr.close(slot)
+
+    # -- staging ---------------------------------------------------------------------------
+    def _pinned_buffer(self, n: int) -> torch.Tensor:
+        i = self._flip
+        self._flip ^= 1
+        if self._pinned_ev[i] is not None:
+            self._pinned_ev[i].synchronize()
+        buf = self._pinned[i]
+        if buf is None or buf.numel() < n:
+            buf = self._alloc_pinned(max(n, 4096))
+            self._pinned[i] = buf
+        return buf, i
+
+    def _plan_splits(self, gi: int, q_lens: Sequence[int], kv_lens: Sequence[int], cap: int) -> List[int]:
+        """kv splits per request: only short query runs over long contexts are split, and only
+        while the launch would otherwise leave most of the 148 SMs idle."""
+        n_kv, G = self._group_geom[gi]
+        qt = max(16 // G, 1) if G <= 16 else 1
+        chunks = 1 if G <= 16 else -(-G // 16)
+        blocks = sum(-(-q // qt) for q in q_lens) * n_kv * chunks
+        if blocks >= 2 * SM_COUNT or cap <= 1:
+            return [1] * len(q_lens)
+        want = -(-2 * SM_COUNT // max(blocks, 1))
+        window = self.mgr.groups[gi].window
+        out = []
+        for q, kv in zip(q_lens, kv_lens):
+            keys = min(kv, window + q) if window else kv
+            out.append(1 if q > 16 else max(1, min(want, keys // MIN_KEYS_PER_SPLIT, cap)))
+        return out
+
+    def _fill(self, host: np.ndarray, lay: _Layout, entries: Sequence[StepEntry], starts: Sequence[int],
+              want_rows: Sequence[int], nsplits: Sequence[Sequence[int]], pad_to: int = 0) -> None:
+        """Write every field of the staging buffer.  Rows beyond len(entries) (graph padding) are
+        single tokens of a request of length 1 on the dump page."""
+        T, B = lay.T, lay.B
+        host[:lay.size] = 0
+        t = 0
+        for r, (e, s) in enumerate(zip(entries, starts)):
+            n = len(e.tokens)
+            host[lay.input_ids + t: lay.input_ids + t + n] = e.tokens
+            host[lay.positions + t: lay.positions + t + n] = np.arange(s, s + n, dtype=np.int32)
+            host[lay.token_req + t: lay.token_req + t + n] = r
+            host[lay.q_start + r] = t
+            host[lay.kv_len + r] = s + n
+            host[lay.slots + r] = e.slot
+            for gi in range(len(self.mgr.groups)):
+                host[lay.out_loc[gi] + t: lay.out_loc[gi] + t + n] = self.mgr.slot_mapping(gi, e.slot, s, n)
+                row = self.mgr.block_table_row(gi, e.slot)
+                mp = lay.max_pages[gi]
+                host[lay.table[gi] + r * mp: lay.table[gi] + r * mp + len(row)] = row
+                host[lay.nsplit[gi] + r] = nsplits[gi][r]
+            t += n
+        for r in range(len(entries), B):          # padding rows of a captured batch size
+            host[lay.token_req + t] = r
+            host[lay.q_start + r] = t
+            host[lay.kv_len + r] = 1
+            for gi in range(len(self.mgr.groups)):
+                host[lay.nsplit[gi] + r] = 1
+            t += 1
+        host[lay.q_start + B] = t
+        host[lay.want: lay.want + len(want_rows)] = want_rows
+
+    def _context(self, dev: torch.Tensor, lay: _Layout, q_lens, kv_lens, slots, max_splits, uniform: bool) -> StepContext:
+        def v(off, n):
+            return dev[off: off + n]
+
+        groups = []
+        for gi, g in enumerate(self.mgr.groups):
+            mp = lay.max_pages[gi]
+            groups.append(GroupContext(block_table=v(lay.table[gi], lay.B * mp).view(lay.B, mp),
+                                       out_loc=v(lay.out_loc[gi], lay.T),
+                                       nsplit=v(lay.nsplit[gi], lay.B) if max_splits[gi] > 1 else None,
+                                       max_split=max_splits[gi], window=g.window))
+        return StepContext(T=lay.T, B=lay.B, page_size=self.page_size, input_ids=v(lay.input_ids, lay.T),
+                           positions=v(lay.positions, lay.T), q_start=v(lay.q_start, lay.B + 1),
+                           kv_len=v(lay.kv_len, lay.B), token_req=v(lay.token_req, lay.T), slots=v(lay.slots, lay.B),
+                           groups=groups, host_q_lens=list(q_lens), host_kv_lens=list(kv_lens),
+                           host_slots=list(slots), uniform_decode=uniform, workspace=self.workspace)
+
+    def _caches(self, ctx: StepContext) -> Dict[int, object]:
+        views: Dict[int, object] = {}
+        for cid, (k, v) in self.storage.kv.items():
+            views[cid] = KVCacheView(k, v, ctx.groups[self.mgr.group_of_cache[cid]], self.page_size)
+        for cid, st in self.storage.state.items():
+            views[cid] = StateCacheView(st)
+        return views
+
+    # -- the step ----------------------------------------------------------------------------
+    def pages_short(self, entries: Sequence[StepEntry]) -> List[int]:
+        """Per group: how many pages the step needs beyond what is free (all zeros: it fits)."""
+        need = [0] * len(self.mgr.groups)
+        for e in entries:
+            for gi, n in enumerate(self.mgr.pages_needed(e.slot, len(e.tokens))):
+                need[gi] += n
+        return [max(0, n - g.pool.available) for n, g in zip(need, self.mgr.groups)]
+
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        V = self.vocab_size
+        for e in entries:
+            toks = np.asarray(e.tokens)
+            if toks.min() < 0 or toks.max() >= V:
+                raise ValueError(f"token id outside [0, {V}) in the entry of slot {e.slot}")
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise ValueError(f"wanted place {w} is outside the entry's {len(e.tokens)} tokens")
+        short = self.pages_short(entries)
+        if any(short):
+            raise OutOfPages(f"the step needs {short} more pages than are free (per group)")
+        starts = [int(self.mgr.length[e.slot]) for e in entries]
+        for e in entries:
+            self.mgr.reserve(e.slot, len(e.tokens))
+        q_lens = [len(e.tokens) for e in entries]
+        kv_lens = [s + n for s, n in zip(starts, q_lens)]
+        want_rows, t = [], 0
+        for e in entries:
+            want_rows.extend(t + w for w in e.want)
+            t += len(e.tokens)
+        T, B = t, len(entries)
+        uniform = all(n == 1 for n in q_lens)
+        all_last = uniform and len(want_rows) == B and all(len(e.want) == 1 for e in entries)
+
+        if self.use_cuda_graph and all_last and B <= self.max_capture_bs:
+            logits = self._step_graph(entries, starts, q_lens, kv_lens)
+        else:
+            nsplits = [self._plan_splits(gi, q_lens, kv_lens, MAX_KV_SPLIT) for gi in range(len(self.mgr.groups))]
+            max_splits = [max(ns) for ns in nsplits]
+            max_pages = [max(int(g.n_pages[e.slot]) for e in entries) for g in self.mgr.groups]
+            lay = _Layout(T, B, len(want_rows), max_pages)
+            host, idx = self._pinned_buffer(lay.size)
+            self._fill(host.numpy(), lay, entries, starts, want_rows, nsplits)
+            if self._dev_staging is None or self._dev_staging.numel() < lay.size:
+                self._dev_staging = torch.empty(max(lay.size, 1 << 16), dtype=torch.int32, device=self.device)
+            dev = self._dev_staging
+            dev[:lay.size].copy_(host[:lay.size], non_blocking=True)
+            self._mark(idx)
+            ctx = self._context(dev, lay, q_lens, kv_lens, [e.slot for e in entries], max_splits, uniform)
+            rows = dev[lay.want: lay.want + len(want_rows)]
+            logits = self.model.forward(ctx, self._caches(ctx), rows)
+        for e in entries:
+            self.mgr.commit(e.slot, len(e.tokens))
+        return logits
+
+    def _mark(self, idx: int) -> None:
+        ev = self._pinned_ev[idx]
+        if ev is None:
+            ev = self._pinned_ev[idx] = self._new_event()
+        ev.record()
+
+    # -- decode through CUDA graphs --------------------------------------------------------------
+    @staticmethod
+    def _bucket(b: int) -> int:
+        """Captured batch sizes: 1, 2, 4, 8, then multiples of 16 (the reference's buckets,
+        mini_sglang/managers/cuda_graph_runner.py:72-82)."""
+        for c in (1, 2, 4, 8):
+            if b <= c:
+                return c
+        return -(-b // 16) * 16
+
+    def _graph_max_split(self, gi: int, b: int) -> int:
+        n_kv, G = self._group_geom[gi]
+        chunks = 1 if G <= 16 else -(-G // 16)
+        blocks = b * n_kv * chunks
+        if blocks >= 2 * SM_COUNT:
+            return 1
+        return max(1, min(MAX_KV_SPLIT, -(-2 * SM_COUNT // blocks)))
+
+    def _step_graph(self, entries, starts, q_lens, kv_lens) -> torch.Tensor:
+        B = len(entries)
+        b = self._bucket(B)
+        need_pages = [max(int(g.n_pages[e.slot]) for e in entries) for g in self.mgr.groups]
+        mp = tuple(max(8, 1 << (n - 1).bit_length()) for n in need_pages)
+        key = (b, mp)
+        gr = self._graphs.get(key)
+        if gr is None:
+            gr = self._capture(b, mp)
+            self._graphs[key] = gr
+        lay = gr.layout
+        nsplits = []
+        for gi in range(len(self.mgr.groups)):
+            ns = self._plan_splits(gi, q_lens, kv_lens, gr.max_split[gi])
+            nsplits.append(ns)
+        host, idx = self._pinned_buffer(lay.size)
+        self._fill(host.numpy(), lay, entries, starts, list(range(b)), nsplits)
+        gr.dev.copy_(host[:lay.size], non_blocking=True)
+        self._mark(idx)
+        gr.graph.replay()
+        return gr.logits[:B]
+
+    def _capture(self, b: int, mp: Tuple[int, ...]) -> _Graph:
+        gr = _Graph()
+        lay = _Layout(b, b, b, mp)
+        gr.layout = lay
+        gr.dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
+        gr.max_split = [self._graph_max_split(gi, b) for gi in range(len(self.mgr.groups))]
+        host = np.zeros(lay.size, dtype=np.int32)
+        self._fill(host, lay, [], [], list(range(b)), [[1] * b for _ in self.mgr.groups])
+        gr.dev.copy_(torch.from_numpy(host))
+        ctx = self._context(gr.dev, lay, [1] * b, [1] * b, [0] * b, gr.max_split, True)
+        caches = self._caches(ctx)
+        rows = gr.dev[lay.want: lay.want + b]
+        # two eager runs size every scratch buffer outside the graph's private pool
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.model.forward(ctx, caches, rows)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        gr.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr.graph, pool=self._graph_pool):
+            gr.logits = self.model.forward(ctx, caches, rows)
+        return gr

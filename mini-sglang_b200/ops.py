@@ -1,0 +1,275 @@
+"""Python face of the engine's CUDA kernels.
+
+Every function here launches hand-written sm_100a kernels from `csrc/` on the current CUDA
+stream of torch and returns torch tensors.  There is no other implementation behind them: a
+tensor that is not on a CUDA device, a missing compiler or an unsupported size raises.
+Matrix products are the one exception to "hand-written": `linear` calls the library GEMM that
+torch binds (cuBLAS), in bfloat16 with float32 accumulation or in true float32 (TF32 off).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from .csrc import build as _build
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_ERR = {1: "element type not handled", 2: "size not supported by the kernel", 3: "kernel launch failed",
+        4: "pointer not aligned"}
+
+c_void_p, c_int, c_float, c_ll, c_ull = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_ulonglong
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        detail = ""
+        if code == 3:
+            detail = f" ({torch.cuda.get_device_name()}: the kernels are built for sm_100a only)"
+        raise KernelError(f"{what}: {_ERR.get(code, f'error {code}')}{detail}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the engine's kernels run on a CUDA device only; got a tensor on " + str(t.device))
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not handled; the engine computes in bfloat16 or float32") from None
+
+
+_common = None
+_attn = {}
+
+
+def _lib():
+    global _common
+    if _common is None:
+        lib = _build.common_library()
+        lib.msgl_embedding.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.msgl_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p,
+                                     c_int, c_int, c_int, c_void_p]
+        lib.msgl_qknorm_rope_kvwrite.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.msgl_swiglu.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.msgl_cast_from_f32.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_void_p]
+        lib.msgl_sample.argtypes = [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_ull, c_void_p,
+                                    c_void_p]
+        _common = lib
+    return _common
+
+
+def _attn_lib(head_dim: int):
+    hd = head_dim if head_dim in _build.MMA_HEAD_DIMS else 128
+    lib = _attn.get(hd)
+    if lib is None:
+        lib = _build.attention_library(hd)
+        lib.msgl_attention.argtypes = [c_void_p] * 10 + [c_int] * 9 + [c_float] + [c_int] * 6 + [c_void_p]
+        lib.msgl_attention_combine.argtypes = [c_void_p] * 5 + [c_int] * 5 + [c_void_p]
+        lib.msgl_attention_head_dim.restype = c_int
+        _attn[hd] = lib
+    return lib
+
+
+def warm_up(head_dims=()) -> None:
+    """Build and load the libraries a model needs (compiles at the first call)."""
+    _lib()
+    for hd in head_dims:
+        _attn_lib(hd)
+
+
+# ---------------------------------------------------------------------------------------
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """ids int32 [T], table [V, H] -> float32 [T, H] (the residual stream starts in float32)."""
+    _need_cuda(ids, table)
+    T, (V, H) = ids.numel(), table.shape
+    assert ids.dtype == torch.int32 and table.is_contiguous()
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _check(_lib().msgl_embedding(_ptr(ids), _ptr(table), _ptr(out), T, H, V, _dt(table), _stream()), "embedding")
+    return out
+
+
+def rmsnorm(weight: torch.Tensor, eps: float, *, x: Optional[torch.Tensor] = None,
+            residual: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None,
+            rows: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = rmsnorm(residual + x) * weight, the sum and the norm in float32.
+
+    x: activation dtype [N, H] or None; residual: float32 [N, H] or None; residual_out: float32
+    buffer that receives the sum (may be `residual` itself when `rows` is None);
+    rows: int32 [R] picks input rows (outputs are then [R, H]).  Returns y in `out_dtype`
+    (default: x's dtype)."""
+    _need_cuda(weight, x, residual, residual_out, rows)
+    src = x if x is not None else residual
+    assert src is not None and src.dim() == 2 and src.is_contiguous()
+    H = src.shape[1]
+    n_out = rows.numel() if rows is not None else src.shape[0]
+    if out_dtype is None:
+        out_dtype = x.dtype if x is not None else torch.float32
+    if x is not None:
+        assert x.dtype == out_dtype
+    if residual is not None:
+        assert residual.dtype == torch.float32 and residual.shape[1] == H
+    assert weight.numel() == H and weight.dtype in (torch.float32, torch.bfloat16)
+    if out is None:
+        out = torch.empty((n_out, H), dtype=out_dtype, device=src.device)
+    code = _lib().msgl_rmsnorm(_ptr(x), _ptr(residual), _ptr(residual_out), _ptr(rows), _ptr(weight),
+                               int(weight.dtype == torch.float32), float(eps), _ptr(out), n_out, H, _DT[out_dtype],
+                               _stream())
+    _check(code, "rmsnorm")
+    return out
+
+
+def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, n_q: int, n_kv: int, d: int, *,
+                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                        rope_table: Optional[torch.Tensor], out_loc: Optional[torch.Tensor],
+                        k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], page_size: int,
+                        q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-head RMSNorm of q and k (if weights are given), rotary encoding from `rope_table`
+    [max_pos, rot] float32 (if given), k and v written to the paged cache at token slots `out_loc`
+    (if a cache is given), q returned as [T, n_q, d]."""
+    _need_cuda(qkv, positions, q_weight, k_weight, rope_table, out_loc, k_cache, v_cache)
+    T = qkv.shape[0]
+    assert qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (n_q + 2 * n_kv) * d
+    if q_out is None:
+        q_out = torch.empty((T, n_q, d), dtype=qkv.dtype, device=qkv.device)
+    w_f32 = 0
+    if q_weight is not None:
+        assert k_weight is not None and q_weight.dtype == k_weight.dtype
+        w_f32 = int(q_weight.dtype == torch.float32)
+    rot, max_pos = (rope_table.shape[1], rope_table.shape[0]) if rope_table is not None else (0, 0)
+    if rope_table is not None:
+        assert rope_table.dtype == torch.float32 and rope_table.is_contiguous()
+    if k_cache is not None:
+        assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+    code = _lib().msgl_qknorm_rope_kvwrite(_ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(out_loc), _ptr(q_weight),
+                                           _ptr(k_weight), w_f32, float(eps), _ptr(rope_table), rot, max_pos,
+                                           _ptr(q_out), _ptr(k_cache), _ptr(v_cache), page_size, n_q, n_kv, d, T,
+                                           _dt(qkv), _stream())
+    _check(code, f"qknorm_rope_kvwrite (head size {d})")
+    return q_out
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[T, 2I] (gate first) -> [T, I] = silu(gate) * up."""
+    _need_cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
+    T, I = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
+    _check(_lib().msgl_swiglu(_ptr(gate_up), _ptr(out), T, I, _dt(gate_up), _stream()), "swiglu")
+    return out
+
+
+def cast_from_f32(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _check(_lib().msgl_cast_from_f32(_ptr(x), _ptr(out), x.numel(), _DT[dtype], _stream()), "cast")
+    return out
+
+
+def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor], row_keys: Optional[torch.Tensor],
+           steps: Optional[torch.Tensor], seed: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 logits [N, V] -> int32 token ids [N]; greedy where temperature is 0."""
+    _need_cuda(logits, temperatures, row_keys, steps)
+    assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1
+    N, V = logits.shape
+    if out is None:
+        out = torch.empty((N,), dtype=torch.int32, device=logits.device)
+    if temperatures is not None:
+        assert temperatures.dtype == torch.float32 and row_keys.dtype == torch.int32 and steps.dtype == torch.int32
+    code = _lib().msgl_sample(_ptr(logits), N, V, logits.stride(0), _ptr(temperatures), _ptr(row_keys), _ptr(steps),
+                              seed & 0xFFFFFFFFFFFFFFFF, _ptr(out), _stream())
+    _check(code, "sample")
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------------------
+VARIANT_SIMT, VARIANT_MMA_ROWS, VARIANT_MMA_DECODE = 0, 1, 2
+
+
+def attention_tile_tokens(variant: int, group: int) -> int:
+    """Tokens per query tile of a kernel variant for a given group size (q heads per kv head)."""
+    rows = 64 if variant == VARIANT_MMA_ROWS else 16
+    return rows // group if group <= rows else 1
+
+
+def mma_supported(head_dim: int, dtype: torch.dtype) -> bool:
+    return dtype == torch.bfloat16 and head_dim in _build.MMA_HEAD_DIMS
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *,
+              q_start: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor,
+              nsplit: Optional[torch.Tensor], part_o: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
+              n_kv: int, page_size: int, window: int, max_split: int, scale: float, qlen_min: int, qlen_max: int,
+              uniform_decode: bool, variant: int, grid_x: int) -> None:
+    """One launch of the paged attention kernel over the requests whose q_len lies in
+    [qlen_min, qlen_max]; see csrc/attention.cu for the meaning of every argument."""
+    _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table, nsplit, part_o, part_ml)
+    T, n_q, d = q.shape
+    B = kv_len.numel()
+    assert q.is_contiguous() and out.is_contiguous() and block_table.dim() == 2 and block_table.stride(1) == 1
+    code = _attn_lib(d).msgl_attention(
+        _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table),
+        _ptr(nsplit), _ptr(part_o), _ptr(part_ml), B, T, n_q, n_kv, d, page_size, block_table.stride(0), window,
+        max_split, float(scale), qlen_min, qlen_max, int(uniform_decode), variant, grid_x, _dt(q), _stream())
+    _check(code, f"attention (head size {d}, variant {variant})")
+
+
+def attention_combine(part_o: torch.Tensor, part_ml: torch.Tensor, token_req: Optional[torch.Tensor],
+                      nsplit: torch.Tensor, out: torch.Tensor, max_split: int) -> None:
+    _need_cuda(part_o, part_ml, token_req, nsplit, out)
+    T, n_q, d = out.shape
+    code = _attn_lib(d).msgl_attention_combine(_ptr(part_o), _ptr(part_ml), _ptr(token_req), _ptr(nsplit), _ptr(out),
+                                               T, n_q, d, max_split, _dt(out), _stream())
+    _check(code, "attention_combine")
+
+
+# ---------------------------------------------------------------------------------------
+# matrix products: the library GEMM (cuBLAS through torch)
+# ---------------------------------------------------------------------------------------
+
+def set_true_fp32() -> None:
+    """float32 products are real float32: no TF32, no reduced-precision reduction."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.set_float32_matmul_precision("highest")
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x @ weight^T (+ bias); weight is [out, in] as stored in the checkpoint."""
+    _need_cuda(x, weight, bias)
+    if out_dtype is not None and out_dtype != x.dtype:
+        y = torch.mm(x, weight.t(), out_dtype=out_dtype)
+        if bias is not None:
+            y += bias.to(out_dtype)
+        return y
+    return torch.nn.functional.linear(x, weight, bias)

@@ -1,0 +1,114 @@
+"""Interfaces and registries of the parts a model is assembled from.
+
+A part is built from a PartSpec (its sizes and constants), the checkpoint-name prefix of the
+layer it sits in, and a BuildEnv (activation dtype, device).  It declares the checkpoint
+tensors it reads (`tensors`), takes them from a source (`load`), and computes (`forward`).
+A part never sees config.json, the model's name, or any other part's internals.
+
+    Mixer          forward(x [T, H], ctx, cache, writes_cache) -> [T, H]
+                   cache_need() -> PagedKVNeed | StateNeed | None
+    FeedForward    forward(x [T, H], ctx) -> [T, H]
+    Norm           forward(x=None, residual=None, residual_out=None, rows=None) -> y
+    PositionEncoding   rotary_table() -> float32 [max_pos, rot] or None;  apply(q, k, positions)
+    Block          forward(delta, residual, ctx, cache, writes_cache) -> (delta, residual)
+
+New kinds are added with the `register_*` decorators below; a model description then names
+them by key.  The activations between parts are `env.dtype`; the residual stream is float32.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Any, Callable, Dict, Optional
+
+import torch
+
+from ..config.spec import PartSpec
+from ..weights.loader import TensorDecl
+
+
+@dataclasses.dataclass
+class BuildEnv:
+    dtype: torch.dtype
+    device: torch.device
+
+
+class Part:
+    def __init__(self, spec: PartSpec, prefix: str, env: BuildEnv):
+        self.spec, self.prefix, self.env = spec, prefix, env
+
+    def name(self, suffix: str) -> str:
+        return f"{self.prefix}.{suffix}" if self.prefix else suffix
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        return {}
+
+    def load(self, src) -> None:
+        pass
+
+
+class Mixer(Part):
+    def cache_need(self):
+        return None
+
+    def forward(self, x, ctx, cache, writes_cache: bool = True):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, ctx):
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, x=None, residual=None, residual_out=None, rows=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotary_table(self) -> Optional[torch.Tensor]:
+        """float32 [max_positions, rotary_dim] = cos | sin if this encoding is a NeoX-style rotation
+        that the fused q/k kernel can apply; None otherwise (then `apply` is called)."""
+        return None
+
+    def apply(self, q, k, positions):
+        raise NotImplementedError
+
+
+class Block(Part):
+    def forward(self, delta, residual, ctx, cache, writes_cache: bool = True):
+        raise NotImplementedError
+
+
+MIXERS: Dict[str, Callable[..., Mixer]] = {}
+FEED_FORWARDS: Dict[str, Callable[..., FeedForward]] = {}
+NORMS: Dict[str, Callable[..., Norm]] = {}
+POSITION_ENCODINGS: Dict[str, Callable[..., PositionEncoding]] = {}
+BLOCKS: Dict[str, Callable[..., Block]] = {}
+EMBEDDINGS: Dict[str, Callable[..., Part]] = {}
+HEADS: Dict[str, Callable[..., Part]] = {}
+
+
+def _register(table: Dict[str, Any], what: str):
+    def deco_factory(kind: str):
+        def deco(cls):
+            table[kind] = cls
+            return cls
+        return deco
+    deco_factory.__doc__ = f"Class decorator: make a {what} available to model descriptions under a key."
+    return deco_factory
+
+
+register_mixer = _register(MIXERS, "mixer")
+register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
+register_norm = _register(NORMS, "norm")
+register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
+register_block = _register(BLOCKS, "block arrangement")
+register_embedding = _register(EMBEDDINGS, "embedding")
+register_head = _register(HEADS, "output head")
+
+
+def build_part(table: Dict[str, Any], what: str, spec: PartSpec, prefix: str, env: BuildEnv, **kw):
+    if spec.kind not in table:
+        raise KeyError(f"unknown {what} {spec.kind!r}; registered: " + ", ".join(sorted(table)))
+    return table[spec.kind](spec, prefix, env, **kw)
