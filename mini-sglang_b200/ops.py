@@ -154,6 +154,9 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, n_q: int, n_
     _need_cuda(qkv, positions, q_weight, k_weight, rope_table, out_loc, k_cache, v_cache)
     T = qkv.shape[0]
     assert qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (n_q + 2 * n_kv) * d
+    assert positions.numel() == T and positions.dtype == torch.int32
+    if out_loc is not None:
+        assert out_loc.numel() == T and out_loc.dtype == torch.int32, "one cache slot per token"
     if q_out is None:
         q_out = torch.empty((T, n_q, d), dtype=qkv.dtype, device=qkv.device)
     w_f32 = 0
@@ -235,6 +238,10 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     T, n_q, d = q.shape
     B = kv_len.numel()
     assert q.is_contiguous() and out.is_contiguous() and block_table.dim() == 2 and block_table.stride(1) == 1
+    assert q_start.numel() == B + 1 and block_table.shape[0] == B and out.shape == q.shape
+    assert nsplit is None or nsplit.numel() == B
+    if max_split > 1:
+        assert part_o.numel() >= max_split * T * n_q * d and part_ml.numel() >= max_split * T * n_q * 2
     code = _attn_lib(d).msgl_attention(
         _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table),
         _ptr(nsplit), _ptr(part_o), _ptr(part_ml), B, T, n_q, n_kv, d, page_size, block_table.stride(0), window,

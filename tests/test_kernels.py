@@ -1,0 +1,306 @@
+"""Each CUDA kernel alone against a plain float32 torch restatement of the same operation, at
+sizes other than the engine's tiny models (odd widths, several head sizes, page sizes, windows,
+kv splits).  The references below are written here, from the formulas, and share nothing with
+the engine."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def ops():
+    from mini_sglang_b200 import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,V", [(1, 64, 50), (37, 120, 333), (300, 4096, 1000)])
+def test_embedding(dtype, T, H, V):
+    g = torch.Generator(device="cpu").manual_seed(0)
+    table = torch.randn(V, H, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32).to(DEV)
+    out = ops().embedding(ids, table)
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out, table[ids.long()].float(), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,H", [(1, 16), (5, 120), (33, 4096), (3, 12288 + 8)])
+def test_rmsnorm_modes(dtype, wdtype, rows, H):
+    g = torch.Generator(device="cpu").manual_seed(1)
+    x = torch.randn(rows, H, generator=g).to(dtype).to(DEV)
+    res = torch.randn(rows, H, generator=g).to(DEV)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(wdtype).to(DEV)
+    eps = 1e-5
+
+    def ref(v):
+        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.float())
+
+    o = ops()
+    # residual only
+    y = o.rmsnorm(w, eps, residual=res, out_dtype=dtype)
+    torch.testing.assert_close(y.float(), ref(res).to(dtype).float(), **tol(dtype))
+    # sum fused, stream updated in place
+    res2 = res.clone()
+    y = o.rmsnorm(w, eps, x=x, residual=res2, residual_out=res2, out_dtype=dtype)
+    v = res + x.float()
+    torch.testing.assert_close(res2, v, rtol=0, atol=0)
+    torch.testing.assert_close(y.float(), ref(v).to(dtype).float(), **tol(dtype))
+    # plain norm of an activation
+    y = o.rmsnorm(w, eps, x=x, out_dtype=dtype)
+    torch.testing.assert_close(y.float(), ref(x.float()).to(dtype).float(), **tol(dtype))
+    # gather of rows, stream untouched
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    y = o.rmsnorm(w, eps, x=x, residual=res, rows=idx, out_dtype=dtype)
+    torch.testing.assert_close(y.float(), ref(v)[idx.long()].to(dtype).float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,I", [(1, 8), (7, 100), (65, 12288)])
+def test_swiglu(dtype, T, I):
+    g = torch.Generator(device="cpu").manual_seed(2)
+    gu = (2 * torch.randn(T, 2 * I, generator=g)).to(dtype).to(DEV)
+    out = ops().swiglu(gu)
+    a, b = gu[:, :I].float(), gu[:, I:].float()
+    ref = (a / (1 + torch.exp(-a)) * b).to(dtype)
+    torch.testing.assert_close(out.float(), ref.float(), **tol(dtype))
+
+
+# ---------------------------------------------------------------------------------------
+def rope_table(max_pos, rot, theta):
+    idx = torch.arange(0, rot, 2, dtype=torch.float32)
+    inv = 1.0 / (theta ** (idx / rot))
+    fr = torch.arange(max_pos, dtype=torch.float32)[:, None] * inv[None, :]
+    return torch.cat((fr.cos(), fr.sin()), -1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,d,rot,P,norm,wdtype", [
+    (4, 2, 16, 16, 1, True, torch.bfloat16),
+    (6, 2, 32, 32, 4, True, torch.float32),
+    (15, 3, 48, 48, 16, True, torch.bfloat16),
+    (8, 1, 128, 64, 16, False, torch.bfloat16),       # partial rotation, no norm
+    (2, 2, 256, 256, 8, True, torch.float32),
+    (3, 1, 80, 0, 2, True, torch.bfloat16),           # no rotation at all
+])
+def test_qknorm_rope_kvwrite(dtype, n_q, n_kv, d, rot, P, norm, wdtype):
+    g = torch.Generator(device="cpu").manual_seed(3)
+    T, max_pos, eps = 19, 300, 1e-6
+    pages = -(-T // P) + 3
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * d, generator=g).to(dtype)
+    pos = torch.randint(0, max_pos, (T,), generator=g, dtype=torch.int32)
+    loc = torch.randperm(pages * P - P, generator=g)[:T].to(torch.int32) + P      # never the dump page
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).to(wdtype) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).to(wdtype) if norm else None
+    table = rope_table(max_pos, rot, 10000.0) if rot else None
+    kc = torch.zeros(pages, n_kv, P, d, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    cu = lambda t: None if t is None else t.to(DEV)
+    q = ops().qknorm_rope_kvwrite(cu(qkv), cu(pos), n_q, n_kv, d, q_weight=cu(qw), k_weight=cu(kw), eps=eps,
+                                  rope_table=cu(table), out_loc=cu(loc), k_cache=kc, v_cache=vc, page_size=P)
+    # reference
+    x = qkv.float()
+    qr = x[:, :n_q * d].reshape(T, n_q, d)
+    kr = x[:, n_q * d:(n_q + n_kv) * d].reshape(T, n_kv, d)
+    vr = x[:, (n_q + n_kv) * d:].reshape(T, n_kv, d)
+    if norm:
+        qr = qr * torch.rsqrt(qr.pow(2).mean(-1, keepdim=True) + eps) * qw.float()
+        kr = kr * torch.rsqrt(kr.pow(2).mean(-1, keepdim=True) + eps) * kw.float()
+    if rot:
+        cs = table[pos.long()]
+        c, s = cs[:, None, :rot // 2], cs[:, None, rot // 2:]
+
+        def rope(t):
+            a, b, rest = t[..., :rot // 2], t[..., rot // 2:rot], t[..., rot:]
+            return torch.cat((a * c - b * s, a * s + b * c, rest), -1)
+        qr, kr = rope(qr), rope(kr)
+    torch.testing.assert_close(q.float().cpu(), qr.to(dtype).float(), **tol(dtype))
+    pg, off = (loc // P).long(), (loc % P).long()
+    torch.testing.assert_close(kc.cpu()[pg, :, off, :].float(), kr.to(dtype).float(), **tol(dtype))
+    torch.testing.assert_close(vc.cpu()[pg, :, off, :].float(), vr.to(dtype).float(), rtol=0, atol=0)
+    # nothing else was written
+    mask = torch.ones(pages, P, dtype=torch.bool)
+    mask[pg, off] = False
+    assert kc.cpu().permute(0, 2, 1, 3)[mask].abs().sum() == 0
+
+
+# ---------------------------------------------------------------------------------------
+def test_sampling_greedy_and_race():
+    import plain_qwen3 as P
+    g = torch.Generator(device="cpu").manual_seed(4)
+    N, V = 6, 333
+    logits = (3 * torch.randn(N, V, generator=g)).float()
+    logits[1, 77] = logits[1, 5] = logits[1].max() + 1          # tie: lowest index wins
+    temps = torch.tensor([0.0, 0.0, 0.7, 1.0, 0.0, 1.3])
+    keys = torch.tensor([11, 12, 13, 14, 15, 16], dtype=torch.int32)
+    steps = torch.tensor([0, 1, 2, 3, 4, 5], dtype=torch.int32)
+    seed = 1234567890123
+    out = ops().sample(logits.to(DEV), temps.to(DEV), keys.to(DEV), steps.to(DEV), seed).cpu()
+    noise = torch.stack([P.exponential_noise(seed, int(k), int(s), V) for k, s in zip(keys, steps)])
+    ref = P.sample_with_noise(logits, temps, noise)
+    assert out.tolist() == ref.tolist()
+    assert out[1].item() == 5
+    # all-greedy fast path
+    out2 = ops().sample(logits.to(DEV), None, None, None, seed).cpu()
+    assert out2.tolist() == logits.argmax(-1).tolist() or out2[1].item() == 5
+    # a request's draw does not depend on its row in the batch
+    out3 = ops().sample(logits[[3, 2]].to(DEV), temps[[3, 2]].to(DEV), keys[[3, 2]].to(DEV), steps[[3, 2]].to(DEV), seed).cpu()
+    assert out3.tolist() == [out[3].item(), out[2].item()]
+
+
+def test_sampling_distribution():
+    # chi-square of 4000 draws on a small vocabulary against softmax(logits / T)
+    V, n = 12, 4000
+    logits = torch.linspace(-1.5, 1.5, V).repeat(n, 1)
+    T = 0.8
+    temps = torch.full((n,), T)
+    keys = torch.arange(n, dtype=torch.int32)
+    steps = torch.zeros(n, dtype=torch.int32)
+    out = ops().sample(logits.to(DEV), temps.to(DEV), keys.to(DEV), steps.to(DEV), 99).cpu()
+    p = torch.softmax(logits[0] / T, -1)
+    counts = torch.bincount(out.long(), minlength=V).float()
+    chi2 = ((counts - n * p) ** 2 / (n * p)).sum().item()
+    assert chi2 < 40.0, chi2          # 11 degrees of freedom: P(chi2 > 40) < 1e-4
+
+
+# ---------------------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------------------
+def attention_reference(q, K, V, q_lens, kv_lens, scale, window):
+    """q [T, n_q, d]; K, V: per request dense [L, n_kv, d] float32."""
+    T, n_q, d = q.shape
+    out = torch.zeros(T, n_q, d)
+    t = 0
+    for r, (ql, L) in enumerate(zip(q_lens, kv_lens)):
+        n_kv = K[r].shape[1]
+        G = n_q // n_kv
+        pos = torch.arange(L)
+        for j in range(ql):
+            p = L - ql + j
+            ok = pos <= p
+            if window:
+                ok &= pos > p - window
+            for h in range(n_q):
+                s = (K[r][:, h // G] @ q[t + j, h]) * scale
+                s = s.masked_fill(~ok, float("-inf"))
+                out[t + j, h] = torch.softmax(s, -1) @ V[r][:, h // G]
+        t += ql
+    return out
+
+
+def run_attention_case(dtype, n_q, n_kv, d, P, q_lens, kv_lens, window=None, force_split=None, seed=0,
+                       spike=False):
+    from mini_sglang_b200.config import PartSpec
+    from mini_sglang_b200.parts import BuildEnv, GroupContext, KVCacheView, StepContext, Workspace
+    from mini_sglang_b200.parts.attention import PagedAttention
+
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    B, T = len(q_lens), sum(q_lens)
+    pages_per = [-(-L // P) for L in kv_lens]
+    n_pages = sum(pages_per) + 1
+    perm = (torch.randperm(n_pages - 1, generator=g) + 1).tolist()          # scattered pages, never page 0
+    maxp = max(pages_per)
+    bt = torch.zeros(B, maxp, dtype=torch.int32)
+    kc = torch.full((n_pages, n_kv, P, d), float("nan")).to(dtype)            # unwritten slots are poison
+    vc = torch.full((n_pages, n_kv, P, d), float("nan")).to(dtype)
+    kc[0] = 0
+    vc[0] = 0
+    Ks, Vs = [], []
+    for r, L in enumerate(kv_lens):
+        pg = [perm.pop() for _ in range(pages_per[r])]
+        bt[r, :len(pg)] = torch.tensor(pg, dtype=torch.int32)
+        k = torch.randn(L, n_kv, d, generator=g).to(dtype)
+        v = torch.randn(L, n_kv, d, generator=g).to(dtype)
+        if spike and L > 40:
+            k[3] *= 6.0            # a far key that must dominate if (and only if) it is read
+        for i in range(L):
+            kc[pg[i // P], :, i % P] = k[i]
+            vc[pg[i // P], :, i % P] = v[i]
+        Ks.append(k.float())
+        Vs.append(v.float())
+    q = torch.randn(T, n_q, d, generator=g).to(dtype)
+    if spike:
+        t = 0
+        for r, (ql, L) in enumerate(zip(q_lens, kv_lens)):
+            if L > 40:
+                q[t + ql - 1] = (Ks[r][3].repeat_interleave(n_q // n_kv, 0) * 0.5).to(dtype)
+            t += ql
+    scale = d ** -0.5
+    ref = attention_reference(q.float(), Ks, Vs, q_lens, kv_lens, scale, window)
+
+    env = BuildEnv(dtype=dtype, device=torch.device(DEV))
+    mixer = PagedAttention(PartSpec("paged_attention", {"hidden_size": 32, "num_heads": n_q, "num_kv_heads": n_kv,
+                                                        "head_dim": d, "scale": scale, "window": window}), "x", env)
+    q_start = [0]
+    for n in q_lens:
+        q_start.append(q_start[-1] + n)
+    token_req = [r for r, n in enumerate(q_lens) for _ in range(n)]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    nsplit, max_split = None, 1
+    if force_split:
+        nsplit, max_split = i32([force_split] * B), force_split
+    grp = GroupContext(block_table=bt.to(DEV), out_loc=i32([0] * T), nsplit=nsplit, max_split=max_split, window=window)
+    uniform = all(n == 1 for n in q_lens)
+    ctx = StepContext(T=T, B=B, page_size=P, input_ids=i32([0] * T), positions=i32([0] * T), q_start=i32(q_start),
+                      kv_len=i32(kv_lens), token_req=i32(token_req), slots=i32([0] * B), groups=[grp],
+                      host_q_lens=list(q_lens), host_kv_lens=list(kv_lens), host_slots=[0] * B,
+                      uniform_decode=uniform, workspace=Workspace(torch.device(DEV)))
+    out = torch.full((T, n_q, d), float("nan"), dtype=dtype, device=DEV)
+    mixer.attend(q.to(DEV), out, ctx, KVCacheView(kc.to(DEV), vc.to(DEV), grp, P))
+    torch.cuda.synchronize()
+    return out.float().cpu(), ref
+
+
+ATT_TOL = {torch.float32: dict(rtol=1e-4, atol=2e-5), torch.bfloat16: dict(rtol=2e-2, atol=2e-2)}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,d,P", [(4, 2, 16, 1), (6, 2, 32, 4), (15, 3, 48, 16), (8, 2, 64, 8),
+                                          (32, 8, 128, 16), (4, 4, 128, 16), (40, 2, 64, 16), (2, 1, 256, 32),
+                                          (3, 1, 72, 4), (8, 8, 80, 16)])
+def test_attention_mixed_batch(dtype, n_q, n_kv, d, P):
+    # portions of prompts (with and without earlier context), single decoded tokens, one long context
+    q_lens = [5, 1, 70, 1, 2, 33]
+    kv_lens = [5, 200, 131, 64, 65, 33 + 128]
+    out, ref = run_attention_case(dtype, n_q, n_kv, d, P, q_lens, kv_lens, seed=d)
+    torch.testing.assert_close(out, ref.to(dtype).float(), **ATT_TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("force_split", [None, 2, 5])
+def test_attention_decode_batch_with_splits(dtype, force_split):
+    kv_lens = [1, 63, 64, 65, 700, 1500, 300, 129]
+    out, ref = run_attention_case(dtype, 32, 8, 128, 16, [1] * len(kv_lens), kv_lens, force_split=force_split,
+                                  seed=7, spike=True)
+    torch.testing.assert_close(out, ref.to(dtype).float(), **ATT_TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [1, 7, 64, 100])
+def test_attention_window(dtype, window):
+    q_lens = [1, 40, 3, 1]
+    kv_lens = [300, 140, 65, 5]
+    out, ref = run_attention_case(dtype, 6, 2, 32, 4, q_lens, kv_lens, window=window, force_split=3, seed=9)
+    torch.testing.assert_close(out, ref.to(dtype).float(), **ATT_TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_far_key_and_page_edges(dtype):
+    # one score stands out: the last query of every long request is aligned with key 3, hundreds of
+    # keys back, in another page and another key tile; a kernel that skips or mis-addresses far keys
+    # cannot pass within tolerance
+    q_lens = [17, 1, 16, 1]
+    kv_lens = [17 + 480, 1023, 16 + 16 * 7, 1025]
+    out, ref = run_attention_case(dtype, 8, 2, 64, 16, q_lens, kv_lens, seed=11, spike=True)
+    torch.testing.assert_close(out, ref.to(dtype).float(), **ATT_TOL[dtype])
