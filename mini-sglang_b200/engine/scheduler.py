@@ -144,6 +144,8 @@ class Scheduler:
     # -- requests --------------------------------------------------------------------------
     def add_request(self, req: Req) -> None:
         limit = self.mgr.max_context_len
+        if req.params.eos_token_id == -1 and not req.eos_ids:
+            req.eos_ids = set(self.eos_ids)          # the model's own end tokens
         if req.n_prompt >= limit:
             req.finish_reason = FinishReason("abort", f"prompt of {req.n_prompt} tokens does not fit the context of {limit}")
             return
@@ -342,19 +344,21 @@ class Scheduler:
                 need = extend + (r.params.max_new_tokens - r.n_output) * ratio
                 if node is not None:
                     self.tree.lock(node)             # the matched pages are no longer evictable
-                if need > self._free_tokens() - used:
+                fits = need <= self._free_tokens() - used
+                if not fits and not self.running and not plan and extend + 1 <= self._free_tokens():
+                    fits = True          # alone: the estimate of its future length must not keep it out
+                if not fits:
                     if node is not None:
                         self.tree.unlock(node)
-                    if not self.running and not plan:
+                    total_tokens = self.mgr.groups[0].pool.num_pages * self.P
+                    if not self.running and not plan and len(r.tokens) + 1 > total_tokens:
                         # alone and still too large for the whole pool: it can never run
-                        total_tokens = self.mgr.groups[0].pool.num_pages * self.P
-                        if len(r.tokens) + 1 > total_tokens:
-                            self.waiting.remove(r)
-                            r.to_abort = f"request of {len(r.tokens)} tokens does not fit the cache of {total_tokens} tokens"
-                            r.check_finished()
-                            outputs.append(StepOutput(r, None, True))
-                            self.stats["aborted"] += 1
-                            continue
+                        self.waiting.remove(r)
+                        r.to_abort = f"request of {len(r.tokens)} tokens does not fit the cache of {total_tokens} tokens"
+                        r.check_finished()
+                        outputs.append(StepOutput(r, None, True))
+                        self.stats["aborted"] += 1
+                        continue
                     break
                 slot = self.mgr.open()
                 r.slot, r.node = slot, node

@@ -1,0 +1,335 @@
+"""Cache manager, prefix tree and scheduler on the CPU: no page lost, held twice or freed twice
+under random orders of requests; what the scheduler decides when pages run out."""
+
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from mini_sglang_b200.cache import CacheManager, OutOfPages, OutOfSlots, PagedKVNeed, PagePool, PrefixTree, StateNeed
+from mini_sglang_b200.engine.scheduler import Req, Scheduler
+from mini_sglang_b200.engine.step import StepEntry
+from mini_sglang_b200.sampling import SamplingParams
+
+
+# ---------------------------------------------------------------------------------------
+def test_pool_fifo_and_double_free():
+    pool = PagePool(5)
+    a = pool.alloc(3)
+    assert a == [1, 2, 3] and pool.available == 2
+    pool.free([2])
+    assert pool.alloc(3) == [4, 5, 2]              # first in, first out; page 0 never appears
+    with pytest.raises(OutOfPages):
+        pool.alloc(1)
+    pool.free([1])
+    with pytest.raises(ValueError, match="freed twice"):
+        pool.free([1])
+    with pytest.raises(ValueError):
+        pool.free([0])
+
+
+def all_held_pages(mgr, gi):
+    g = mgr.groups[gi]
+    out = []
+    for slot in range(1, mgr.max_reqs + 1):
+        if mgr.is_open(slot):
+            out += [int(p) for p in g.table[slot, int(g.first_live[slot]):int(g.n_pages[slot])]]
+    return out
+
+
+@pytest.mark.parametrize("page_size", [1, 4, 16])
+def test_manager_random_orders_no_page_lost_or_held_twice(page_size):
+    rnd = random.Random(page_size)
+    needs = {0: PagedKVNeed(2, 16), 1: PagedKVNeed(2, 16), 2: PagedKVNeed(1, 32, window=24), 3: StateNeed((4,))}
+    mgr = CacheManager(needs, page_size=page_size, num_pages=400 // page_size, max_reqs=6, max_context_len=300,
+                       max_step_tokens=40)
+    assert len(mgr.groups) == 2 and mgr.groups[0].cache_ids == [0, 1] and mgr.groups[1].window == 24
+    live = {}
+    for it in range(3000):
+        op = rnd.random()
+        if op < 0.25 and mgr.free_slots:
+            live[mgr.open()] = 0
+        elif op < 0.85 and live:
+            slot = rnd.choice(list(live))
+            n = rnd.choice([1, 1, 1, 2, 7, 33])
+            if live[slot] + n > 300:
+                continue
+            try:
+                mgr.reserve(slot, n)
+            except OutOfPages:
+                continue
+            loc = mgr.slot_mapping(0, slot, live[slot], n)
+            assert (loc >= page_size).all()                         # never the dump page
+            mgr.commit(slot, n)
+            live[slot] += n
+        elif live:
+            slot = rnd.choice(list(live))
+            mgr.close(slot)
+            del live[slot]
+        for gi, g in enumerate(mgr.groups):
+            held = all_held_pages(mgr, gi)
+            assert len(held) == len(set(held)), "a page is held twice"
+            assert 0 not in held
+            assert len(held) + g.pool.available == g.pool.num_pages, "a page was lost"
+            for slot, n_tok in live.items():
+                # every token still inside the window has a live page
+                lo = 0 if g.window is None else max(0, n_tok - g.window + 1)
+                if n_tok:
+                    pages = g.table[slot, lo // page_size: -(-n_tok // page_size)]
+                    assert (pages > 0).all()
+    for slot in list(live):
+        mgr.close(slot)
+    mgr.check_idle()
+    with pytest.raises(ValueError, match="closed twice"):
+        mgr.close(1)
+
+
+def test_window_pages_are_given_back_as_the_window_passes():
+    mgr = CacheManager({0: PagedKVNeed(1, 16, window=8)}, page_size=4, num_pages=6, max_reqs=2, max_context_len=1000,
+                       max_step_tokens=4)
+    s = mgr.open()
+    total = mgr.groups[0].pool.num_pages
+    for i in range(200):                      # far more tokens than the pool holds
+        mgr.reserve(s, 1)
+        mgr.commit(s, 1)
+        assert mgr.groups[0].pool.in_use <= 4
+    g = mgr.groups[0]
+    assert g.first_live[s] == (200 - 8 + 1) // 4
+    assert (g.table[s, :g.first_live[s]] == 0).all()
+    mgr.close(s)
+    assert g.pool.available == total
+
+
+def test_slots_run_out_and_state_rows_are_zeroed():
+    mgr = CacheManager({0: StateNeed((3,))}, page_size=4, num_pages=4, max_reqs=2, max_context_len=64)
+    zeroed = []
+    mgr.on_open.append(zeroed.append)
+    a, b = mgr.open(), mgr.open()
+    assert {a, b} == {1, 2} and zeroed == [a, b]
+    with pytest.raises(OutOfSlots):
+        mgr.open()
+    mgr.close(a)
+    assert mgr.open() == a
+
+
+def test_reserve_is_all_or_nothing():
+    mgr = CacheManager({0: PagedKVNeed(1, 16), 1: PagedKVNeed(1, 16, window=4)}, page_size=4, num_pages=5,
+                       max_reqs=2, max_context_len=64, max_step_tokens=4)
+    s = mgr.open()
+    mgr.reserve(s, 16)
+    before = [g.pool.available for g in mgr.groups]
+    with pytest.raises(OutOfPages):
+        mgr.reserve(s, 8)
+    assert [g.pool.available for g in mgr.groups] == before and mgr.reserved[s] == 16
+
+
+# ---------------------------------------------------------------------------------------
+def test_prefix_tree_match_insert_lock_evict():
+    P = 4
+    tree = PrefixTree(P)
+    toks = list(range(100, 119))                         # 19 tokens: 4 full pages
+    table, dup, node = tree.insert(toks, [11, 12, 13, 14], owned_from=0)
+    assert table == [11, 12, 13, 14] and dup == [] and tree.evictable_pages == 4
+    pages, n2 = tree.match(toks[:-1])
+    assert pages == [11, 12, 13, 14] and n2 is node
+    pages, _ = tree.match(toks[:7])
+    assert pages == [11]
+    other = toks[:8] + [7, 7, 7, 7, 9]
+    table, dup, node_b = tree.insert(other, [11, 12, 21], owned_from=2)
+    assert table == [11, 12, 21] and dup == []
+    # a request that computed the same content on pages of its own gets the tree's pages back
+    table, dup, _ = tree.insert(toks, [31, 32, 33, 34], owned_from=0)
+    assert table == [11, 12, 13, 14] and dup == [31, 32, 33, 34]
+    tree.lock(node)
+    assert tree.protected_pages == 4 and tree.evictable_pages == 1
+    assert tree.evict(10) == [21]                        # only the unpinned leaf goes
+    tree.unlock(node)
+    assert tree.protected_pages == 0
+    freed = tree.evict(10)
+    assert sorted(freed) == [11, 12, 13, 14] and freed[0] == 14   # leaves first, parents follow
+    assert tree.num_nodes == 0
+
+
+def test_prefix_tree_lru_order():
+    tree = PrefixTree(1)
+    tree.insert([1, 2], [5, 6], 0)
+    tree.insert([1, 3], [5, 7], 1)
+    tree.match([1, 2])                                   # touch branch [1, 2]
+    assert tree.evict(1) == [7]
+
+
+# ---------------------------------------------------------------------------------------
+class FakeRunner:
+    """Keeps the real cache manager busy; the 'logits' at a wanted place depend only on the
+    request's tokens up to that place, so any schedule must generate the same tokens."""
+
+    V = 64
+
+    def __init__(self, mgr):
+        self.mgr = mgr
+        self.history = {}
+        self.steps = []
+
+    def step(self, entries):
+        rows = []
+        self.steps.append([(e.slot, len(e.tokens)) for e in entries])
+        short = [0] * len(self.mgr.groups)
+        for e in entries:
+            for gi, n in enumerate(self.mgr.pages_needed(e.slot, len(e.tokens))):
+                short[gi] += n
+        for gi, g in enumerate(self.mgr.groups):
+            assert short[gi] <= g.pool.available, "the scheduler planned a step that does not fit"
+        for e in entries:
+            start = int(self.mgr.length[e.slot])
+            # tokens before `start` may sit in pages taken over from the prefix cache: the request knows them
+            req = next(r for r in self.sched.running if r.slot == e.slot)
+            hist = list(req.tokens[:start]) + list(e.tokens)
+            assert list(req.tokens[start:start + len(e.tokens)]) == list(e.tokens)
+            self.mgr.reserve(e.slot, len(e.tokens))
+            for w in e.want:
+                row = torch.zeros(self.V)
+                row[hash(tuple(hist[:start + w + 1])) % (self.V - 1) + 1] = 1.0     # never token 0 (eos)
+                rows.append(row)
+            self.mgr.commit(e.slot, len(e.tokens))
+        return torch.stack(rows) if rows else torch.zeros(0, self.V)
+
+
+class ArgmaxSampler:
+    def sample(self, logits, temperatures, row_keys, steps):
+        return logits.argmax(-1)
+
+
+def run_all(page_size, num_pages, prompts, max_new, *, chunk=8192, budget=16384, policy="lpm", max_reqs=8,
+            prefix_cache=True, conservativeness=1.0):
+    mgr = CacheManager({0: PagedKVNeed(2, 16)}, page_size=page_size, num_pages=num_pages, max_reqs=max_reqs,
+                       max_context_len=4096, max_step_tokens=budget)
+    runner = FakeRunner(mgr)
+    sch = Scheduler(runner, ArgmaxSampler(), max_num_reqs=max_reqs, max_step_tokens=budget, chunk_size=chunk,
+                    policy=policy, enable_prefix_cache=prefix_cache, eos_ids=[0], conservativeness=conservativeness,
+                    retract_decode_steps=4)
+    runner.sched = sch
+    reqs = [Req(f"r{i}", p, SamplingParams(max_new_tokens=m, ignore_eos=True)) for i, (p, m) in enumerate(zip(prompts, max_new))]
+    for r in reqs:
+        sch.add_request(r)
+    guard = 0
+    while not sch.idle:
+        sch.step()
+        guard += 1
+        assert guard < 20000, "scheduler does not make progress"
+    sch.check_idle_invariants()
+    return reqs, sch, runner
+
+
+def prompts_for(seed, n, lo, hi, shared=0):
+    rnd = random.Random(seed)
+    common = [rnd.randrange(1, 60) for _ in range(shared)]
+    return [(common if (shared and i % 2 == 0) else []) + [rnd.randrange(1, 60) for _ in range(rnd.randrange(lo, hi))]
+            for i in range(n)]
+
+
+def test_scheduler_outputs_do_not_depend_on_the_schedule():
+    prompts = prompts_for(1, 12, 5, 90, shared=40)
+    max_new = [3 + (i * 7) % 20 for i in range(12)]
+    base, sch0, _ = run_all(4, 4000, prompts, max_new, policy="fcfs", prefix_cache=False)
+    want = [r.output for r in base]
+    assert all(len(o) == m for o, m in zip(want, max_new))
+    assert sch0.stats["retractions"] == 0
+    for kw in [dict(page_size=1, num_pages=400), dict(page_size=16, num_pages=30, chunk=16, budget=48),
+               dict(page_size=4, num_pages=70, chunk=7, budget=20, policy="lpm"),
+               dict(page_size=4, num_pages=45, policy="random", max_reqs=3),
+               dict(page_size=4, num_pages=60, policy="lof", prefix_cache=False)]:
+        page_size, num_pages = kw.pop("page_size"), kw.pop("num_pages")
+        reqs, sch, runner = run_all(page_size, num_pages, prompts, max_new, **kw)
+        assert [r.output for r in reqs] == want, kw
+        assert all(r.finish_reason.type == "length" for r in reqs)
+        budget = kw.get("budget", 16384)
+        assert all(sum(n for _, n in st) <= budget for st in runner.steps)
+        assert all(n <= kw.get("chunk", 8192) for st in runner.steps for _, n in st)
+
+
+def test_scheduler_mixes_decode_tokens_with_prompt_portions():
+    prompts = [[3] * 10, [4] * 50]
+    reqs, sch, runner = run_all(4, 100, prompts, [30, 5], chunk=16, budget=24, policy="fcfs", prefix_cache=False)
+    mixed = [st for st in runner.steps if any(n == 1 for _, n in st) and any(n > 1 for _, n in st)]
+    assert mixed, "no step held a decoded token beside a prompt portion"
+    assert [n for _, n in runner.steps[0]] == [10, 14]          # budget 24: whole first prompt, portion of the second
+
+
+def test_prefix_cache_reuse_and_accounting():
+    shared = list(range(1, 41))
+    prompts = [shared + [50 + i] * 6 for i in range(6)]
+    reqs, sch, runner = run_all(4, 200, prompts, [4] * 6, policy="lpm")
+    # the first request fills the cache; the others wait for it and then reuse 40 tokens each
+    assert reqs[0].cached_tokens == 0
+    assert [r.cached_tokens for r in reqs[1:]] == [40] * 5
+    assert sch.stats["cached_tokens"] == 200
+    assert sch.tree.protected_pages == 0 and sch.tree.num_nodes == sch.mgr.groups[0].pool.in_use
+    assert sch.flush_cache() and sch.mgr.groups[0].pool.in_use == 0
+
+
+def test_pages_run_out_retract_and_finish_everything():
+    prompts = prompts_for(3, 6, 20, 30)
+    max_new = [40] * 6
+    want = [r.output for r in run_all(4, 4000, prompts, max_new, policy="fcfs", prefix_cache=False)[0]]
+    # 6 requests want about 6 * 65 tokens; the pool holds 160: optimistic admission must retract
+    reqs, sch, runner = run_all(4, 40, prompts, max_new, policy="fcfs", prefix_cache=False, conservativeness=0.3)
+    assert sch.stats["retractions"] > 0
+    assert [r.output for r in reqs] == want
+    assert any(r.retractions for r in reqs)
+    assert sch.new_token_ratio > sch.min_ratio
+
+
+def test_request_that_can_never_fit_is_aborted_not_hung():
+    reqs, sch, _ = run_all(4, 8, [[5] * 100, [6] * 10], [4, 4], policy="fcfs", prefix_cache=False)
+    assert reqs[0].finish_reason.type == "abort" and "does not fit" in reqs[0].finish_reason.detail
+    assert reqs[1].finish_reason.type == "length" and len(reqs[1].output) == 4
+    # a lone request that outgrows the pool while decoding is finished with abort as well
+    reqs, sch, _ = run_all(4, 8, [[5] * 20], [100], policy="fcfs", prefix_cache=False)
+    assert reqs[0].finish_reason.type == "abort" and 0 < len(reqs[0].output) < 100
+
+
+def test_finish_reasons_and_abort():
+    mgr = CacheManager({0: PagedKVNeed(2, 16)}, page_size=4, num_pages=100, max_reqs=4, max_context_len=64)
+    runner = FakeRunner(mgr)
+    sch = Scheduler(runner, ArgmaxSampler(), policy="fcfs", eos_ids=[9])
+    runner.sched = sch
+    r_len = Req("a", [1, 2, 3], SamplingParams(max_new_tokens=2))
+    r_ctx = Req("b", [1] * 60, SamplingParams(max_new_tokens=50, ignore_eos=True))
+    r_abort = Req("c", [4, 5], SamplingParams(max_new_tokens=50))
+    r_long = Req("d", [1] * 64, SamplingParams())
+    for r in (r_len, r_ctx, r_abort, r_long):
+        sch.add_request(r)
+    assert r_long.finish_reason.type == "abort"                 # prompt fills the whole context
+    sch.step()
+    sch.abort("c")
+    while not sch.idle:
+        sch.step()
+    assert r_len.finish_reason.type == "length" and len(r_len.output) == 2
+    assert r_ctx.finish_reason.type == "length" and len(r_ctx.output) == 5   # 60 + 5 - 1 = 64 tokens in the cache
+    assert r_abort.finish_reason.type == "abort"
+    sch.check_idle_invariants()
+    # eos: make the fake model emit the eos id
+    class Eos(ArgmaxSampler):
+        def sample(self, logits, *a):
+            return torch.full((logits.shape[0],), 9)
+    sch = Scheduler(runner, Eos(), policy="fcfs", eos_ids=[9])
+    runner.sched = sch
+    r_eos = Req("e", [1, 2], SamplingParams(max_new_tokens=10))
+    r_ign = Req("f", [1, 2], SamplingParams(max_new_tokens=3, ignore_eos=True))
+    sch.add_request(r_eos)
+    sch.add_request(r_ign)
+    while not sch.idle:
+        sch.step()
+    assert r_eos.finish_reason.type == "stop" and r_eos.output == [9]
+    assert r_ign.finish_reason.type == "length" and r_ign.output == [9, 9, 9]
+
+
+def test_policies_order():
+    mgr = CacheManager({0: PagedKVNeed(2, 16)}, page_size=4, num_pages=1000, max_reqs=16, max_context_len=512)
+    sch = Scheduler(FakeRunner(mgr), ArgmaxSampler(), policy="lof")
+    for i, m in enumerate([5, 50, 20]):
+        sch.add_request(Req(f"r{i}", [1 + i] * 8, SamplingParams(max_new_tokens=m)))
+    assert [r.rid for r, _, _ in sch._ordered_waiting()] == ["r1", "r2", "r0"]
+    with pytest.raises(ValueError, match="dfs-weight"):
+        Scheduler(FakeRunner(mgr), ArgmaxSampler(), policy="dfs-weight")
