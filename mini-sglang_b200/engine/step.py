@@ -109,6 +109,7 @@ class _Graph:
         self.layout = None
         self.logits = None
         self.max_split = None
+        self.n_kernels = 0     # this engine's kernels inside the captured graph
 
 
 class ModelRunner:
@@ -386,6 +387,7 @@ class ModelRunner:
         gr.dev.copy_(host[:lay.size], non_blocking=True)
         self._mark(idx)
         gr.graph.replay()
+        ops.LAUNCHES += gr.n_kernels
         return gr.logits[:B]
 
     def _capture(self, b: int, mp: Tuple[int, ...]) -> _Graph:
@@ -411,6 +413,8 @@ class ModelRunner:
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
         gr.graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES
         with torch.cuda.graph(gr.graph, pool=self._graph_pool):
             gr.logits = self.model.forward(ctx, caches, rows)
+        gr.n_kernels = ops.LAUNCHES - before
         return gr

@@ -27,7 +27,12 @@ class KernelError(RuntimeError):
     pass
 
 
+LAUNCHES = 0      # kernels of this engine launched (or recorded into a graph) so far
+
+
 def _check(code: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if code != 0:
         detail = ""
         if code == 3:
