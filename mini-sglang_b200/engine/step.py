@@ -155,7 +155,7 @@ class ModelRunner:
         self._pinned_ev = [None, None]
         self._flip = 0
         self._dev_staging = None
-        self.use_cuda_graph = use_cuda_graph
+        self.use_cuda_graph = use_cuda_graph and all(getattr(l.mixer, "graph_safe", False) for l in self.model.layers)
         self.max_capture_bs = max_capture_bs
         self._graphs: Dict[Tuple[int, Tuple[int, ...]], _Graph] = {}
         self._graph_pool = None

@@ -26,6 +26,8 @@ class PagedAttention(Mixer):
             window (None = all keys; W = the last W keys).
     """
 
+    graph_safe = True
+
     def __init__(self, spec, prefix, env, position=None):
         super().__init__(spec, prefix, env)
         s = spec

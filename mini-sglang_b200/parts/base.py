@@ -48,6 +48,11 @@ class Part:
 
 
 class Mixer(Part):
+    # True if forward() only launches work whose shapes and addresses are fixed by (T, B) and reads
+    # everything else (lengths, slots, tables) from the context's device tensors, so that a decode
+    # step can be captured once and replayed.  Mixers that loop over requests on the host say False.
+    graph_safe = False
+
     def cache_need(self):
         return None
 

@@ -1,0 +1,136 @@
+"""Generation through the Python entry point and the command line."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen3 as P
+from helpers import PAGE, model_dir, plain_logits, weights
+from tiny_models import CONFIGS, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def make_engine(name, dtype, **kw):
+    from mini_sglang_b200 import Engine, EngineArgs
+    args = dict(model=model_dir(name), dtype=dtype, page_size=PAGE[name], num_pages=256, max_num_reqs=8, random_seed=0,
+                log_level="WARNING")
+    args.update(kw)
+    return Engine(EngineArgs(**args))
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_float32_equals_plain(name):
+    cfg = CONFIGS[name]
+    eng = make_engine(name, "float32")
+    prompts = [random_tokens(n, cfg["vocab_size"], 900 + n) for n in (5, 9, 13)]
+    outs = eng.generate(input_ids=prompts, sampling_params={"temperature": 0.0, "max_new_tokens": 8, "ignore_eos": True})
+    for p, o in zip(prompts, outs):
+        want = P.greedy_generate(cfg, weights(name), p, 8, device="cuda")
+        assert o["token_ids"] == want
+        assert o["meta_info"]["finish_reason"] == {"type": "length", "length": 8}
+        assert o["meta_info"]["prompt_tokens"] == len(p) and o["meta_info"]["completion_tokens"] == 8
+    eng.scheduler.check_idle_invariants()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_bfloat16_follows_plain_logits(name):
+    """bfloat16 may break a near-tie differently; every chosen token must be (near-)best under the
+    plain implementation given the same history."""
+    cfg = CONFIGS[name]
+    eng = make_engine(name, "bfloat16")
+    p = random_tokens(11, cfg["vocab_size"], 950)
+    out = eng.generate(input_ids=p, sampling_params={"max_new_tokens": 12, "ignore_eos": True})
+    toks = out["token_ids"]
+    ref = plain_logits(name, p + toks)
+    for i, t in enumerate(toks):
+        row = ref[len(p) - 1 + i]
+        assert row[t] >= row.max() - 0.05, (i, t, row[t].item(), row.max().item())
+
+
+def test_chunked_prefill_budget_and_small_pool_same_tokens():
+    name, cfg = "B", CONFIGS["B"]
+    prompts = [random_tokens(n, cfg["vocab_size"], 1000 + n) for n in (7, 16, 23, 31, 40, 12)]
+    sp = {"temperature": 0.0, "max_new_tokens": 10, "ignore_eos": True}
+    base = make_engine(name, "float32", disable_radix_cache=True, schedule_policy="fcfs").generate(input_ids=prompts, sampling_params=sp)
+    tight = make_engine(name, "float32", num_pages=24, chunk_size=8, max_prefill_tokens=20, schedule_conservativeness=0.3)
+    outs = tight.generate(input_ids=prompts, sampling_params=sp)
+    assert [o["token_ids"] for o in outs] == [o["token_ids"] for o in base]
+    tight.scheduler.check_idle_invariants()
+    assert tight.scheduler.stats["retractions"] > 0 or tight.scheduler.stats["evicted_pages"] > 0
+
+
+def test_prefix_reuse_gives_same_tokens_and_counts_cached():
+    name, cfg = "B", CONFIGS["B"]
+    shared = random_tokens(24, cfg["vocab_size"], 1100)
+    prompts = [shared + random_tokens(5, cfg["vocab_size"], 1101 + i) for i in range(4)]
+    sp = {"max_new_tokens": 6, "ignore_eos": True}
+    eng = make_engine(name, "float32")
+    outs = eng.generate(input_ids=prompts, sampling_params=sp)
+    assert [o["meta_info"]["cached_tokens"] for o in outs] == [0, 24, 24, 24]
+    for p, o in zip(prompts, outs):
+        assert o["token_ids"] == P.greedy_generate(cfg, weights(name), p, 6, device="cuda")
+    # and again, now everything but the last page comes from the cache
+    again = eng.generate(input_ids=prompts[0], sampling_params=sp)
+    assert again["token_ids"] == outs[0]["token_ids"] and again["meta_info"]["cached_tokens"] == 28
+    assert eng.flush_cache()
+    eng.scheduler.check_idle_invariants()
+
+
+def test_temperature_sampling_is_seeded_and_batch_independent():
+    name, cfg = "B", CONFIGS["B"]
+    prompts = [random_tokens(n, cfg["vocab_size"], 1200 + n) for n in (7, 16, 23, 31)]
+    sps = [{"temperature": 0.7, "max_new_tokens": 6, "ignore_eos": True, "seed": 1 + i} for i in range(4)]
+    a = make_engine(name, "float32", random_seed=1).generate(input_ids=prompts, sampling_params=sps)
+    b = make_engine(name, "float32", random_seed=1, chunk_size=8, max_prefill_tokens=16).generate(input_ids=prompts, sampling_params=sps)
+    assert [o["token_ids"] for o in a] == [o["token_ids"] for o in b]
+    alone = make_engine(name, "float32", random_seed=1).generate(input_ids=prompts[2], sampling_params=sps[2])
+    assert alone["token_ids"] == a[2]["token_ids"]
+    other = make_engine(name, "float32", random_seed=2).generate(input_ids=prompts, sampling_params=sps)
+    assert [o["token_ids"] for o in other] != [o["token_ids"] for o in a]
+    greedy = make_engine(name, "float32").generate(input_ids=prompts[0], sampling_params={"max_new_tokens": 6, "ignore_eos": True})
+    assert greedy["token_ids"] == P.greedy_generate(cfg, weights(name), prompts[0], 6, device="cuda")
+
+
+def test_stream_and_eos_stop():
+    name, cfg = "A", CONFIGS["A"]
+    eng = make_engine(name, "float32")
+    p = random_tokens(9, cfg["vocab_size"], 1300)
+    want = P.greedy_generate(cfg, weights(name), p, 5, device="cuda")
+    chunks = list(eng.generate(input_ids=p, sampling_params={"max_new_tokens": 5, "ignore_eos": True}, stream=True))
+    assert [len(c["token_ids"]) for c in chunks] == [1, 2, 3, 4, 5] and chunks[-1]["token_ids"] == want
+    out = eng.generate(input_ids=p, sampling_params={"max_new_tokens": 5, "eos_token_id": want[2]})
+    assert out["token_ids"] == want[:3] and out["meta_info"]["finish_reason"] == {"type": "stop", "matched": want[2]}
+
+
+def test_command_line():
+    name, cfg = "A", CONFIGS["A"]
+    p = random_tokens(6, cfg["vocab_size"], 1400)
+    proc = subprocess.run([sys.executable, "-m", "mini_sglang_b200.engine.cli", "--model", model_dir(name), "--dtype", "float32",
+                           "--page_size", "1", "--num_pages", "64", "--max_num_reqs", "4", "--log_level", "ERROR",
+                           "--input_ids", ",".join(map(str, p)), "--max_new_tokens", "4", "--ignore_eos"],
+                          capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    out = json.loads(proc.stdout.strip().split("\n")[-1])
+    assert out["token_ids"] == P.greedy_generate(cfg, weights(name), p, 4, device="cuda")
+
+
+def test_dummy_load_runs_without_a_checkpoint(tmp_path):
+    from mini_sglang_b200 import Engine, EngineArgs
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(CONFIGS["C"], f)
+    eng = Engine(EngineArgs(model=str(tmp_path), dummy_load=True, random_seed=3, page_size=16, num_pages=16,
+                            max_num_reqs=2, log_level="ERROR"))
+    out = eng.generate(input_ids=[1, 2, 3], sampling_params={"max_new_tokens": 3, "ignore_eos": True})
+    assert len(out["token_ids"]) == 3
+
+
+def test_missing_extension_or_cpu_tensor_fails_loudly():
+    from mini_sglang_b200 import ops
+    with pytest.raises(ops.KernelError, match="CUDA device only"):
+        ops.swiglu(torch.zeros(2, 8))

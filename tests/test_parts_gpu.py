@@ -1,0 +1,314 @@
+"""Each part of the model alone against the plain functions, and the part interfaces at work: a
+toy architecture, defined here, with a mixer that keeps state of its own, a layer run twice and a
+run that reads another run's cache, registered, built and stepped without touching the engine."""
+
+import pytest
+import torch
+
+import plain_qwen3 as P
+from helpers import TOL
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def env(dtype):
+    from mini_sglang_b200.parts import BuildEnv
+    return BuildEnv(dtype=dtype, device=torch.device(DEV))
+
+
+class DictSource:
+    def __init__(self, tensors, dtype):
+        self.t, self.dtype = tensors, dtype
+
+    def fetch(self, name):
+        t = self.t[name]
+        return t.to(DEV, self.dtype if t.dim() > 1 or self.dtype == torch.float32 else t.dtype)
+
+    def has(self, name):
+        return name in self.t
+
+    def close(self):
+        pass
+
+
+def rand_for(part, seed, dtype):
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, decl in part.tensors().items():
+        t = torch.randn(decl.shape, generator=g)
+        t = 1 + 0.1 * t if decl.init == "norm" else 0.05 * t
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from mini_sglang_b200.config import PartSpec
+    from mini_sglang_b200.parts import NORMS
+    n = NORMS["rmsnorm"](PartSpec("rmsnorm", {"size": 120, "eps": 3e-6}), "blk.norm", env(dtype))
+    assert list(n.tensors()) == ["blk.norm.weight"]
+    w = rand_for(n, 0, dtype)
+    n.load(DictSource(w, dtype))
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(9, 120, generator=g).to(dtype)
+    res = torch.randn(9, 120, generator=g)
+    y = n.forward(x=x.to(DEV), residual=res.to(DEV))
+    ref = P.rms_norm(res + x.float(), w["blk.norm.weight"].float(), 3e-6)
+    torch.testing.assert_close(y.float().cpu(), ref.to(dtype).float(), **TOL["float32" if dtype == torch.float32 else "bfloat16"])
+
+
+def test_rope_part_table():
+    from mini_sglang_b200.config import PartSpec
+    from mini_sglang_b200.parts import POSITION_ENCODINGS
+    r = POSITION_ENCODINGS["rope_neox"](PartSpec("rope_neox", {"head_dim": 48, "rotary_dim": 48, "theta": 50000.0,
+                                                               "max_positions": 777}), "", env(torch.float32))
+    tab = r.rotary_table().cpu()
+    assert tab.shape == (777, 48) and tab.dtype == torch.float32
+    cos, sin = P.rope_angles(torch.arange(777), 48, 50000.0, torch.float32)
+    torch.testing.assert_close(tab[:, :24], cos, rtol=0, atol=2e-6)
+    torch.testing.assert_close(tab[:, 24:], sin, rtol=0, atol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from mini_sglang_b200.config import PartSpec
+    from mini_sglang_b200.parts import FEED_FORWARDS
+    f = FEED_FORWARDS["swiglu_mlp"](PartSpec("swiglu_mlp", {"hidden_size": 72, "intermediate_size": 200}), "l.mlp", env(dtype))
+    w = rand_for(f, 2, dtype)
+    f.load(DictSource(w, dtype))
+    x = torch.randn(11, 72, generator=torch.Generator().manual_seed(3)).to(dtype)
+    y = f.forward(x.to(DEV), None)
+    ref = P.mlp_block(x.float(), {k: v.float() for k, v in w.items()}, "l.mlp.")
+    torch.testing.assert_close(y.float().cpu(), ref, **TOL["float32" if dtype == torch.float32 else "bfloat16"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_head_parts(dtype):
+    from mini_sglang_b200.config import PartSpec
+    from mini_sglang_b200.parts import EMBEDDINGS, HEADS
+    e = EMBEDDINGS["token_embedding"](PartSpec("token_embedding", {"vocab_size": 333, "hidden_size": 40, "name": "emb.w"}), "", env(dtype))
+    w = rand_for(e, 4, dtype)
+    e.load(DictSource(w, dtype))
+    ids = torch.tensor([0, 332, 7, 7], dtype=torch.int32)
+    torch.testing.assert_close(e.forward(ids.to(DEV)).cpu(), w["emb.w"].float()[ids.long()], rtol=0, atol=0)
+    for tied in (True, False):
+        h = HEADS["lm_head"](PartSpec("lm_head", {"vocab_size": 333, "hidden_size": 40, "tied": tied, "name": "head.w",
+                                                  "tied_to": "emb.w"}), "", env(dtype))
+        hw = rand_for(h, 5, dtype)
+        h.load(DictSource(hw, dtype), embedding=e)
+        x = torch.randn(3, 40, generator=torch.Generator().manual_seed(6)).to(dtype)
+        out = h.forward(x.to(DEV))
+        assert out.dtype == torch.float32
+        W = w["emb.w"] if tied else hw["head.w"]
+        torch.testing.assert_close(out.cpu(), x.float() @ W.float().T, **TOL["float32" if dtype == torch.float32 else "bfloat16"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 5])
+def test_attention_mixer_part_alone(dtype, window):
+    """The mixer with its own projections, norms, rotation and cache write, fed in two portions."""
+    from mini_sglang_b200.config import PartSpec
+    from mini_sglang_b200.parts import (MIXERS, POSITION_ENCODINGS, GroupContext, KVCacheView, StepContext, Workspace)
+    H, nq, nkv, d, Pg = 40, 6, 3, 16, 4
+    rope = POSITION_ENCODINGS["rope_neox"](PartSpec("rope_neox", {"head_dim": d, "theta": 1e4, "max_positions": 64}), "", env(dtype))
+    m = MIXERS["paged_attention"](PartSpec("paged_attention", {
+        "hidden_size": H, "num_heads": nq, "num_kv_heads": nkv, "head_dim": d, "scale": d ** -0.5, "qkv_bias": True,
+        "qk_norm": True, "qk_norm_eps": 1e-5, "window": window}), "l.self_attn", env(dtype), position=rope)
+    w = rand_for(m, 7, dtype)
+    m.load(DictSource(w, dtype))
+    need = m.cache_need()
+    assert (need.n_kv_heads, need.head_dim, need.window) == (nkv, d, window)
+    S = 13
+    x = torch.randn(S, H, generator=torch.Generator().manual_seed(8)).to(dtype)
+    kc = torch.zeros(8, nkv, Pg, d, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    table = torch.tensor([[3, 1, 5, 2]], dtype=torch.int32, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    outs = []
+    for s0, s1 in ((0, 6), (6, 13)):
+        n = s1 - s0
+        pos = list(range(s0, s1))
+        loc = [int(table[0, p // Pg]) * Pg + p % Pg for p in pos]
+        grp = GroupContext(block_table=table, out_loc=i32(loc), nsplit=None, max_split=1, window=window)
+        ctx = StepContext(T=n, B=1, page_size=Pg, input_ids=i32([0] * n), positions=i32(pos), q_start=i32([0, n]),
+                          kv_len=i32([s1]), token_req=i32([0] * n), slots=i32([1]), groups=[grp], host_q_lens=[n],
+                          host_kv_lens=[s1], host_slots=[1], workspace=Workspace(torch.device(DEV)))
+        outs.append(m.forward(x[s0:s1].to(DEV), ctx, KVCacheView(kc, vc, grp, Pg)))
+    got = torch.cat(outs).float().cpu()
+    # plain: the same block on the whole sequence
+    cfg = {"num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": d, "hidden_size": H, "rms_norm_eps": 1e-5,
+           "attention_bias": True, "rope_theta": 1e4}
+    wf = {k: v.float() for k, v in w.items()}
+    if window is None:
+        ref = P.attention_block(x.float(), wf, "l.self_attn.", cfg, torch.arange(S))
+    else:
+        p = "l.self_attn."
+        q = (x.float() @ wf[p + "q_proj.weight"].T + wf[p + "q_proj.bias"]).reshape(S, nq, d)
+        k = (x.float() @ wf[p + "k_proj.weight"].T + wf[p + "k_proj.bias"]).reshape(S, nkv, d)
+        v = (x.float() @ wf[p + "v_proj.weight"].T + wf[p + "v_proj.bias"]).reshape(S, nkv, d)
+        q, k = P.rms_norm(q, wf[p + "q_norm.weight"], 1e-5), P.rms_norm(k, wf[p + "k_norm.weight"], 1e-5)
+        cos, sin = P.rope_angles(torch.arange(S), d, 1e4, torch.float32)
+        o = P.causal_gqa_attention(P.rope_neox(q, cos, sin), P.rope_neox(k, cos, sin), v, d ** -0.5, window=window)
+        ref = o.reshape(S, nq * d) @ wf[p + "o_proj.weight"].T
+    torch.testing.assert_close(got, ref, **TOL["float32" if dtype == torch.float32 else "bfloat16"])
+
+
+# ---------------------------------------------------------------------------------------
+# a toy architecture with a stateful mixer, defined entirely in this test
+# ---------------------------------------------------------------------------------------
+def _register_toy():
+    from mini_sglang_b200.cache import StateNeed
+    from mini_sglang_b200.config import ARCHITECTURES, LayerSpec, ModelSpec, PartSpec, Run, register_architecture
+    from mini_sglang_b200.parts import MIXERS, Mixer, register_mixer
+    from mini_sglang_b200.weights import TensorDecl
+
+    if "running_mean" not in MIXERS:
+        @register_mixer("running_mean")
+        class RunningMean(Mixer):
+            """y_t = W * mean(x_0..x_t): keeps the running sum of its inputs per request as state."""
+
+            def __init__(self, spec, prefix, env, position=None):
+                super().__init__(spec, prefix, env)
+                self.H = spec["hidden_size"]
+                self.w = None
+
+            def tensors(self):
+                return {self.name("mix.weight"): TensorDecl((self.H, self.H))}
+
+            def load(self, src):
+                self.w = src.fetch(self.name("mix.weight"))
+
+            def cache_need(self):
+                return StateNeed((self.H,), "float32")
+
+            def forward(self, x, ctx, cache, writes_cache=True):
+                out = torch.empty_like(x)
+                t = 0
+                for r, n in enumerate(ctx.host_q_lens):
+                    slot, n_prev = ctx.host_slots[r], ctx.host_kv_lens[r] - n
+                    cs = torch.cumsum(x[t:t + n].float(), 0) + cache.state[slot]
+                    cnt = torch.arange(n_prev + 1, n_prev + n + 1, device=x.device, dtype=torch.float32)
+                    out[t:t + n] = ((cs / cnt[:, None]) @ self.w.float().T).to(x.dtype)
+                    if writes_cache:
+                        cache.state[slot] = cs[-1]
+                    t += n
+                return out
+
+    class ToyConfig:
+        def __init__(self, raw):
+            self.raw = raw
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw)
+
+    def build(cfg):
+        r = cfg.raw
+        H, V = r["width"], r["vocab"]
+        norm = PartSpec("rmsnorm", {"size": H, "eps": r["eps"]})
+        ffn = PartSpec("swiglu_mlp", {"hidden_size": H, "intermediate_size": r["ffn"]})
+        rope = PartSpec("rope_neox", {"head_dim": 16, "theta": 1e4, "max_positions": 256})
+        toy = LayerSpec("toy.layers.0", PartSpec("running_mean", {"hidden_size": H}), ffn,
+                        {"input": norm, "post_mixer": norm}, position=None)
+        att = LayerSpec("toy.layers.1", PartSpec("paged_attention", {
+            "hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "qk_norm": False}), ffn,
+            {"input": norm, "post_mixer": norm}, position=rope)
+        # layer 0 runs twice (each run with state of its own), and the last run of the attention
+        # layer reads the keys and values its first run wrote
+        schedule = [Run(0, cache=0), Run(1, cache=1), Run(0, cache=2), Run(1, cache=1, writes_cache=False)]
+        return ModelSpec("ToyStateLM", H, V, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "name": "toy.embed.weight"}),
+                         PartSpec("rmsnorm", {"size": H, "eps": r["eps"], "name": "toy.norm.weight"}),
+                         PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": True, "name": "toy.head.weight",
+                                              "tied_to": "toy.embed.weight"}),
+                         [toy, att], schedule, max_context_len=256)
+
+    register_architecture("ToyStateLM", ToyConfig, build)
+    return build, ToyConfig
+
+
+def toy_plain(w, tokens, eps):
+    """Whole sequence, float32, no cache: the toy model's formulas restated."""
+    f = {k: v.float() for k, v in w.items()}
+    S = len(tokens)
+    res = f["toy.embed.weight"][torch.tensor(tokens)]
+    cnt = torch.arange(1, S + 1, dtype=torch.float32)[:, None]
+
+    def toy_layer(res):
+        y = P.rms_norm(res, f["toy.layers.0.input_layernorm.weight"], eps)
+        res = res + (torch.cumsum(y, 0) / cnt) @ f["toy.layers.0.self_attn.mix.weight"].T
+        y = P.rms_norm(res, f["toy.layers.0.post_attention_layernorm.weight"], eps)
+        return res + P.mlp_block(y, f, "toy.layers.0.mlp.")
+
+    def qkv(y):
+        p = "toy.layers.1.self_attn."
+        q = (y @ f[p + "q_proj.weight"].T).reshape(S, 4, 16)
+        k = (y @ f[p + "k_proj.weight"].T).reshape(S, 2, 16)
+        v = (y @ f[p + "v_proj.weight"].T).reshape(S, 2, 16)
+        cos, sin = P.rope_angles(torch.arange(S), 16, 1e4, torch.float32)
+        return P.rope_neox(q, cos, sin), P.rope_neox(k, cos, sin), v
+
+    def att_layer(res, kv=None):
+        y = P.rms_norm(res, f["toy.layers.1.input_layernorm.weight"], eps)
+        q, k, v = qkv(y)
+        if kv is not None:
+            k, v = kv
+        o = P.causal_gqa_attention(q, k, v, 16 ** -0.5).reshape(S, 64) @ f["toy.layers.1.self_attn.o_proj.weight"].T
+        res = res + o
+        y = P.rms_norm(res, f["toy.layers.1.post_attention_layernorm.weight"], eps)
+        return res + P.mlp_block(y, f, "toy.layers.1.mlp."), (k, v)
+
+    res = toy_layer(res)
+    res, kv = att_layer(res)
+    res = toy_layer(res)
+    res, _ = att_layer(res, kv)
+    return P.rms_norm(res, f["toy.norm.weight"], eps) @ f["toy.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_state_is_registered_built_and_stepped(dtype):
+    from mini_sglang_b200.cache import PagedKVNeed, StateNeed
+    from mini_sglang_b200.config import ARCHITECTURES
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    from mini_sglang_b200.weights import RandomSource
+
+    build, Cfg = _register_toy()
+    try:
+        spec = build(Cfg({"width": 40, "vocab": 97, "ffn": 56, "eps": 1e-5}))
+        spec.validate()
+        holder = {}
+
+        def factory(expected, dt, dev):
+            src = RandomSource(expected, 11, dt, dev, std=0.08)
+            holder["w"] = {n: src.draw(n).cpu() for n in expected if src.has(n)}
+            return src
+
+        runner = ModelRunner(spec, factory, dtype=dtype, page_size=4, num_pages=32, max_reqs=3, max_step_tokens=64)
+        needs = runner.mgr.needs
+        assert isinstance(needs[0], StateNeed) and isinstance(needs[1], PagedKVNeed) and isinstance(needs[2], StateNeed)
+        assert not runner.use_cuda_graph                      # the toy mixer loops on the host
+        g = torch.Generator().manual_seed(5)
+        a = torch.randint(0, 97, (29,), generator=g).tolist()
+        b = torch.randint(0, 97, (17,), generator=g).tolist()
+        sa, sb = runner.open(), runner.open()
+        got = {}
+        # portions of a beside portions and single tokens of b
+        plan = [((0, 7), (0, 5)), ((7, 9), (5, 6)), ((9, 20), (6, 7)), ((20, 29), (7, 17))]
+        for (a0, a1), (b0, b1) in plan:
+            out = runner.step([StepEntry(sa, a[a0:a1], list(range(a1 - a0))), StepEntry(sb, b[b0:b1], list(range(b1 - b0)))])
+            out = out.float().cpu()
+            for i in range(a1 - a0):
+                got[("a", a0 + i)] = out[i]
+            for i in range(b1 - b0):
+                got[("b", b0 + i)] = out[a1 - a0 + i]
+        runner.close(sa)
+        # the slot is taken again: its state rows must start from zero
+        sc = runner.open()
+        assert sc == sa
+        out = runner.step([StepEntry(sc, b, list(range(len(b))))]).float().cpu()
+        ref_a, ref_b = toy_plain(holder["w"], a, 1e-5), toy_plain(holder["w"], b, 1e-5)
+        for (rid, pos), row in got.items():
+            torch.testing.assert_close(row, (ref_a if rid == "a" else ref_b)[pos], **TOL[dtype])
+        torch.testing.assert_close(out, ref_b, **TOL[dtype])
+    finally:
+        ARCHITECTURES.pop("ToyStateLM", None)
