@@ -27,10 +27,11 @@ class RotaryNeox(PositionEncoding):
 
     def rotary_table(self) -> torch.Tensor:
         if self._table is None:
-            dev = self.env.device
-            idx = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32, device=dev)
+            # built on the host in float32, operation by operation as the reference does, so the
+            # table does not depend on the device's pow/sin/cos roundings; then moved to the device
+            idx = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32)
             inv_freq = 1.0 / (self.theta ** (idx / self.rotary_dim))
-            t = torch.arange(self.max_positions, dtype=torch.float32, device=dev)
+            t = torch.arange(self.max_positions, dtype=torch.float32)
             freqs = t[:, None] * inv_freq[None, :]
-            self._table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous()
+            self._table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(self.env.device)
         return self._table

@@ -32,10 +32,8 @@ def weights(name: str):
 
 
 def plain_logits(name: str, tokens: Sequence[int]) -> torch.Tensor:
-    dev = "cuda" if torch.cuda.is_available() else "cpu"
-    with torch.no_grad():
-        torch.backends.cuda.matmul.allow_tf32 = False
-        return plain_qwen3.forward_sequence(CONFIGS[name], weights(name), list(tokens), device=dev).cpu()
+    with torch.no_grad():                      # on the CPU: IEEE float32, no device-specific roundings
+        return plain_qwen3.forward_sequence(CONFIGS[name], weights(name), list(tokens), device="cpu")
 
 
 def make_runner(name: str, dtype: str, num_pages: int, max_reqs: int = 4, page_size: int = None, graphs: bool = True):

@@ -31,7 +31,7 @@ def test_greedy_generation_float32_equals_plain(name):
     prompts = [random_tokens(n, cfg["vocab_size"], 900 + n) for n in (5, 9, 13)]
     outs = eng.generate(input_ids=prompts, sampling_params={"temperature": 0.0, "max_new_tokens": 8, "ignore_eos": True})
     for p, o in zip(prompts, outs):
-        want = P.greedy_generate(cfg, weights(name), p, 8, device="cuda")
+        want = P.greedy_generate(cfg, weights(name), p, 8, device="cpu")
         assert o["token_ids"] == want
         assert o["meta_info"]["finish_reason"] == {"type": "length", "length": 8}
         assert o["meta_info"]["prompt_tokens"] == len(p) and o["meta_info"]["completion_tokens"] == 8
@@ -67,17 +67,17 @@ def test_chunked_prefill_budget_and_small_pool_same_tokens():
 
 def test_prefix_reuse_gives_same_tokens_and_counts_cached():
     name, cfg = "B", CONFIGS["B"]
-    shared = random_tokens(24, cfg["vocab_size"], 1100)
+    shared = random_tokens(40, cfg["vocab_size"], 1100)        # longer than the 32 tokens that make a request wait
     prompts = [shared + random_tokens(5, cfg["vocab_size"], 1101 + i) for i in range(4)]
     sp = {"max_new_tokens": 6, "ignore_eos": True}
     eng = make_engine(name, "float32")
     outs = eng.generate(input_ids=prompts, sampling_params=sp)
-    assert [o["meta_info"]["cached_tokens"] for o in outs] == [0, 24, 24, 24]
+    assert [o["meta_info"]["cached_tokens"] for o in outs] == [0, 40, 40, 40]
     for p, o in zip(prompts, outs):
-        assert o["token_ids"] == P.greedy_generate(cfg, weights(name), p, 6, device="cuda")
+        assert o["token_ids"] == P.greedy_generate(cfg, weights(name), p, 6, device="cpu")
     # and again, now everything but the last page comes from the cache
     again = eng.generate(input_ids=prompts[0], sampling_params=sp)
-    assert again["token_ids"] == outs[0]["token_ids"] and again["meta_info"]["cached_tokens"] == 28
+    assert again["token_ids"] == outs[0]["token_ids"] and again["meta_info"]["cached_tokens"] == 44
     assert eng.flush_cache()
     eng.scheduler.check_idle_invariants()
 
@@ -94,18 +94,19 @@ def test_temperature_sampling_is_seeded_and_batch_independent():
     other = make_engine(name, "float32", random_seed=2).generate(input_ids=prompts, sampling_params=sps)
     assert [o["token_ids"] for o in other] != [o["token_ids"] for o in a]
     greedy = make_engine(name, "float32").generate(input_ids=prompts[0], sampling_params={"max_new_tokens": 6, "ignore_eos": True})
-    assert greedy["token_ids"] == P.greedy_generate(cfg, weights(name), prompts[0], 6, device="cuda")
+    assert greedy["token_ids"] == P.greedy_generate(cfg, weights(name), prompts[0], 6, device="cpu")
 
 
 def test_stream_and_eos_stop():
     name, cfg = "A", CONFIGS["A"]
     eng = make_engine(name, "float32")
     p = random_tokens(9, cfg["vocab_size"], 1300)
-    want = P.greedy_generate(cfg, weights(name), p, 5, device="cuda")
+    want = P.greedy_generate(cfg, weights(name), p, 5, device="cpu")
     chunks = list(eng.generate(input_ids=p, sampling_params={"max_new_tokens": 5, "ignore_eos": True}, stream=True))
     assert [len(c["token_ids"]) for c in chunks] == [1, 2, 3, 4, 5] and chunks[-1]["token_ids"] == want
-    out = eng.generate(input_ids=p, sampling_params={"max_new_tokens": 5, "eos_token_id": want[2]})
-    assert out["token_ids"] == want[:3] and out["meta_info"]["finish_reason"] == {"type": "stop", "matched": want[2]}
+    k = max(i for i in range(5) if want[i] not in want[:i])          # generation stops at the first occurrence
+    out = eng.generate(input_ids=p, sampling_params={"max_new_tokens": 5, "eos_token_id": want[k]})
+    assert out["token_ids"] == want[:k + 1] and out["meta_info"]["finish_reason"] == {"type": "stop", "matched": want[k]}
 
 
 def test_command_line():
@@ -117,7 +118,7 @@ def test_command_line():
                           capture_output=True, text=True, cwd=ROOT, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     out = json.loads(proc.stdout.strip().split("\n")[-1])
-    assert out["token_ids"] == P.greedy_generate(cfg, weights(name), p, 4, device="cuda")
+    assert out["token_ids"] == P.greedy_generate(cfg, weights(name), p, 4, device="cpu")
 
 
 def test_dummy_load_runs_without_a_checkpoint(tmp_path):

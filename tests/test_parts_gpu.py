@@ -303,6 +303,7 @@ def test_toy_architecture_with_state_is_registered_built_and_stepped(dtype):
                 got[("b", b0 + i)] = out[a1 - a0 + i]
         runner.close(sa)
         # the slot is taken again: its state rows must start from zero
+        runner.open()                                              # slots are handed out first-in first-out
         sc = runner.open()
         assert sc == sa
         out = runner.step([StepEntry(sc, b, list(range(len(b))))]).float().cpu()
