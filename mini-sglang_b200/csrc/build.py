@@ -60,9 +60,14 @@ def build_dir() -> str:
     raise KernelBuildError("no writable folder for built kernels; set MSGL_BUILD_DIR")
 
 
+# files a source pulls in with #include: an edit of any of them rebuilds the library
+INCLUDED = {"attention_noalloc.cu": ["attention.cu", "attention_noalloc.h"]}
+
+
 def _digest(sources: Sequence[str], flags: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for s in list(sources) + ["common.cuh"]:
+    deps = [d for s in sources for d in INCLUDED.get(s, [])]
+    for s in list(sources) + deps + ["common.cuh"]:
         with open(os.path.join(HERE, s), "rb") as f:
             h.update(f.read())
     h.update(" ".join(flags).encode())
@@ -143,9 +148,16 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     return load_library(f"attention_d{hd}", ATTENTION_SOURCES, {"MSGL_HEAD_DIM": hd})
 
 
+def attention_noalloc_library(head_dim: int) -> ctypes.CDLL:
+    """The library of csrc/attention_noalloc.h (decode attention with built-in scratch memory)."""
+    hd = head_dim if head_dim in MMA_HEAD_DIMS else 128
+    return load_library(f"attention_noalloc_d{hd}", ["attention_noalloc.cu"], {"MSGL_HEAD_DIM": hd})
+
+
 def build_all(head_dims: Sequence[int] = (16, 32, 48, 64, 128)) -> List[str]:
     """Compile every library ahead of time (used by the repository's build check)."""
     paths = [compile_library("common", COMMON_SOURCES)]
     for hd in head_dims:
         paths.append(compile_library(f"attention_d{hd}", ATTENTION_SOURCES, {"MSGL_HEAD_DIM": hd}))
+    paths.append(compile_library("attention_noalloc_d128", ["attention_noalloc.cu"], {"MSGL_HEAD_DIM": 128}))
     return paths
