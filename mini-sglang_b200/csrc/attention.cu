@@ -29,6 +29,12 @@
 #ifndef MSGL_HEAD_DIM
 #define MSGL_HEAD_DIM 128
 #endif
+#ifndef MSGL_DEC_WARPS
+#define MSGL_DEC_WARPS 4          // warps of the decode kernel
+#endif
+#ifndef MSGL_DEC_STAGES
+#define MSGL_DEC_STAGES 3         // cp.async stages per warp of the decode kernel
+#endif
 
 struct AttnParams {
     const void* q;            // [T, n_q, d]
@@ -408,6 +414,535 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
 }
 
 // ---------------------------------------------------------------------------------------
+// bfloat16 decode kernel: 16 rows per block (the heads of one group, one or a few tokens), the
+// block's keys dealt out to NW warps in units of 16.  Every warp streams its own units through a
+// private ring of ST shared-memory stages with cp.async and never waits for another warp until
+// the merge at the end, so loads stay in flight while other warps compute.
+// ---------------------------------------------------------------------------------------
+constexpr int DEC_WT = 16;        // keys per warp unit
+
+template <int D, int NW, int ST>
+__global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnParams p) {
+    constexpr int R = 16;
+    constexpr int LDS = D + 8;
+    constexpr int NDB = D / 8;
+    constexpr int CH = D / 8;                       // 16-byte chunks per row
+    constexpr int THREADS = NW * 32;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);              // [16][LDS]
+    __nv_bfloat16* ring = Qs + R * LDS;                                          // [NW][ST][K|V][16][LDS]
+    __shared__ int sh_tile[4];
+
+    const int G = p.n_q / p.n_kv;
+    const int Gc = G <= R ? G : R;
+    const int n_chunks = G <= R ? 1 : (G + R - 1) / R;
+    const int QT = G <= R ? R / G : 1;
+    const int kvh = blockIdx.y / n_chunks;
+    const int chunk = blockIdx.y - kvh * n_chunks;
+
+    TileInfo ti;
+    if (!find_tile(p, QT, ti, sh_tile)) return;
+    const int ns = p.nsplit ? min(max(p.nsplit[ti.req], 1), p.max_split) : 1;
+    const int split = blockIdx.z;
+    if (split >= ns) return;
+
+    int p_min, p_max, kt_begin, kt_end;
+    key_tile_range(p, ti, MMA_KT, split, ns, p_min, p_max, kt_begin, kt_end);
+    const int u_begin = kt_begin * (MMA_KT / DEC_WT);
+    const int u_end = min(kt_end * (MMA_KT / DEC_WT), p_max / DEC_WT + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(p.q);
+    const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(p.k_cache);
+    const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(p.v_cache);
+    const int* bt = p.block_table + (size_t)ti.req * p.bt_stride;
+
+    for (int idx = tid; idx < R * CH; idx += THREADS) {
+        const int r = idx / CH, c = idx - r * CH;
+        const int tl = r / Gc, hl = r - tl * Gc;
+        const int hg = chunk * R + hl;
+        const bool valid = tl < ti.n_tok && hg < G && tl < QT;
+        const size_t tok = (size_t)(ti.q_base + ti.t0 + (valid ? tl : 0));
+        const __nv_bfloat16* src = qg + (tok * p.n_q + (size_t)kvh * G + (valid ? hg : 0)) * D + c * 8;
+        cp_async16(Qs + r * LDS + c * 8, valid ? (const void*)src : (const void*)qg, valid);
+    }
+    cp_async_commit();
+
+    // this warp's units: u_begin + warp, + NW, ...
+    const int n_my = (u_end - u_begin > warp) ? (u_end - u_begin - warp + NW - 1) / NW : 0;
+    __nv_bfloat16* my_ring = ring + (size_t)warp * ST * 2 * DEC_WT * LDS;
+    const int l_key = lane >> 1, l_half = lane & 1;
+
+    // Page of this lane's key in unit i of this warp, or -1 past the last key.  The lookup is a
+    // dependent global load, so it is issued one iteration before the copy that needs it.
+    auto unit_page = [&](int i) -> int {
+        const int key = (u_begin + warp + i * NW) * DEC_WT + l_key;
+        return (i < n_my && key <= p_max) ? bt[key / p.page_size] : -1;
+    };
+    auto load_unit = [&](int i, int pg) {      // unit i of this warp into stage i % ST
+        __nv_bfloat16* Ks = my_ring + (size_t)(i % ST) * 2 * DEC_WT * LDS;
+        __nv_bfloat16* Vs = Ks + DEC_WT * LDS;
+        const int key = (u_begin + warp + i * NW) * DEC_WT + l_key;
+        const bool valid = pg >= 0;
+        size_t off = 0;
+        if (valid) off = (((size_t)pg * p.n_kv + kvh) * p.page_size + key % p.page_size) * D;
+#pragma unroll
+        for (int j = 0; j < CH / 2; ++j) {
+            const int c = l_half * (CH / 2) + j;
+            cp_async16(Ks + l_key * LDS + c * 8, kc + off + c * 8, valid);
+            cp_async16(Vs + l_key * LDS + c * 8, vc + off + c * 8, valid);
+        }
+    };
+
+    int pg_first[ST - 1];
+#pragma unroll
+    for (int i = 0; i < ST - 1; ++i) pg_first[i] = unit_page(i);
+    int pg_next = unit_page(ST - 1);
+#pragma unroll
+    for (int i = 0; i < ST - 1; ++i) {
+        if (i < n_my) load_unit(i, pg_first[i]);
+        cp_async_commit();
+    }
+    // Q has landed once all but the newest ST-1 groups are complete
+    cp_async_wait<ST - 1>();
+    __syncthreads();
+
+    unsigned qf[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+        ldmatrix_x4(qf[kk], Qs + (lane & 15) * LDS + kk * 16 + (lane >> 4) * 8);
+
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    const int pos_lo = p_min + r_lo / Gc, pos_hi = p_min + r_hi / Gc;
+    const float sc = p.scale * 1.4426950408889634f;
+
+    float o[NDB][4];
+#pragma unroll
+    for (int i = 0; i < NDB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+    for (int i = 0; i < n_my; ++i) {
+        if (i + ST - 1 < n_my) load_unit(i + ST - 1, pg_next);
+        cp_async_commit();
+        pg_next = unit_page(i + ST);
+        cp_async_wait<ST - 1>();
+        __syncwarp();
+        const __nv_bfloat16* Ks = my_ring + (size_t)(i % ST) * 2 * DEC_WT * LDS;
+        const __nv_bfloat16* Vs = Ks + DEC_WT * LDS;
+        const int key0 = (u_begin + warp + i * NW) * DEC_WT;
+
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
+        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            unsigned b[4];
+            ldmatrix_x4(b, Ks + ((lane & 7) + ((lane >> 4) & 1) * 8) * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16_16816(s[0], qf[kk], b[0], b[1]);
+            mma_bf16_16816(s[1], qf[kk], b[2], b[3]);
+        }
+        const bool need_mask = (key0 + DEC_WT - 1 > p_min) || (p.window > 0 && key0 <= p_max - p.window);
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = s[nb][e] * sc;
+                if (need_mask) {
+                    const int key = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+                    const int pos = (e < 2) ? pos_lo : pos_hi;
+                    bool ok = key <= pos;
+                    if (p.window > 0) ok = ok && (key > pos - p.window);
+                    if (!ok) v = -INFINITY;
+                }
+                s[nb][e] = v;
+                if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+            }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float mu_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, mu_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
+        const float al_lo = exp2f(m_lo - mu_lo), al_hi = exp2f(m_hi - mu_hi);
+        m_lo = mn_lo; m_hi = mn_hi;
+        l_lo *= al_lo; l_hi *= al_hi;
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+            s[nb][0] = exp2f(s[nb][0] - mu_lo); s[nb][1] = exp2f(s[nb][1] - mu_lo);
+            s[nb][2] = exp2f(s[nb][2] - mu_hi); s[nb][3] = exp2f(s[nb][3] - mu_hi);
+            l_lo += s[nb][0] + s[nb][1];
+            l_hi += s[nb][2] + s[nb][3];
+        }
+        if (al_lo != 1.f || al_hi != 1.f) {
+#pragma unroll
+            for (int j = 0; j < NDB; ++j) { o[j][0] *= al_lo; o[j][1] *= al_lo; o[j][2] *= al_hi; o[j][3] *= al_hi; }
+        }
+        unsigned a[4];
+        a[0] = pack_bf16(s[0][0], s[0][1]);
+        a[1] = pack_bf16(s[0][2], s[0][3]);
+        a[2] = pack_bf16(s[1][0], s[1][1]);
+        a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int nd2 = 0; nd2 < D / 16; ++nd2) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, Vs + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDS + nd2 * 16 + ((lane >> 4) & 1) * 8);
+            mma_bf16_16816(o[2 * nd2], a, b[0], b[1]);
+            mma_bf16_16816(o[2 * nd2 + 1], a, b[2], b[3]);
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+    // merge the warps (same rows, disjoint keys) through shared memory, in warp order
+    float* Om = reinterpret_cast<float*>(ring);             // [NW][16][D]
+    float* Mm = Om + NW * 16 * D;                           // [NW][16]
+    float* Lm = Mm + NW * 16;                               // [NW][16]
+    __syncthreads();
+#pragma unroll
+    for (int nd = 0; nd < NDB; ++nd) {
+        const int col = nd * 8 + (lane & 3) * 2;
+        float* d0 = Om + ((size_t)warp * 16 + (lane >> 2)) * D + col;
+        float* d1 = d0 + 8 * D;
+        *reinterpret_cast<float2*>(d0) = make_float2(o[nd][0], o[nd][1]);
+        *reinterpret_cast<float2*>(d1) = make_float2(o[nd][2], o[nd][3]);
+    }
+    if ((lane & 3) == 0) {
+        Mm[warp * 16 + (lane >> 2)] = m_lo; Mm[warp * 16 + (lane >> 2) + 8] = m_hi;
+        Lm[warp * 16 + (lane >> 2)] = l_lo; Lm[warp * 16 + (lane >> 2) + 8] = l_hi;
+    }
+    __syncthreads();
+    __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(p.out);
+    const int n_rows = min(ti.n_tok, QT) * Gc;              // valid rows come first
+    for (int idx = tid; idx < n_rows * D; idx += THREADS) {
+        const int r = idx / D, col = idx - r * D;
+        const int tl = r / Gc, hl = r - tl * Gc, hg = chunk * R + hl;
+        if (hg >= G) continue;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, Mm[w * 16 + r]);
+        const float Mu = (M == -INFINITY) ? 0.f : M;
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float f = exp2f(Mm[w * 16 + r] - Mu);
+            acc += f * Om[((size_t)w * 16 + r) * D + col];
+            L += f * Lm[w * 16 + r];
+        }
+        const size_t tok = (size_t)(ti.q_base + ti.t0 + tl);
+        const int head = kvh * G + hg;
+        if (ns == 1) {
+            og[(tok * p.n_q + head) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            const size_t prow = ((size_t)split * p.T + tok) * p.n_q + head;
+            p.part_o[prow * D + col] = acc;
+            if (col == 0) { p.part_ml[prow * 2] = M; p.part_ml[prow * 2 + 1] = L; }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// bfloat16 decode kernel, transposed: the 16 keys of a unit ride the M dimension of the mma and
+// the (token, head) pairs of the block ride N (8 per n-block), so
+//     S^T[key][col] = K[key][:] . Q[col][:]          O^T[dim][col] += V^T[dim][key] P^T[key][col]
+//  * K goes from global memory straight into the A-operand registers (16-byte loads; the k index
+//    inside each 32-element group is permuted the same way for K and Q, which leaves the dot
+//    products unchanged), Q sits in B-operand registers for the whole block: neither touches
+//    shared memory;
+//  * V streams through a per-warp cp.async ring and is read with ldmatrix.trans as A operand;
+//  * P^T gets from accumulator to B-operand layout with movmatrix;
+//  * every warp walks its own units (block's units dealt round-robin) without block barriers;
+//    warps are merged in warp order at the end.
+// Compared with putting the heads on M this halves the tensor work and the accumulator
+// registers (few heads per kv head waste N = 8, not M = 16), so 16 warps fit an SM.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned v) {
+    unsigned r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ void mma_bf16_regs(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                              unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 ldg16_stream(const void* ptr) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+    return v;
+}
+
+template <int D, int NW, int ST, int NBH>
+__global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_decode_t_kernel(const AttnParams p) {
+    constexpr int LDS = D + 8;
+    constexpr int C = 8 * NBH;                      // (token, head) columns per block
+    constexpr int KP = D / 32;                      // 32-element groups of the head size
+    constexpr int MT = D / 16;                      // 16-row tiles of O^T
+    constexpr int CH = D / 8;
+    constexpr int THREADS = NW * 32;
+    static_assert(D % 32 == 0, "the transposed decode kernel needs head sizes in steps of 32");
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [NW][ST][16][LDS]  (V only)
+    __shared__ int sh_tile[4];
+
+    const int G = p.n_q / p.n_kv;
+    const int Gc = G <= C ? G : C;
+    const int n_chunks = G <= C ? 1 : (G + C - 1) / C;
+    const int QT = G <= C ? C / G : 1;
+    const int kvh = blockIdx.y / n_chunks;
+    const int chunk = blockIdx.y - kvh * n_chunks;
+
+    TileInfo ti;
+    if (!find_tile(p, QT, ti, sh_tile)) return;
+    const int ns = p.nsplit ? min(max(p.nsplit[ti.req], 1), p.max_split) : 1;
+    const int split = blockIdx.z;
+    if (split >= ns) return;
+
+    int p_min, p_max, kt_begin, kt_end;
+    key_tile_range(p, ti, MMA_KT, split, ns, p_min, p_max, kt_begin, kt_end);
+    const int u_begin = kt_begin * (MMA_KT / DEC_WT);
+    const int u_end = min(kt_end * (MMA_KT / DEC_WT), p_max / DEC_WT + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(p.q);
+    const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(p.k_cache);
+    const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(p.v_cache);
+    const int* bt = p.block_table + (size_t)ti.req * p.bt_stride;
+
+    // Q as B operand: lane (g, t) holds Q[column nb*8 + g][32 j + 8 t .. + 7]
+    uint4 qf[NBH][KP];
+#pragma unroll
+    for (int nb = 0; nb < NBH; ++nb) {
+        const int c = nb * 8 + g;
+        const int tl = c / Gc, hl = c - tl * Gc, hg = chunk * C + hl;
+        const bool valid = tl < ti.n_tok && tl < QT && hg < G;
+        const __nv_bfloat16* src = qg + ((size_t)(ti.q_base + ti.t0 + (valid ? tl : 0)) * p.n_q + (size_t)kvh * G + (valid ? hg : 0)) * D + 8 * t;
+#pragma unroll
+        for (int j = 0; j < KP; ++j)
+            qf[nb][j] = valid ? *reinterpret_cast<const uint4*>(src + 32 * j) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    // the columns this lane sees in the accumulators: nb*8 + 2t and + 1
+    int pos_c[NBH][2];
+#pragma unroll
+    for (int nb = 0; nb < NBH; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) pos_c[nb][e] = p_min + (nb * 8 + 2 * t + e) / Gc;
+
+    const int n_my = (u_end - u_begin > warp) ? (u_end - u_begin - warp + NW - 1) / NW : 0;
+    __nv_bfloat16* my_ring = ring + (size_t)warp * ST * DEC_WT * LDS;
+    const int v_key = lane >> 1, v_half = lane & 1;
+
+    // page of key (unit i, row lane & 15), or -1 past the last key; one lookup per lane and unit
+    auto unit_page = [&](int i) -> int {
+        const int key = (u_begin + warp + i * NW) * DEC_WT + (lane & 15);
+        return (i < n_my && key <= p_max) ? bt[key / p.page_size] : -1;
+    };
+    auto load_v = [&](int i, int pg_row) {         // V of unit i -> stage i % ST; pg_row: page of row v_key
+        __nv_bfloat16* Vs = my_ring + (size_t)(i % ST) * DEC_WT * LDS;
+        const int key = (u_begin + warp + i * NW) * DEC_WT + v_key;
+        const bool valid = pg_row >= 0;
+        size_t off = 0;
+        if (valid) off = (((size_t)pg_row * p.n_kv + kvh) * p.page_size + key % p.page_size) * D;
+#pragma unroll
+        for (int j = 0; j < CH / 2; ++j) {
+            const int c = 2 * j + v_half;
+            cp_async16(Vs + v_key * LDS + c * 8, vc + off + c * 8, valid);
+        }
+    };
+    uint4 k_lo[KP], k_hi[KP];
+    auto load_k = [&](int i, int pg_lo, int pg_hi) {      // K of unit i -> registers (rows g and g + 8)
+        const int key0 = (u_begin + warp + i * NW) * DEC_WT;
+        const __nv_bfloat16* lo = kc + (((size_t)max(pg_lo, 0) * p.n_kv + kvh) * p.page_size + (key0 + g) % p.page_size) * D + 8 * t;
+        const __nv_bfloat16* hi = kc + (((size_t)max(pg_hi, 0) * p.n_kv + kvh) * p.page_size + (key0 + 8 + g) % p.page_size) * D + 8 * t;
+#pragma unroll
+        for (int j = 0; j < KP; ++j) {
+            k_lo[j] = pg_lo >= 0 ? ldg16_stream(lo + 32 * j) : make_uint4(0u, 0u, 0u, 0u);
+            k_hi[j] = pg_hi >= 0 ? ldg16_stream(hi + 32 * j) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+
+    // prologue: V of the first ST-1 units, K of unit 0, page of the next unit to fetch
+#pragma unroll
+    for (int i = 0; i < ST - 1; ++i) {
+        const int pg = unit_page(i);
+        if (i < n_my) load_v(i, __shfl_sync(0xffffffffu, pg, v_key));
+        cp_async_commit();
+        if (i == 0 && n_my > 0) load_k(0, __shfl_sync(0xffffffffu, pg, g), __shfl_sync(0xffffffffu, pg, g + 8));
+    }
+    int pg_v_next = unit_page(ST - 1);             // for the V copy issued in iteration 0
+    int pg_k_next = unit_page(1);                  // for the K load issued in iteration 0
+
+    float o[NBH][MT][4];
+#pragma unroll
+    for (int nb = 0; nb < NBH; ++nb)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) { o[nb][mt][0] = o[nb][mt][1] = o[nb][mt][2] = o[nb][mt][3] = 0.f; }
+    float m_c[NBH][2], l_c[NBH][2];
+#pragma unroll
+    for (int nb = 0; nb < NBH; ++nb) { m_c[nb][0] = m_c[nb][1] = -INFINITY; l_c[nb][0] = l_c[nb][1] = 0.f; }
+    const float sc = p.scale * 1.4426950408889634f;
+
+    for (int i = 0; i < n_my; ++i) {
+        // ---- S^T = K Q^T from registers
+        float s[NBH][4], s2[NBH][4];
+#pragma unroll
+        for (int nb = 0; nb < NBH; ++nb) {
+            s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+            s2[nb][0] = s2[nb][1] = s2[nb][2] = s2[nb][3] = 0.f;
+#pragma unroll
+            for (int j = 0; j < KP; ++j) {
+                mma_bf16_regs(s[nb], k_lo[j].x, k_hi[j].x, k_lo[j].y, k_hi[j].y, qf[nb][j].x, qf[nb][j].y);
+                mma_bf16_regs(s2[nb], k_lo[j].z, k_hi[j].z, k_lo[j].w, k_hi[j].w, qf[nb][j].z, qf[nb][j].w);
+            }
+        }
+        // ---- next K into the same registers, next V into the ring
+        {
+            const int pk = pg_k_next;
+            if (i + 1 < n_my) load_k(i + 1, __shfl_sync(0xffffffffu, pk, g), __shfl_sync(0xffffffffu, pk, g + 8));
+            const int pv = pg_v_next;
+            if (i + ST - 1 < n_my) load_v(i + ST - 1, __shfl_sync(0xffffffffu, pv, v_key));
+            cp_async_commit();
+            pg_k_next = unit_page(i + 2);
+            pg_v_next = unit_page(i + ST);
+        }
+        // ---- scale, mask, online softmax per column
+        const int key0 = (u_begin + warp + i * NW) * DEC_WT;
+        const bool need_mask = (key0 + DEC_WT - 1 > p_min) || (p.window > 0 && key0 <= p_max - p.window);
+        unsigned pb0[NBH], pb1[NBH];
+        float alpha[NBH][2];
+        bool rescale = false;
+#pragma unroll
+        for (int nb = 0; nb < NBH; ++nb) {
+            float v[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                v[e] = (s[nb][e] + s2[nb][e]) * sc;
+                if (need_mask) {
+                    const int key = key0 + g + ((e & 2) ? 8 : 0);
+                    const int pos = pos_c[nb][e & 1];
+                    bool ok = key <= pos;
+                    if (p.window > 0) ok = ok && (key > pos - p.window);
+                    if (!ok) v[e] = -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float mx = fmaxf(v[e], v[e + 2]);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                const float mn = fmaxf(m_c[nb][e], mx);
+                const float mu = (mn == -INFINITY) ? 0.f : mn;
+                alpha[nb][e] = exp2f(m_c[nb][e] - mu);
+                m_c[nb][e] = mn;
+                v[e] = exp2f(v[e] - mu);
+                v[e + 2] = exp2f(v[e + 2] - mu);
+                l_c[nb][e] = l_c[nb][e] * alpha[nb][e] + v[e] + v[e + 2];
+                rescale = rescale || alpha[nb][e] != 1.f;
+            }
+            // accumulator layout (key g | g+8 ; columns 2t, 2t+1) -> B operand layout (keys 2t, 2t+1 ; column g)
+            pb0[nb] = movmatrix_trans(pack_bf16(v[0], v[1]));
+            pb1[nb] = movmatrix_trans(pack_bf16(v[2], v[3]));
+        }
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+            for (int nb = 0; nb < NBH; ++nb)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    o[nb][mt][0] *= alpha[nb][0]; o[nb][mt][1] *= alpha[nb][1];
+                    o[nb][mt][2] *= alpha[nb][0]; o[nb][mt][3] *= alpha[nb][1];
+                }
+        }
+        // ---- O^T += V^T P^T
+        cp_async_wait<ST - 1>();
+        __syncwarp();
+        const __nv_bfloat16* Vs = my_ring + (size_t)(i % ST) * DEC_WT * LDS;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            unsigned a[4];
+            ldmatrix_x4_trans(a, Vs + ((lane & 7) + ((lane >> 4) & 1) * 8) * LDS + mt * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+            for (int nb = 0; nb < NBH; ++nb) mma_bf16_16816(o[nb][mt], a, pb0[nb], pb1[nb]);
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+
+    // column sums over the 8 lanes that share a column pair
+#pragma unroll
+    for (int nb = 0; nb < NBH; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float l = l_c[nb][e];
+            l += __shfl_xor_sync(0xffffffffu, l, 4);
+            l += __shfl_xor_sync(0xffffffffu, l, 8);
+            l += __shfl_xor_sync(0xffffffffu, l, 16);
+            l_c[nb][e] = l;
+        }
+
+    // merge the warps through shared memory, in warp order
+    float* Om = reinterpret_cast<float*>(ring);             // [NW][C][D]
+    float* Mm = Om + NW * C * D;                            // [NW][C]
+    float* Lm = Mm + NW * C;                                // [NW][C]
+    __syncthreads();
+#pragma unroll
+    for (int nb = 0; nb < NBH; ++nb) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int c = nb * 8 + 2 * t + (e & 1);
+                const int dim = mt * 16 + g + ((e & 2) ? 8 : 0);
+                Om[((size_t)warp * C + c) * D + dim] = o[nb][mt][e];
+            }
+        if (g == 0) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                Mm[warp * C + nb * 8 + 2 * t + e] = m_c[nb][e];
+                Lm[warp * C + nb * 8 + 2 * t + e] = l_c[nb][e];
+            }
+        }
+    }
+    __syncthreads();
+    __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(p.out);
+    const int n_cols = min(min(ti.n_tok, QT) * Gc, C);      // valid columns come first
+    for (int idx = tid; idx < n_cols * D; idx += THREADS) {
+        const int c = idx / D, col = idx - c * D;
+        const int tl = c / Gc, hl = c - tl * Gc, hg = chunk * C + hl;
+        if (hg >= G) continue;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, Mm[w * C + c]);
+        const float Mu = (M == -INFINITY) ? 0.f : M;
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float f = exp2f(Mm[w * C + c] - Mu);
+            acc += f * Om[((size_t)w * C + c) * D + col];
+            L += f * Lm[w * C + c];
+        }
+        const size_t tok = (size_t)(ti.q_base + ti.t0 + tl);
+        const int head = kvh * G + hg;
+        if (ns == 1) {
+            og[(tok * p.n_q + head) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            const size_t prow = ((size_t)split * p.T + tok) * p.n_q + head;
+            p.part_o[prow * D + col] = acc;
+            if (col == 0) { p.part_ml[prow * 2] = M; p.part_ml[prow * 2 + 1] = L; }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // float32-arithmetic kernel for any head size (the true 32-bit path; also takes bfloat16 data)
 // ---------------------------------------------------------------------------------------
 constexpr int SIMT_R = 16;        // rows per block
@@ -544,23 +1079,27 @@ template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int* __restrict__ token_req, const int* __restrict__ nsplit,
                                     T* __restrict__ out, int T_, int n_q, int d, int max_split) {
-    const int tok = blockIdx.x;
+    // one block per (token, head); threads over the head's elements
+    const int tok = blockIdx.x, h = blockIdx.y;
     const int req = token_req ? token_req[tok] : tok;
     const int ns = min(max(nsplit[req], 1), max_split);
     if (ns <= 1) return;
-    for (int idx = threadIdx.x; idx < n_q * d; idx += blockDim.x) {
-        const int h = idx / d, c = idx - h * d;
-        float M = -INFINITY;
-        for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[(((size_t)s * T_ + tok) * n_q + h) * 2]);
-        const float Mu = (M == -INFINITY) ? 0.f : M;
-        float acc = 0.f, L = 0.f;
+    float M = -INFINITY;
+    for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[(((size_t)s * T_ + tok) * n_q + h) * 2]);
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f;
+    for (int s = 0; s < ns; ++s) {
+        const size_t prow = ((size_t)s * T_ + tok) * n_q + h;
+        L += exp2f(part_ml[prow * 2] - Mu) * part_ml[prow * 2 + 1];
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float acc = 0.f;
         for (int s = 0; s < ns; ++s) {
             const size_t prow = ((size_t)s * T_ + tok) * n_q + h;
-            const float f = exp2f(part_ml[prow * 2] - Mu);
-            acc += f * part_o[prow * d + c];
-            L += f * part_ml[prow * 2 + 1];
+            acc += exp2f(part_ml[prow * 2] - Mu) * part_o[prow * d + c];
         }
-        out[((size_t)tok * n_q + h) * d + c] = from_f32<T>(L > 0.f ? acc / L : 0.f);
+        out[((size_t)tok * n_q + h) * d + c] = from_f32<T>(acc * inv);
     }
 }
 
@@ -572,6 +1111,29 @@ MSGL_API int msgl_attention_head_dim() { return MSGL_HEAD_DIM; }
 // rows per block and tokens per query tile of a variant, for the host's grid arithmetic
 // variant: 0 = simt, 1 = mma 64-row, 2 = mma key-split (16-row)
 MSGL_API int msgl_attention_tile_rows(int variant) { return variant == 1 ? 64 : 16; }
+
+// tokens per query tile of the decode variant for a group size (q heads per kv head)
+MSGL_API int msgl_attention_decode_tile_tokens(int G) {
+    if (MSGL_HEAD_DIM % 32 == 0 && G <= 16) return (G <= 8 ? 8 : 16) / G;
+    return G <= 16 ? 16 / G : 1;
+}
+
+// how many blocks of the decode kernel fit one SM, for the host's choice of kv splits
+MSGL_API int msgl_attention_decode_blocks_per_sm(int G) {
+    size_t smem;
+    int reg_limit;
+    if (MSGL_HEAD_DIM % 32 == 0 && G <= 16) {
+        smem = sizeof(__nv_bfloat16) * (size_t)MSGL_DEC_WARPS * MSGL_DEC_STAGES * 16 * (MSGL_HEAD_DIM + 8) + 1024;
+        reg_limit = (G <= 8 && MSGL_HEAD_DIM <= 128) ? 4 : 2;
+    } else {
+        constexpr int ST = (MSGL_HEAD_DIM <= 128) ? MSGL_DEC_STAGES : 2;
+        smem = sizeof(__nv_bfloat16) * ((size_t)16 * (MSGL_HEAD_DIM + 8) + (size_t)MSGL_DEC_WARPS * ST * 2 * 16 * (MSGL_HEAD_DIM + 8)) + 1024;
+        reg_limit = 3;
+    }
+    int n = (int)((227 * 1024) / smem);
+    n = n < reg_limit ? n : reg_limit;
+    return n < 1 ? 1 : n;
+}
 
 static size_t simt_smem_bytes(int d) {
     return sizeof(float) * ((size_t)2 * SIMT_R * d + (size_t)SIMT_KT * (2 * d + 1) + SIMT_R * SIMT_KT + 3 * SIMT_R);
@@ -635,13 +1197,33 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
         }
         attn_mma_kernel<MSGL_HEAD_DIM, false><<<grid, MMA_THREADS, smem, stream>>>(p);
     } else if (variant == 2) {
-        const size_t smem = mma_smem_bytes<MSGL_HEAD_DIM, true>();
-        static bool attr_set = false;
-        if (!attr_set) {
-            cudaFuncSetAttribute(attn_mma_kernel<MSGL_HEAD_DIM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            attr_set = true;
+        constexpr int NW = MSGL_DEC_WARPS;
+        if (MSGL_HEAD_DIM % 32 == 0 && G <= 16) {
+            // transposed kernel: columns = (token, head) pairs, 8 or 16 per block
+            constexpr int DT = (MSGL_HEAD_DIM % 32 == 0) ? MSGL_HEAD_DIM : 32;      // keeps the template legal for other head sizes
+            constexpr int ST = MSGL_DEC_STAGES;
+            const size_t smem = sizeof(__nv_bfloat16) * (size_t)NW * ST * DEC_WT * (DT + 8);
+            const int C = G <= 8 ? 8 : 16;
+            grid.y = n_kv;      // G <= C: one chunk
+            static bool attr_set = false;
+            if (!attr_set) {
+                cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                attr_set = true;
+            }
+            if (C == 8) attn_decode_t_kernel<DT, NW, ST, 1><<<grid, NW * 32, smem, stream>>>(p);
+            else attn_decode_t_kernel<DT, NW, ST, 2><<<grid, NW * 32, smem, stream>>>(p);
+        } else {
+            constexpr int ST = (MSGL_HEAD_DIM <= 128) ? MSGL_DEC_STAGES : 2;   // the ring must fit 227 KB
+            const size_t smem = sizeof(__nv_bfloat16) * ((size_t)16 * (MSGL_HEAD_DIM + 8) +
+                                                         (size_t)NW * ST * 2 * DEC_WT * (MSGL_HEAD_DIM + 8));
+            static bool attr_set = false;
+            if (!attr_set) {
+                cudaFuncSetAttribute(attn_decode_kernel<MSGL_HEAD_DIM, NW, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                attr_set = true;
+            }
+            attn_decode_kernel<MSGL_HEAD_DIM, NW, ST><<<grid, NW * 32, smem, stream>>>(p);
         }
-        attn_mma_kernel<MSGL_HEAD_DIM, true><<<grid, MMA_THREADS, smem, stream>>>(p);
     } else {
         return MSGL_ERR_SIZE;
     }
@@ -652,11 +1234,12 @@ MSGL_API int msgl_attention_combine(const float* part_o, const float* part_ml, c
                                     const int* nsplit, void* out, int T_, int n_q, int d, int max_split, int dtype,
                                     cudaStream_t stream) {
     if (T_ <= 0 || max_split <= 1) return MSGL_OK;
-    const int threads = n_q * d >= 1024 ? 256 : 128;
+    const int threads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
+    const dim3 grid(T_, n_q);
     if (dtype == MSGL_F32)
-        attn_combine_kernel<float><<<T_, threads, 0, stream>>>(part_o, part_ml, token_req, nsplit, (float*)out, T_, n_q, d, max_split);
+        attn_combine_kernel<float><<<grid, threads, 0, stream>>>(part_o, part_ml, token_req, nsplit, (float*)out, T_, n_q, d, max_split);
     else if (dtype == MSGL_BF16)
-        attn_combine_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(part_o, part_ml, token_req, nsplit,
+        attn_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(part_o, part_ml, token_req, nsplit,
                                                                        (__nv_bfloat16*)out, T_, n_q, d, max_split);
     else
         return MSGL_ERR_DTYPE;

@@ -131,13 +131,17 @@ def load_library(name: str, sources: Sequence[str], defines: Optional[Dict[str, 
 
 # the libraries of the engine -----------------------------------------------------------
 
-COMMON_SOURCES = ["elementwise.cu", "sampling.cu"]
+COMMON_SOURCES = ["elementwise.cu", "sampling.cu", "gemm_small_m.cu"]
 ATTENTION_SOURCES = ["attention.cu"]
 MMA_HEAD_DIMS = tuple(range(16, 257, 16))   # head sizes the tensor-core attention kernel is built for
 
 
 def common_library() -> ctypes.CDLL:
-    return load_library("common", COMMON_SOURCES)
+    defines = {}
+    for knob in ("MSGL_GS_WARPS", "MSGL_GS_PF"):                 # tuning knobs of the small-M GEMM
+        if os.environ.get(knob):
+            defines[knob] = int(os.environ[knob])
+    return load_library("common", COMMON_SOURCES, defines or None)
 
 
 def attention_library(head_dim: int) -> ctypes.CDLL:
@@ -145,7 +149,11 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     of MMA_HEAD_DIMS; other head sizes get the library of head size 128, whose float32-arithmetic
     kernel takes any head size up to 512."""
     hd = head_dim if head_dim in MMA_HEAD_DIMS else 128
-    return load_library(f"attention_d{hd}", ATTENTION_SOURCES, {"MSGL_HEAD_DIM": hd})
+    defines = {"MSGL_HEAD_DIM": hd}
+    for knob in ("MSGL_DEC_WARPS", "MSGL_DEC_STAGES"):          # tuning knobs of the decode kernel
+        if os.environ.get(knob):
+            defines[knob] = int(os.environ[knob])
+    return load_library(f"attention_d{hd}", ATTENTION_SOURCES, defines)
 
 
 def attention_noalloc_library(head_dim: int) -> ctypes.CDLL:

@@ -83,11 +83,111 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const float* res_in, flo
     }
 }
 
+// Vectorised variant: 8 elements per thread and pass, the whole row held in registers between the
+// two passes (VPT vectors per thread).  Used when the row length is a multiple of 8 and every
+// pointer is 16-byte aligned; same arithmetic and the same reduction tree per launch shape.
+template <typename T> struct Vec8 {};
+template <> struct Vec8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+template <> struct Vec8<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        uint4 u;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+        *reinterpret_cast<uint4*>(p) = u;
+    }
+};
+
+template <typename T, int VPT>
+__global__ void rmsnorm_vec_kernel(const T* __restrict__ x, const float* res_in, float* res_out,
+                                   const int* __restrict__ row_idx, const void* __restrict__ w, int w_is_f32,
+                                   float eps, T* __restrict__ y, int H) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(row_idx ? row_idx[r] : r) * H;
+    const size_t dst = (size_t)r * H;
+    const int nvec = H >> 3;
+    float v[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) << 3;
+        if ((i >> 3) < nvec) {
+            if (res_in) Vec8<float>::load(res_in + src + i, v[j]);
+            else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[j][k] = 0.f;
+            }
+            if (x) {
+                float xv[8];
+                Vec8<T>::load(x + src + i, xv);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[j][k] += xv[k];
+            }
+            if (res_out) Vec8<float>::store(res_out + dst + i, v[j]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss += v[j][k] * v[j][k];
+        }
+    }
+    const float total = block_sum(ss, red);
+    const float inv = rsqrtf(total / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) << 3;
+        if ((i >> 3) < nvec) {
+            float wv[8];
+            if (w_is_f32) Vec8<float>::load(reinterpret_cast<const float*>(w) + i, wv);
+            else Vec8<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(w) + i, wv);
+            float o[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = v[j][k] * inv * wv[k];
+            Vec8<T>::store(y + dst + i, o);
+        }
+    }
+}
+
+template <typename T>
+static bool launch_rmsnorm_vec(const void* x, const float* res_in, float* res_out, const int* row_idx, const void* w,
+                               int w_is_f32, float eps, void* y, int rows, int H, cudaStream_t stream) {
+    const uintptr_t all = (uintptr_t)x | (uintptr_t)res_in | (uintptr_t)res_out | (uintptr_t)w | (uintptr_t)y;
+    if ((H & 7) || (all & 15)) return false;
+    const int nvec = H >> 3;
+    int threads = ((nvec + 31) / 32) * 32;
+    int vpt = 1;
+    while (threads > 512) { vpt *= 2; threads = (((nvec + vpt - 1) / vpt + 31) / 32) * 32; }
+    if (vpt > 4) return false;
+    const T* xp = (const T*)x;
+    T* yp = (T*)y;
+    if (vpt == 1) rmsnorm_vec_kernel<T, 1><<<rows, threads, 0, stream>>>(xp, res_in, res_out, row_idx, w, w_is_f32, eps, yp, H);
+    else if (vpt == 2) rmsnorm_vec_kernel<T, 2><<<rows, threads, 0, stream>>>(xp, res_in, res_out, row_idx, w, w_is_f32, eps, yp, H);
+    else rmsnorm_vec_kernel<T, 4><<<rows, threads, 0, stream>>>(xp, res_in, res_out, row_idx, w, w_is_f32, eps, yp, H);
+    return true;
+}
+
 MSGL_API int msgl_rmsnorm(const void* x, const float* res_in, float* res_out, const int* row_idx,
                           const void* w, int w_is_f32, float eps, void* y, int rows, int H,
                           int dtype, cudaStream_t stream) {
     if (rows <= 0) return MSGL_OK;
     if (H <= 0) return MSGL_ERR_SIZE;
+    if (dtype == MSGL_F32 && launch_rmsnorm_vec<float>(x, res_in, res_out, row_idx, w, w_is_f32, eps, y, rows, H, stream))
+        return msgl_check_launch();
+    if (dtype == MSGL_BF16 && launch_rmsnorm_vec<__nv_bfloat16>(x, res_in, res_out, row_idx, w, w_is_f32, eps, y, rows, H, stream))
+        return msgl_check_launch();
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     const int cache_row = (size_t)H * 4 <= 40 * 1024;
     const size_t smem = cache_row ? (size_t)H * 4 : 0;
@@ -196,6 +296,108 @@ __global__ void qknorm_rope_kvwrite_kernel(const T* __restrict__ qkv, int qkv_st
     }
 }
 
+// Fast path for head sizes 32, 64, 128, 256 with full rotation: a lane owns E = d / 32 consecutive
+// elements, so loads and stores are contiguous, and its rotation partner (element + d/2) sits in
+// lane ^ 16 -- no shared memory.  Same arithmetic as the general kernel above.
+// E consecutive elements of T as one access of E * sizeof(T) bytes (2 ... 32 bytes, aligned to that size)
+template <typename T, int E> struct Pack {
+    static constexpr int BYTES = E * (int)sizeof(T);
+    static __device__ __forceinline__ void load(const T* p, float (&v)[E]) {
+        __align__(16) T tmp[E];
+        if constexpr (BYTES == 32) {
+            reinterpret_cast<uint4*>(tmp)[0] = reinterpret_cast<const uint4*>(p)[0];
+            reinterpret_cast<uint4*>(tmp)[1] = reinterpret_cast<const uint4*>(p)[1];
+        } else if constexpr (BYTES == 16) {
+            *reinterpret_cast<uint4*>(tmp) = *reinterpret_cast<const uint4*>(p);
+        } else if constexpr (BYTES == 8) {
+            *reinterpret_cast<uint2*>(tmp) = *reinterpret_cast<const uint2*>(p);
+        } else if constexpr (BYTES == 4) {
+            *reinterpret_cast<unsigned*>(tmp) = *reinterpret_cast<const unsigned*>(p);
+        } else {
+#pragma unroll
+            for (int j = 0; j < E; ++j) tmp[j] = p[j];
+        }
+#pragma unroll
+        for (int j = 0; j < E; ++j) v[j] = to_f32<T>(tmp[j]);
+    }
+    static __device__ __forceinline__ void store(T* p, const float (&v)[E]) {
+        __align__(16) T tmp[E];
+#pragma unroll
+        for (int j = 0; j < E; ++j) tmp[j] = from_f32<T>(v[j]);
+        if constexpr (BYTES == 32) {
+            reinterpret_cast<uint4*>(p)[0] = reinterpret_cast<const uint4*>(tmp)[0];
+            reinterpret_cast<uint4*>(p)[1] = reinterpret_cast<const uint4*>(tmp)[1];
+        } else if constexpr (BYTES == 16) {
+            *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(tmp);
+        } else if constexpr (BYTES == 8) {
+            *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(tmp);
+        } else if constexpr (BYTES == 4) {
+            *reinterpret_cast<unsigned*>(p) = *reinterpret_cast<const unsigned*>(tmp);
+        } else {
+#pragma unroll
+            for (int j = 0; j < E; ++j) p[j] = tmp[j];
+        }
+    }
+};
+
+template <typename T, int E>
+__global__ void qknorm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, int qkv_stride,
+                                               const int* __restrict__ positions, const int* __restrict__ out_loc,
+                                               const void* __restrict__ qw, const void* __restrict__ kw, int w_is_f32,
+                                               float eps, const float* __restrict__ table, int max_pos,
+                                               T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                               int page_size, int n_q, int n_kv) {
+    constexpr int d = 32 * E;
+    const int t = blockIdx.x;
+    const int warps = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int head = blockIdx.y * warps + (threadIdx.x >> 5);
+    const int n_heads = n_q + 2 * n_kv;
+    if (head >= n_heads) return;
+    const bool is_q = head < n_q;
+    const bool is_k = !is_q && head < n_q + n_kv;
+    const bool writes_cache = (k_cache != nullptr) && (out_loc != nullptr);
+    if (!is_q && !writes_cache) return;
+
+    const T* src = qkv + (size_t)t * qkv_stride + (size_t)head * d + lane * E;
+    float v[E];
+    Pack<T, E>::load(src, v);
+    const void* nw = is_q ? qw : (is_k ? kw : nullptr);
+    if (nw != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < E; ++j) ss += v[j] * v[j];
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+        for (int j = 0; j < E; ++j) v[j] = v[j] * inv * load_weight(nw, lane * E + j, w_is_f32);
+    }
+    if (table != nullptr && (is_q || is_k)) {
+        int pos = positions[t];
+        pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+        const float* cs = table + (size_t)pos * d;
+        const int pi = (lane & 15) * E;               // index of the pair within the half
+        const bool upper = lane >= 16;
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+            const float c = cs[pi + j], sn = cs[d / 2 + pi + j];
+            v[j] = upper ? (other * sn + v[j] * c) : (v[j] * c - other * sn);
+        }
+    }
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * n_q + head) * d;
+    } else {
+        const int slot = out_loc[t];
+        const int page = slot / page_size, off = slot - page * page_size;
+        const int kvh = is_k ? head - n_q : head - n_q - n_kv;
+        T* base = is_k ? k_cache : v_cache;
+        dst = base + (((size_t)page * n_kv + kvh) * page_size + off) * d;
+    }
+    Pack<T, E>::store(dst + lane * E, v);
+}
+
 MSGL_API int msgl_qknorm_rope_kvwrite(const void* qkv, int qkv_stride, const int* positions, const int* out_loc,
                                       const void* qw, const void* kw, int w_is_f32, float eps,
                                       const float* table, int rot, int max_pos, void* q_out, void* k_cache,
@@ -207,6 +409,24 @@ MSGL_API int msgl_qknorm_rope_kvwrite(const void* qkv, int qkv_stride, const int
     const int warps = n_heads < 8 ? n_heads : 8;
     dim3 grid(T_, (n_heads + warps - 1) / warps);
     const size_t smem = table ? (size_t)warps * d * sizeof(float) : 0;
+    const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 31) == 0 &&
+                         (qkv_stride % (d / 32 > 0 ? d / 32 : 1)) == 0;
+    if (aligned && (d == 32 || d == 64 || d == 128 || d == 256) && (table == nullptr || rot == d) &&
+        (dtype == MSGL_F32 || dtype == MSGL_BF16)) {
+#define QKR_VEC(TT, EE)                                                                                              \
+    qknorm_rope_kvwrite_vec_kernel<TT, EE><<<grid, warps * 32, 0, stream>>>(                                         \
+        (const TT*)qkv, qkv_stride, positions, out_loc, qw, kw, w_is_f32, eps, table, max_pos, (TT*)q_out,           \
+        (TT*)k_cache, (TT*)v_cache, page_size, n_q, n_kv)
+        const int E = d / 32;
+        if (dtype == MSGL_F32) {
+            if (E == 1) QKR_VEC(float, 1); else if (E == 2) QKR_VEC(float, 2); else if (E == 4) QKR_VEC(float, 4); else QKR_VEC(float, 8);
+        } else {
+            if (E == 1) QKR_VEC(__nv_bfloat16, 1); else if (E == 2) QKR_VEC(__nv_bfloat16, 2);
+            else if (E == 4) QKR_VEC(__nv_bfloat16, 4); else QKR_VEC(__nv_bfloat16, 8);
+        }
+#undef QKR_VEC
+        return msgl_check_launch();
+    }
     if (dtype == MSGL_F32)
         qknorm_rope_kvwrite_kernel<float><<<grid, warps * 32, smem, stream>>>(
             (const float*)qkv, qkv_stride, positions, out_loc, qw, kw, w_is_f32, eps, table, rot, max_pos,

@@ -165,7 +165,9 @@ class ModelRunner:
             cid = g.cache_ids[0]
             need = needs[cid]
             G = max(need.q_heads // need.n_kv_heads, 1) if need.q_heads else 1
-            self._group_geom.append((need.n_kv_heads, G))
+            qt = ops.attention_tile_tokens(ops.VARIANT_MMA_DECODE, G, need.head_dim) if ops.mma_supported(need.head_dim, self.dtype) \
+                else ops.attention_tile_tokens(ops.VARIANT_SIMT, G)
+            self._group_geom.append((need.n_kv_heads, G, ops.decode_blocks_per_sm(need.head_dim, self.dtype, G), qt))
 
     # -- device ------------------------------------------------------------------------------
     def _init_device(self, device: str) -> torch.device:
@@ -213,13 +215,12 @@ class ModelRunner:
     def _plan_splits(self, gi: int, q_lens: Sequence[int], kv_lens: Sequence[int], cap: int) -> List[int]:
         """kv splits per request: only short query runs over long contexts are split, and only
         while the launch would otherwise leave most of the 148 SMs idle."""
-        n_kv, G = self._group_geom[gi]
-        qt = max(16 // G, 1) if G <= 16 else 1
+        n_kv, G, per_sm, qt = self._group_geom[gi]
         chunks = 1 if G <= 16 else -(-G // 16)
         blocks = sum(-(-q // qt) for q in q_lens) * n_kv * chunks
-        if blocks >= 2 * SM_COUNT or cap <= 1:
+        want = (SM_COUNT * per_sm) // max(blocks, 1)      # fill the SMs once, not more
+        if want <= 1 or cap <= 1:
             return [1] * len(q_lens)
-        want = -(-2 * SM_COUNT // max(blocks, 1))
         window = self.mgr.groups[gi].window
         out = []
         for q, kv in zip(q_lens, kv_lens):
@@ -360,12 +361,10 @@ class ModelRunner:
         return -(-b // 16) * 16
 
     def _graph_max_split(self, gi: int, b: int) -> int:
-        n_kv, G = self._group_geom[gi]
+        n_kv, G, per_sm, _ = self._group_geom[gi]
         chunks = 1 if G <= 16 else -(-G // 16)
         blocks = b * n_kv * chunks
-        if blocks >= 2 * SM_COUNT:
-            return 1
-        return max(1, min(MAX_KV_SPLIT, -(-2 * SM_COUNT // blocks)))
+        return max(1, min(MAX_KV_SPLIT, (SM_COUNT * per_sm) // blocks))
 
     def _step_graph(self, entries, starts, q_lens, kv_lens) -> torch.Tensor:
         B = len(entries)

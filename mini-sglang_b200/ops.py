@@ -10,6 +10,7 @@ torch binds (cuBLAS), in bfloat16 with float32 accumulation or in true float32 (
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -79,6 +80,8 @@ def _lib():
                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.msgl_swiglu.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.msgl_cast_from_f32.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_void_p]
+        lib.msgl_gemm_small_m.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_int,
+                                          c_int, c_void_p]
         lib.msgl_sample.argtypes = [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_ull, c_void_p,
                                     c_void_p]
         _common = lib
@@ -222,10 +225,23 @@ def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor], row_keys:
 VARIANT_SIMT, VARIANT_MMA_ROWS, VARIANT_MMA_DECODE = 0, 1, 2
 
 
-def attention_tile_tokens(variant: int, group: int) -> int:
+def attention_tile_tokens(variant: int, group: int, head_dim: int = 128) -> int:
     """Tokens per query tile of a kernel variant for a given group size (q heads per kv head)."""
+    if variant == VARIANT_MMA_DECODE:
+        lib = _attn_lib(head_dim)
+        lib.msgl_attention_decode_tile_tokens.restype = c_int
+        return int(lib.msgl_attention_decode_tile_tokens(int(group)))
     rows = 64 if variant == VARIANT_MMA_ROWS else 16
     return rows // group if group <= rows else 1
+
+
+def decode_blocks_per_sm(head_dim: int, dtype: torch.dtype, group: int = 1) -> int:
+    """Blocks of the decode attention kernel that fit one SM (used to choose the kv splits)."""
+    if not mma_supported(head_dim, dtype):
+        return 4
+    lib = _attn_lib(head_dim)
+    lib.msgl_attention_decode_blocks_per_sm.restype = c_int
+    return int(lib.msgl_attention_decode_blocks_per_sm(int(group)))
 
 
 def mma_supported(head_dim: int, dtype: torch.dtype) -> bool:
@@ -275,13 +291,49 @@ def set_true_fp32() -> None:
     torch.set_float32_matmul_precision("highest")
 
 
+SMALL_M_MAX = 8           # tokens up to which the weight-streaming kernel replaces the library GEMM (measured: faster up to 8)
+USE_SMALL_M = os.environ.get("MSGL_NO_SMALL_M", "") == ""
+
+
+def _small_m_ok(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:
+    return (USE_SMALL_M and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+            and 0 < x.shape[0] <= SMALL_M_MAX and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous()
+            and weight.shape[1] % 32 == 0 and weight.shape[0] % 16 == 0
+            and (bias is None or bias.dtype == torch.bfloat16))
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """y = x @ weight^T (+ bias); weight is [out, in] as stored in the checkpoint."""
+    """y = x @ weight^T (+ bias); weight is [out, in] as stored in the checkpoint.
+
+    Up to SMALL_M_MAX bfloat16 rows go through this engine's weight-streaming kernel
+    (csrc/gemm_small_m.cu); everything else is the library GEMM."""
     _need_cuda(x, weight, bias)
+    if _small_m_ok(x, weight, bias) and out_dtype in (None, torch.bfloat16, torch.float32):
+        M, (N, K) = x.shape[0], weight.shape
+        od = out_dtype or torch.bfloat16
+        out = torch.empty((M, N), dtype=od, device=x.device)
+        code = _lib().msgl_gemm_small_m(_ptr(weight), _ptr(x), _ptr(bias), _ptr(out), M, N, K, x.stride(0), N, 0,
+                                        int(od == torch.float32), _stream())
+        _check(code, "gemm_small_m")
+        return out
     if out_dtype is not None and out_dtype != x.dtype:
         y = torch.mm(x, weight.t(), out_dtype=out_dtype)
         if bias is not None:
             y += bias.to(out_dtype)
         return y
     return torch.nn.functional.linear(x, weight, bias)
+
+
+def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x @ gate^T) * (x @ up^T) with gate_up = [gate; up] packed row-wise ([2I, H]).  For a few
+    rows the product and the activation are one kernel and the [T, 2I] intermediate never exists."""
+    _need_cuda(x, gate_up)
+    if _small_m_ok(x, gate_up, None) and (gate_up.shape[0] // 2) % 8 == 0:
+        M, (N, K) = x.shape[0], gate_up.shape
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        code = _lib().msgl_gemm_small_m(_ptr(gate_up), _ptr(x), None, _ptr(out), M, N, K, x.stride(0), N // 2, 1, 0,
+                                        _stream())
+        _check(code, "gemm_small_m (swiglu)")
+        return out
+    return swiglu(torch.nn.functional.linear(x, gate_up))

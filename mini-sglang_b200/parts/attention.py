@@ -112,7 +112,7 @@ class PagedAttention(Mixer):
             gx = ctx.B if ctx.uniform_decode else sum(-(-n // qt) for n in ctx.host_q_lens)
             ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=big, variant=ops.VARIANT_SIMT, grid_x=gx, **common)
         else:
-            qt_dec = ops.attention_tile_tokens(ops.VARIANT_MMA_DECODE, G)
+            qt_dec = ops.attention_tile_tokens(ops.VARIANT_MMA_DECODE, G, self.d)
             qt_row = ops.attention_tile_tokens(ops.VARIANT_MMA_ROWS, G)
             if ctx.uniform_decode:
                 ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=1, variant=ops.VARIANT_MMA_DECODE,

@@ -32,5 +32,4 @@ class SwiGLUMLP(FeedForward):
         self.down = src.fetch(self.name("down_proj.weight")).contiguous()
 
     def forward(self, x, ctx):
-        gu = ops.linear(x, self.gate_up)
-        return ops.linear(ops.swiglu(gu), self.down)
+        return ops.linear(ops.linear_swiglu(x, self.gate_up), self.down)

@@ -77,6 +77,38 @@ def test_swiglu(dtype, T, I):
     torch.testing.assert_close(out.float(), ref.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(16, 32), (48, 96), (6144, 4096), (4096, 12288), (1008, 160)])
+def test_small_m_gemm(M, N, K):
+    g = torch.Generator(device="cpu").manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV)
+    o = ops()
+    o.SMALL_M_MAX = 16            # the kernel takes up to 16 rows; the engine uses it up to 8
+    assert o._small_m_ok(x, w, b)
+    ref = x.float() @ w.float().T
+    y = o.linear(x, w)
+    assert y.dtype == torch.bfloat16
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+    y32 = o.linear(x, w, b, out_dtype=torch.float32)
+    assert y32.dtype == torch.float32
+    torch.testing.assert_close(y32, ref + b.float(), rtol=2e-3, atol=2e-3)
+    # a view with a row stride (rows picked out of a wider buffer)
+    wide = torch.randn(M, K + 64, generator=g).to(torch.bfloat16).to(DEV)
+    torch.testing.assert_close(o.linear(wide[:, :K], w).float(), wide[:, :K].float() @ w.float().T, rtol=2e-2, atol=2e-2)
+    # fused SwiGLU: rows [0, N/2) are the gate, [N/2, N) the up projection
+    if (N // 2) % 8 == 0:
+        z = o.linear_swiglu(x, w)
+        gate, up = ref[:, :N // 2], ref[:, N // 2:]
+        torch.testing.assert_close(z.float(), gate / (1 + torch.exp(-gate)) * up, rtol=2e-2, atol=2e-2)
+    # the library path gives the same numbers (17 rows are past the kernel's limit)
+    x17 = torch.randn(17, K, generator=g).to(torch.bfloat16).to(DEV)
+    assert not o._small_m_ok(x17, w, None)
+    torch.testing.assert_close(o.linear(x17[:M], w).float(), o.linear(x17, w)[:M].float(), rtol=2e-2, atol=2e-2)
+    o.SMALL_M_MAX = 8
+
+
 # ---------------------------------------------------------------------------------------
 def rope_table(max_pos, rot, theta):
     idx = torch.arange(0, rot, 2, dtype=torch.float32)
@@ -93,6 +125,9 @@ def rope_table(max_pos, rot, theta):
     (8, 1, 128, 64, 16, False, torch.bfloat16),       # partial rotation, no norm
     (2, 2, 256, 256, 8, True, torch.float32),
     (3, 1, 80, 0, 2, True, torch.bfloat16),           # no rotation at all
+    (8, 2, 128, 128, 16, True, torch.bfloat16),
+    (5, 5, 64, 64, 3, True, torch.float32),
+    (2, 1, 128, 0, 16, False, torch.bfloat16),
 ])
 def test_qknorm_rope_kvwrite(dtype, n_q, n_kv, d, rot, P, norm, wdtype):
     g = torch.Generator(device="cpu").manual_seed(3)
