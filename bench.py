@@ -224,6 +224,29 @@ def main():
     step_bytes = weight_bytes + B * (CTX - K // 2) * kv_bytes_per_token
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
 
+    # ---- end to end through the Python entry point: host tokens in, host tokens out
+    prompt_len = CTX - (W + K) - 2
+    reqs = [eng.add_request(input_ids=rand_tokens(prompt_len),
+                            sampling_params={"temperature": 0.0, "max_new_tokens": W + K + 1, "ignore_eos": True})
+            for _ in range(B)]
+    while any(r.n_output == 0 for r in reqs):
+        eng.step()
+    for _ in range(W - 1):
+        eng.step()
+    torch.cuda.synchronize()
+    done0 = sum(r.n_output for r in reqs)
+    t0 = time.perf_counter()
+    for _ in range(K):
+        eng.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    done = sum(r.n_output for r in reqs) - done0
+    while not eng.scheduler.idle:
+        eng.step()
+    key = next(iter(runner._graphs)) if runner._graphs else None
+    h2d = 4 * max((g.layout.size for g in runner._graphs.values() if g.layout.B == runner._bucket(B)), default=0)
+    e2e = {"value": round(done / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B}
+
     points = {}
     if not args.skip_points:
         for b in (1, 64):
@@ -250,29 +273,6 @@ def main():
     pf_flops = lin_flops + attn_flops
     prefill = {"value": round(PREFILL / (pf * 1e-3), 1), "tokens": PREFILL, "ms": round(pf, 3),
                "frac": round(pf_flops / (pf * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
-
-    # ---- end to end through the Python entry point: host tokens in, host tokens out
-    prompt_len = CTX - (W + K) - 2
-    reqs = [eng.add_request(input_ids=rand_tokens(prompt_len),
-                            sampling_params={"temperature": 0.0, "max_new_tokens": W + K + 1, "ignore_eos": True})
-            for _ in range(B)]
-    while any(r.n_output == 0 for r in reqs):
-        eng.step()
-    for _ in range(W - 1):
-        eng.step()
-    torch.cuda.synchronize()
-    done0 = sum(r.n_output for r in reqs)
-    t0 = time.perf_counter()
-    for _ in range(K):
-        eng.step()
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
-    done = sum(r.n_output for r in reqs) - done0
-    while not eng.scheduler.idle:
-        eng.step()
-    key = next(iter(runner._graphs)) if runner._graphs else None
-    h2d = 4 * max((g.layout.size for g in runner._graphs.values() if g.layout.B == runner._bucket(B)), default=0)
-    e2e = {"value": round(done / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B}
 
     clocks.stop()
     line = {

@@ -152,6 +152,13 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+// 2^x by the special-function unit (relative error about 2^-22; -inf gives 0), for the bfloat16 kernels
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 constexpr int MMA_KT = 64;        // keys per tile
 constexpr int MMA_WARPS = 4;
 constexpr int MMA_THREADS = MMA_WARPS * 32;
@@ -203,22 +210,25 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
         cp_async16(Qs + r * LDS + c * 8, valid ? (const void*)src : (const void*)qg, valid);
     }
 
-    auto load_kv = [&](int stage, int kt) {
+    // a thread copies half a row of K and of V per tile: row tid / 2, 16-byte chunks 2j + (tid & 1);
+    // the row's page is looked up once per tile, one tile ahead of the copy that needs it
+    const int ld_row = tid >> 1, ld_half = tid & 1;
+    auto tile_page = [&](int kt) -> int {
+        const int key = kt * MMA_KT + ld_row;
+        return (kt < kt_end && key <= p_max) ? bt[key / p.page_size] : -1;
+    };
+    auto load_kv = [&](int stage, int kt, int pg) {
         __nv_bfloat16* Ks = KVs + (size_t)stage * 2 * MMA_KT * LDS;
         __nv_bfloat16* Vs = Ks + MMA_KT * LDS;
-        const int key0 = kt * MMA_KT;
-        for (int idx = tid; idx < MMA_KT * CH; idx += MMA_THREADS) {
-            const int kl = idx / CH, c = idx - kl * CH;
-            const int key = key0 + kl;
-            const bool valid = key <= p_max;
-            size_t off = 0;
-            if (valid) {
-                const int pg = bt[key / p.page_size];
-                const int sl = key % p.page_size;
-                off = (((size_t)pg * p.n_kv + kvh) * p.page_size + sl) * D + c * 8;
-            }
-            cp_async16(Ks + kl * LDS + c * 8, kc + off, valid);
-            cp_async16(Vs + kl * LDS + c * 8, vc + off, valid);
+        const int key = kt * MMA_KT + ld_row;
+        const bool valid = pg >= 0;
+        size_t off = 0;
+        if (valid) off = (((size_t)pg * p.n_kv + kvh) * p.page_size + key % p.page_size) * D;
+#pragma unroll
+        for (int j = 0; j < CH / 2; ++j) {
+            const int c = 2 * j + ld_half;
+            cp_async16(Ks + ld_row * LDS + c * 8, kc + off + c * 8, valid);
+            cp_async16(Vs + ld_row * LDS + c * 8, vc + off + c * 8, valid);
         }
     };
 
@@ -235,14 +245,16 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
     const int n_tiles = kt_end - kt_begin;
-    if (n_tiles > 0) load_kv(0, kt_begin);
+    if (n_tiles > 0) load_kv(0, kt_begin, tile_page(kt_begin));
     cp_async_commit();
+    int pg_next = tile_page(kt_begin + 1);
 
     for (int it = 0; it < n_tiles; ++it) {
         const int kt = kt_begin + it;
         if (it + 1 < n_tiles) {
-            load_kv((it + 1) & 1, kt + 1);
+            load_kv((it + 1) & 1, kt + 1, pg_next);
             cp_async_commit();
+            pg_next = tile_page(kt + 2);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -296,13 +308,13 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
         const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
         const float mu_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, mu_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
-        const float al_lo = exp2f(m_lo - mu_lo), al_hi = exp2f(m_hi - mu_hi);
+        const float al_lo = fast_exp2(m_lo - mu_lo), al_hi = fast_exp2(m_hi - mu_hi);
         m_lo = mn_lo; m_hi = mn_hi;
         l_lo *= al_lo; l_hi *= al_hi;
 #pragma unroll
         for (int nb = 0; nb < NKB; ++nb) {
-            s[nb][0] = exp2f(s[nb][0] - mu_lo); s[nb][1] = exp2f(s[nb][1] - mu_lo);
-            s[nb][2] = exp2f(s[nb][2] - mu_hi); s[nb][3] = exp2f(s[nb][3] - mu_hi);
+            s[nb][0] = fast_exp2(s[nb][0] - mu_lo); s[nb][1] = fast_exp2(s[nb][1] - mu_lo);
+            s[nb][2] = fast_exp2(s[nb][2] - mu_hi); s[nb][3] = fast_exp2(s[nb][3] - mu_hi);
             l_lo += s[nb][0] + s[nb][1];
             l_hi += s[nb][2] + s[nb][3];
         }
@@ -396,7 +408,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
             float acc = 0.f, L = 0.f;
 #pragma unroll
             for (int w = 0; w < MMA_WARPS; ++w) {
-                const float f = exp2f(Mm[w * 16 + r] - Mu);
+                const float f = fast_exp2(Mm[w * 16 + r] - Mu);
                 acc += f * Om[((size_t)w * 16 + r) * D + col];
                 L += f * Lm[w * 16 + r];
             }
@@ -566,13 +578,13 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnParams p
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
         const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
         const float mu_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, mu_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
-        const float al_lo = exp2f(m_lo - mu_lo), al_hi = exp2f(m_hi - mu_hi);
+        const float al_lo = fast_exp2(m_lo - mu_lo), al_hi = fast_exp2(m_hi - mu_hi);
         m_lo = mn_lo; m_hi = mn_hi;
         l_lo *= al_lo; l_hi *= al_hi;
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) {
-            s[nb][0] = exp2f(s[nb][0] - mu_lo); s[nb][1] = exp2f(s[nb][1] - mu_lo);
-            s[nb][2] = exp2f(s[nb][2] - mu_hi); s[nb][3] = exp2f(s[nb][3] - mu_hi);
+            s[nb][0] = fast_exp2(s[nb][0] - mu_lo); s[nb][1] = fast_exp2(s[nb][1] - mu_lo);
+            s[nb][2] = fast_exp2(s[nb][2] - mu_hi); s[nb][3] = fast_exp2(s[nb][3] - mu_hi);
             l_lo += s[nb][0] + s[nb][1];
             l_hi += s[nb][2] + s[nb][3];
         }
@@ -630,7 +642,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnParams p
         float acc = 0.f, L = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
-            const float f = exp2f(Mm[w * 16 + r] - Mu);
+            const float f = fast_exp2(Mm[w * 16 + r] - Mu);
             acc += f * Om[((size_t)w * 16 + r) * D + col];
             L += f * Lm[w * 16 + r];
         }
@@ -842,10 +854,10 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
                 const float mn = fmaxf(m_c[nb][e], mx);
                 const float mu = (mn == -INFINITY) ? 0.f : mn;
-                alpha[nb][e] = exp2f(m_c[nb][e] - mu);
+                alpha[nb][e] = fast_exp2(m_c[nb][e] - mu);
                 m_c[nb][e] = mn;
-                v[e] = exp2f(v[e] - mu);
-                v[e + 2] = exp2f(v[e + 2] - mu);
+                v[e] = fast_exp2(v[e] - mu);
+                v[e + 2] = fast_exp2(v[e + 2] - mu);
                 l_c[nb][e] = l_c[nb][e] * alpha[nb][e] + v[e] + v[e + 2];
                 rescale = rescale || alpha[nb][e] != 1.f;
             }
@@ -926,7 +938,7 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
         float acc = 0.f, L = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
-            const float f = exp2f(Mm[w * C + c] - Mu);
+            const float f = fast_exp2(Mm[w * C + c] - Mu);
             acc += f * Om[((size_t)w * C + c) * D + col];
             L += f * Lm[w * C + c];
         }

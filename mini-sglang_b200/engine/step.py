@@ -234,22 +234,42 @@ class ModelRunner:
         single tokens of a request of length 1 on the dump page."""
         T, B = lay.T, lay.B
         host[:lay.size] = 0
-        t = 0
-        for r, (e, s) in enumerate(zip(entries, starts)):
-            n = len(e.tokens)
-            host[lay.input_ids + t: lay.input_ids + t + n] = e.tokens
-            host[lay.positions + t: lay.positions + t + n] = np.arange(s, s + n, dtype=np.int32)
-            host[lay.token_req + t: lay.token_req + t + n] = r
-            host[lay.q_start + r] = t
-            host[lay.kv_len + r] = s + n
-            host[lay.slots + r] = e.slot
-            for gi in range(len(self.mgr.groups)):
-                host[lay.out_loc[gi] + t: lay.out_loc[gi] + t + n] = self.mgr.slot_mapping(gi, e.slot, s, n)
-                row = self.mgr.block_table_row(gi, e.slot)
+        n_ent = len(entries)
+        if n_ent and all(len(e.tokens) == 1 for e in entries):
+            # one token per request (decode): every field with a handful of vector operations
+            slots = np.fromiter((e.slot for e in entries), dtype=np.int64, count=n_ent)
+            pos = np.asarray(starts, dtype=np.int64)
+            host[lay.input_ids: lay.input_ids + n_ent] = [e.tokens[0] for e in entries]
+            host[lay.positions: lay.positions + n_ent] = pos
+            host[lay.token_req: lay.token_req + n_ent] = np.arange(n_ent, dtype=np.int32)
+            host[lay.q_start: lay.q_start + n_ent] = np.arange(n_ent, dtype=np.int32)
+            host[lay.kv_len: lay.kv_len + n_ent] = pos + 1
+            host[lay.slots: lay.slots + n_ent] = slots
+            P = self.page_size
+            for gi, g in enumerate(self.mgr.groups):
                 mp = lay.max_pages[gi]
-                host[lay.table[gi] + r * mp: lay.table[gi] + r * mp + len(row)] = row
-                host[lay.nsplit[gi] + r] = nsplits[gi][r]
-            t += n
+                host[lay.out_loc[gi]: lay.out_loc[gi] + n_ent] = g.table[slots, pos // P].astype(np.int64) * P + pos % P
+                host[lay.nsplit[gi]: lay.nsplit[gi] + n_ent] = nsplits[gi]
+                width = min(mp, g.table.shape[1])
+                host[lay.table[gi]: lay.table[gi] + n_ent * mp].reshape(n_ent, mp)[:, :width] = g.table[slots, :width]
+            t = n_ent
+        else:
+            t = 0
+            for r, (e, s) in enumerate(zip(entries, starts)):
+                n = len(e.tokens)
+                host[lay.input_ids + t: lay.input_ids + t + n] = e.tokens
+                host[lay.positions + t: lay.positions + t + n] = np.arange(s, s + n, dtype=np.int32)
+                host[lay.token_req + t: lay.token_req + t + n] = r
+                host[lay.q_start + r] = t
+                host[lay.kv_len + r] = s + n
+                host[lay.slots + r] = e.slot
+                for gi in range(len(self.mgr.groups)):
+                    host[lay.out_loc[gi] + t: lay.out_loc[gi] + t + n] = self.mgr.slot_mapping(gi, e.slot, s, n)
+                    row = self.mgr.block_table_row(gi, e.slot)
+                    mp = lay.max_pages[gi]
+                    host[lay.table[gi] + r * mp: lay.table[gi] + r * mp + len(row)] = row
+                    host[lay.nsplit[gi] + r] = nsplits[gi][r]
+                t += n
         for r in range(len(entries), B):          # padding rows of a captured batch size
             host[lay.token_req + t] = r
             host[lay.q_start + r] = t
