@@ -91,16 +91,99 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
 
 
-def reference_arm(args):
-    ref = os.path.join(ROOT, "baseline", "_ref")
-    why = None
-    if not os.path.isdir(os.path.join(ref, "mini_sglang")):
-        why = "reference not installed under baseline/_ref (offline install did not succeed)"
-    else:
-        why = ("the reference's public API (Engine) needs a tokenizer folder, ZMQ worker processes and an attention "
-               "wheel (sgl_kernel FA3, absent; its gate refuses sm_100) that are not available offline on this box")
+def _unavailable(why):
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
+
+
+def reference_arm(args):
+    """The unmodified reference (installed under baseline/_ref) through its own public API:
+    Engine(ServerArgs(...)).async_generate with token ids.  Decode tokens/s = B * (N2 - N1) / (T(N2) - T(N1)) for
+    two runs of B concurrent requests that differ only in max_new_tokens; prefill = a 2,048-token request with
+    one new token.  Its attention comes from the flash_attn 2.x wheel (backend fa2, page size 256: the only one
+    of its backends that has its wheel on this box; fa3 needs sgl_kernel and refuses sm_100)."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "mini_sglang")):
+        return _unavailable("reference not installed under baseline/_ref")
+    import asyncio
+    import multiprocessing
+    import signal
+
+    W, K, B, CTX, PREFILL = max(args.warmup, 3), args.steps, args.batch, args.context, 2048
+    tmp = tempfile.mkdtemp(prefix="msgl_ref_")
+    with open(os.path.join(tmp, "config.json"), "w") as f:
+        json.dump(QWEN3_8B, f)
+    try:
+        from tokenizers import Tokenizer, models, pre_tokenizers
+        tok = Tokenizer(models.WordLevel({f"t{i}": i for i in range(QWEN3_8B["vocab_size"])}, unk_token="t0"))
+        tok.pre_tokenizer = pre_tokenizers.Whitespace()
+        tok.save(os.path.join(tmp, "tokenizer.json"))
+        with open(os.path.join(tmp, "tokenizer_config.json"), "w") as f:
+            json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "unk_token": "t0"}, f)
+    except Exception as e:                                    # noqa: BLE001
+        return _unavailable(f"could not write a stand-in tokenizer for the reference's front end: {e}")
+
+    def cleanup():
+        for ch in multiprocessing.active_children():
+            ch.terminate()
+
+    def on_alarm(signum, frame):
+        cleanup()
+        _unavailable("the reference did not finish within its time limit on this box")
+        os._exit(0)
+
+    signal.signal(signal.SIGALRM, on_alarm)
+    signal.alarm(1500)
+    sys.path.insert(0, ref)
+    try:
+        import torch
+        from mini_sglang import Engine, ServerArgs
+        engine = Engine(ServerArgs(model=tmp, attention_backend="fa2", page_size=256, dummy_load=True,
+                                   max_prefill_tokens=1 << 20, gpu_memory_utilization=0.6, random_seed=0, disable_cuda_graph=True,
+                                   log_level="ERROR"))
+        gen = torch.Generator().manual_seed(0)
+        V = QWEN3_8B["vocab_size"]
+        loop = asyncio.new_event_loop()          # the caller owns the loop the reference's front end runs on
+        asyncio.set_event_loop(loop)
+
+        def run(n_req, prompt_len, max_new):
+            prompts = [torch.randint(0, V, (prompt_len,), generator=gen).tolist() for _ in range(n_req)]
+            sp = {"temperature": 0.0, "max_new_tokens": max_new, "ignore_eos": True}
+
+            async def go():
+                t0 = time.perf_counter()
+                outs = await asyncio.gather(*[engine.async_generate(input_ids=p, sampling_params=sp) for p in prompts])
+                return time.perf_counter() - t0, outs
+            dt, outs = loop.run_until_complete(go())
+            assert all(o["meta_info"]["completion_tokens"] == max_new for o in outs)
+            return dt
+
+        n1, n2 = W, W + K
+        prompt_len = CTX - n2 - 1
+        run(B, prompt_len, n1)                                  # warm-up
+        t1 = min(run(B, prompt_len, n1) for _ in range(2))
+        t2 = min(run(B, prompt_len, n2) for _ in range(2))
+        ms_step = (t2 - t1) / K * 1e3
+        value = B / (ms_step * 1e-3)
+        run(1, PREFILL, 1)
+        pf = min(run(1, PREFILL, 1) for _ in range(3))
+        line = {"metric": "decode tokens/s, Qwen3-8B shape, batch 8, context 4096 (one B200)", "value": round(value, 1),
+                "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(ms_step, 4),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic: random weights (the reference's dummy_load), uniform random token ids",
+                "config": {"model": "Qwen3-8B shape", "layers": 36, "global_batch": B, "seq_len": CTX, "page_size": 256,
+                           "attention_backend": "fa2", "cuda_graph": False, "timing": "wall clock through Engine.async_generate, difference of two runs"},
+                "e2e": {"value": round(value, 1), "unit": "tokens/s"},
+                "prefill": {"value": round(PREFILL / pf, 1), "tokens": PREFILL, "ms": round(pf * 1e3, 3)},
+                "impl": "reference"}
+        print(json.dumps(line))
+    except BaseException as e:                                   # noqa: BLE001
+        _unavailable(f"the reference failed on this box: {type(e).__name__}: {str(e)[:300]}")
+    finally:
+        signal.alarm(0)
+        cleanup()
+    sys.stdout.flush()
+    os._exit(0)
 
 
 def main():
