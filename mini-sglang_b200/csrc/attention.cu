@@ -48,10 +48,19 @@ struct AttnParams {
     float* part_o;            // [(split * T + token) * n_q + head][d]
     float* part_ml;           // [(split * T + token) * n_q + head][2]  (max in log2 units, sum)
     int B, T, n_q, n_kv, d, page_size, bt_stride, window, max_split;
+    int page_shift;           // log2(page_size) when it is a power of two, else -1
     float scale;
     int qlen_min, qlen_max;   // this launch takes the requests with qlen_min <= q_len <= qlen_max
     int uniform_decode;       // every request has exactly one token: tile index == request index
 };
+
+// position -> (page index within the request, slot within the page)
+__device__ __forceinline__ int page_index(const AttnParams& p, int key) {
+    return p.page_shift >= 0 ? (key >> p.page_shift) : (key / p.page_size);
+}
+__device__ __forceinline__ int page_slot(const AttnParams& p, int key) {
+    return p.page_shift >= 0 ? (key & (p.page_size - 1)) : (key % p.page_size);
+}
 
 struct TileInfo {
     int req, t0, n_tok;       // request, first token of the tile within the request, tokens in the tile
@@ -215,7 +224,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
     const int ld_row = tid >> 1, ld_half = tid & 1;
     auto tile_page = [&](int kt) -> int {
         const int key = kt * MMA_KT + ld_row;
-        return (kt < kt_end && key <= p_max) ? bt[key / p.page_size] : -1;
+        return (kt < kt_end && key <= p_max) ? bt[page_index(p, key)] : -1;
     };
     auto load_kv = [&](int stage, int kt, int pg) {
         __nv_bfloat16* Ks = KVs + (size_t)stage * 2 * MMA_KT * LDS;
@@ -223,7 +232,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
         const int key = kt * MMA_KT + ld_row;
         const bool valid = pg >= 0;
         size_t off = 0;
-        if (valid) off = (((size_t)pg * p.n_kv + kvh) * p.page_size + key % p.page_size) * D;
+        if (valid) off = (((size_t)pg * p.n_kv + kvh) * p.page_size + page_slot(p, key)) * D;
 #pragma unroll
         for (int j = 0; j < CH / 2; ++j) {
             const int c = 2 * j + ld_half;
@@ -490,7 +499,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnParams p
     // dependent global load, so it is issued one iteration before the copy that needs it.
     auto unit_page = [&](int i) -> int {
         const int key = (u_begin + warp + i * NW) * DEC_WT + l_key;
-        return (i < n_my && key <= p_max) ? bt[key / p.page_size] : -1;
+        return (i < n_my && key <= p_max) ? bt[page_index(p, key)] : -1;
     };
     auto load_unit = [&](int i, int pg) {      // unit i of this warp into stage i % ST
         __nv_bfloat16* Ks = my_ring + (size_t)(i % ST) * 2 * DEC_WT * LDS;
@@ -498,7 +507,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnParams p
         const int key = (u_begin + warp + i * NW) * DEC_WT + l_key;
         const bool valid = pg >= 0;
         size_t off = 0;
-        if (valid) off = (((size_t)pg * p.n_kv + kvh) * p.page_size + key % p.page_size) * D;
+        if (valid) off = (((size_t)pg * p.n_kv + kvh) * p.page_size + page_slot(p, key)) * D;
 #pragma unroll
         for (int j = 0; j < CH / 2; ++j) {
             const int c = l_half * (CH / 2) + j;
@@ -756,25 +765,37 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
     // page of key (unit i, row lane & 15), or -1 past the last key; one lookup per lane and unit
     auto unit_page = [&](int i) -> int {
         const int key = (u_begin + warp + i * NW) * DEC_WT + (lane & 15);
-        return (i < n_my && key <= p_max) ? bt[key / p.page_size] : -1;
+        return (i < n_my && key <= p_max) ? bt[page_index(p, key)] : -1;
     };
     auto load_v = [&](int i, int pg_row) {         // V of unit i -> stage i % ST; pg_row: page of row v_key
         __nv_bfloat16* Vs = my_ring + (size_t)(i % ST) * DEC_WT * LDS;
         const int key = (u_begin + warp + i * NW) * DEC_WT + v_key;
         const bool valid = pg_row >= 0;
         size_t off = 0;
-        if (valid) off = (((size_t)pg_row * p.n_kv + kvh) * p.page_size + key % p.page_size) * D;
+        if (valid) off = (((size_t)pg_row * p.n_kv + kvh) * p.page_size + page_slot(p, key)) * D;
 #pragma unroll
         for (int j = 0; j < CH / 2; ++j) {
             const int c = 2 * j + v_half;
             cp_async16(Vs + v_key * LDS + c * 8, vc + off + c * 8, valid);
         }
     };
+    // K of unit i into L2 ahead of the register load (no registers, no shared memory spent on it);
+    // pg_row: page of row lane >> 1, each lane touches 128-byte lines of that row
+    auto prefetch_k = [&](int i, int pg_row) {
+        if (pg_row < 0) return;
+        const int key = (u_begin + warp + i * NW) * DEC_WT + v_key;
+        const __nv_bfloat16* row = kc + (((size_t)pg_row * p.n_kv + kvh) * p.page_size + page_slot(p, key)) * D;
+#pragma unroll
+        for (int ln = 0; ln < (D + 127) / 128; ++ln) {
+            const int e = (2 * ln + v_half) * 64;
+            if (e < D) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(row + e));
+        }
+    };
     uint4 k_lo[KP], k_hi[KP];
     auto load_k = [&](int i, int pg_lo, int pg_hi) {      // K of unit i -> registers (rows g and g + 8)
         const int key0 = (u_begin + warp + i * NW) * DEC_WT;
-        const __nv_bfloat16* lo = kc + (((size_t)max(pg_lo, 0) * p.n_kv + kvh) * p.page_size + (key0 + g) % p.page_size) * D + 8 * t;
-        const __nv_bfloat16* hi = kc + (((size_t)max(pg_hi, 0) * p.n_kv + kvh) * p.page_size + (key0 + 8 + g) % p.page_size) * D + 8 * t;
+        const __nv_bfloat16* lo = kc + (((size_t)max(pg_lo, 0) * p.n_kv + kvh) * p.page_size + page_slot(p, key0 + g)) * D + 8 * t;
+        const __nv_bfloat16* hi = kc + (((size_t)max(pg_hi, 0) * p.n_kv + kvh) * p.page_size + page_slot(p, key0 + 8 + g)) * D + 8 * t;
 #pragma unroll
         for (int j = 0; j < KP; ++j) {
             k_lo[j] = pg_lo >= 0 ? ldg16_stream(lo + 32 * j) : make_uint4(0u, 0u, 0u, 0u);
@@ -786,9 +807,11 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
 #pragma unroll
     for (int i = 0; i < ST - 1; ++i) {
         const int pg = unit_page(i);
-        if (i < n_my) load_v(i, __shfl_sync(0xffffffffu, pg, v_key));
+        const int pg_row = __shfl_sync(0xffffffffu, pg, v_key);
+        if (i < n_my) load_v(i, pg_row);
         cp_async_commit();
         if (i == 0 && n_my > 0) load_k(0, __shfl_sync(0xffffffffu, pg, g), __shfl_sync(0xffffffffu, pg, g + 8));
+        if (i > 0 && i < n_my) prefetch_k(i, pg_row);
     }
     int pg_v_next = unit_page(ST - 1);             // for the V copy issued in iteration 0
     int pg_k_next = unit_page(1);                  // for the K load issued in iteration 0
@@ -820,8 +843,11 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
         {
             const int pk = pg_k_next;
             if (i + 1 < n_my) load_k(i + 1, __shfl_sync(0xffffffffu, pk, g), __shfl_sync(0xffffffffu, pk, g + 8));
-            const int pv = pg_v_next;
-            if (i + ST - 1 < n_my) load_v(i + ST - 1, __shfl_sync(0xffffffffu, pv, v_key));
+            const int pv = __shfl_sync(0xffffffffu, pg_v_next, v_key);
+            if (i + ST - 1 < n_my) {
+                load_v(i + ST - 1, pv);
+                prefetch_k(i + ST - 1, pv);
+            }
             cp_async_commit();
             pg_k_next = unit_page(i + 2);
             pg_v_next = unit_page(i + ST);
@@ -1017,8 +1043,8 @@ __global__ void __launch_bounds__(SIMT_THREADS) attn_simt_kernel(const AttnParam
             const int key = key0 + kl;
             float kv = 0.f, vv = 0.f;
             if (key <= p_max) {
-                const int pg = bt[key / p.page_size];
-                const int sl = key % p.page_size;
+                const int pg = bt[page_index(p, key)];
+                const int sl = page_slot(p, key);
                 const size_t off = (((size_t)pg * p.n_kv + kvh) * p.page_size + sl) * D + c;
                 kv = to_f32<T>(kc[off]);
                 vv = to_f32<T>(vc[off]);
@@ -1169,7 +1195,9 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
     p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len;
     p.block_table = block_table; p.nsplit = nsplit; p.part_o = part_o; p.part_ml = part_ml;
     p.B = B; p.T = T_; p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.page_size = page_size; p.bt_stride = bt_stride;
-    p.window = window; p.max_split = max_split; p.scale = scale; p.qlen_min = qlen_min; p.qlen_max = qlen_max;
+    p.window = window; p.max_split = max_split;
+    p.page_shift = -1;
+    if ((page_size & (page_size - 1)) == 0) { int sh = 0; while ((1 << sh) < page_size) ++sh; p.page_shift = sh; } p.scale = scale; p.qlen_min = qlen_min; p.qlen_max = qlen_max;
     p.uniform_decode = uniform_decode;
     const int G = n_q / n_kv;
     const int R = variant == 1 ? 64 : 16;
