@@ -151,8 +151,23 @@ __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* 
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
+// the same with 32-bit shared-memory addresses, so that the hot loops add compile-time offsets to one
+// base register instead of converting a generic pointer for every access
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16_u32(unsigned s, const void* gmem, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void ldmatrix_x4_u32(unsigned (&r)[4], unsigned s) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans_u32(unsigned (&r)[4], unsigned s) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -226,18 +241,21 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
         const int key = kt * MMA_KT + ld_row;
         return (kt < kt_end && key <= p_max) ? bt[page_index(p, key)] : -1;
     };
+    constexpr unsigned STAGE_BYTES = 2u * MMA_KT * LDS * 2u, TILE_BYTES = MMA_KT * LDS * 2u;
+    const unsigned q_s = smem_u32(Qs), kv_s = smem_u32(KVs);
+    const unsigned ld_dst = kv_s + (unsigned)(ld_row * LDS + ld_half * 8) * 2u;
     auto load_kv = [&](int stage, int kt, int pg) {
-        __nv_bfloat16* Ks = KVs + (size_t)stage * 2 * MMA_KT * LDS;
-        __nv_bfloat16* Vs = Ks + MMA_KT * LDS;
+        const unsigned ks = ld_dst + (unsigned)stage * STAGE_BYTES, vs = ks + TILE_BYTES;
         const int key = kt * MMA_KT + ld_row;
         const bool valid = pg >= 0;
         size_t off = 0;
         if (valid) off = (((size_t)pg * p.n_kv + kvh) * p.page_size + page_slot(p, key)) * D;
+        const __nv_bfloat16* ksrc = kc + off + ld_half * 8;
+        const __nv_bfloat16* vsrc = vc + off + ld_half * 8;
 #pragma unroll
         for (int j = 0; j < CH / 2; ++j) {
-            const int c = 2 * j + ld_half;
-            cp_async16(Ks + ld_row * LDS + c * 8, kc + off + c * 8, valid);
-            cp_async16(Vs + ld_row * LDS + c * 8, vc + off + c * 8, valid);
+            cp_async16_u32(ks + j * 32, ksrc + j * 16, valid);
+            cp_async16_u32(vs + j * 32, vsrc + j * 16, valid);
         }
     };
 
@@ -247,6 +265,10 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
     const int r_lo = row_base + (lane >> 2), r_hi = r_lo + 8;
     const int pos_lo = p_min + r_lo / Gc, pos_hi = p_min + r_hi / Gc;   // position of each row's query
     const float sc = p.scale * 1.4426950408889634f;                     // scores in log2 units
+    // per-lane parts of the ldmatrix addresses (bytes)
+    const unsigned q_a = q_s + (unsigned)((row_base + (lane & 15)) * LDS + (lane >> 4) * 8) * 2u;
+    const unsigned k_lane = (unsigned)((key_base + (lane & 7) + ((lane >> 4) & 1) * 8) * LDS + ((lane >> 3) & 1) * 8) * 2u;
+    const unsigned v_lane = (unsigned)((key_base + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS + ((lane >> 4) & 1) * 8) * 2u;
 
     float o[NDB][4];
 #pragma unroll
@@ -269,8 +291,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
             cp_async_wait<0>();
         }
         __syncthreads();
-        const __nv_bfloat16* Ks = KVs + (size_t)(it & 1) * 2 * MMA_KT * LDS;
-        const __nv_bfloat16* Vs = Ks + MMA_KT * LDS;
+        const unsigned ks_a = kv_s + (unsigned)(it & 1) * STAGE_BYTES + k_lane, vs_a = ks_a - k_lane + TILE_BYTES + v_lane;
 
         // ---- S = Q K^T
         float s[NKB][4];
@@ -279,12 +300,11 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
             unsigned a[4];
-            ldmatrix_x4(a, Qs + (row_base + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
+            ldmatrix_x4_u32(a, q_a + kk * 32);
 #pragma unroll
             for (int nb2 = 0; nb2 < NKB / 2; ++nb2) {
                 unsigned b[4];
-                const int key = key_base + nb2 * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
-                ldmatrix_x4(b, Ks + key * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
+                ldmatrix_x4_u32(b, ks_a + (unsigned)(nb2 * 16 * LDS + kk * 16) * 2u);
                 mma_bf16_16816(s[2 * nb2], a, b[0], b[1]);
                 mma_bf16_16816(s[2 * nb2 + 1], a, b[2], b[3]);
             }
@@ -294,20 +314,21 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
         const int key0 = kt * MMA_KT + key_base;
         const bool need_mask = (kt * MMA_KT + MMA_KT - 1 > p_min) ||
                                (p.window > 0 && kt * MMA_KT <= p_max - p.window);
+        // raw scores stay unscaled: the scale is folded into the exponent, 2^(s * sc - m)
         float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
         for (int nb = 0; nb < NKB; ++nb) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                float v = s[nb][e] * sc;
+                float v = s[nb][e];
                 if (need_mask) {
                     const int key = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = (e < 2) ? pos_lo : pos_hi;
                     bool ok = key <= pos;
                     if (p.window > 0) ok = ok && (key > pos - p.window);
                     if (!ok) v = -INFINITY;
+                    s[nb][e] = v;
                 }
-                s[nb][e] = v;
                 if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
             }
         }
@@ -315,20 +336,22 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
         mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float mn_lo = fmaxf(m_lo, mx_lo * sc), mn_hi = fmaxf(m_hi, mx_hi * sc);       // -inf * sc = -inf (sc > 0)
         const float mu_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, mu_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
         const float al_lo = fast_exp2(m_lo - mu_lo), al_hi = fast_exp2(m_hi - mu_hi);
         m_lo = mn_lo; m_hi = mn_hi;
         l_lo *= al_lo; l_hi *= al_hi;
 #pragma unroll
         for (int nb = 0; nb < NKB; ++nb) {
-            s[nb][0] = fast_exp2(s[nb][0] - mu_lo); s[nb][1] = fast_exp2(s[nb][1] - mu_lo);
-            s[nb][2] = fast_exp2(s[nb][2] - mu_hi); s[nb][3] = fast_exp2(s[nb][3] - mu_hi);
+            s[nb][0] = fast_exp2(fmaf(s[nb][0], sc, -mu_lo)); s[nb][1] = fast_exp2(fmaf(s[nb][1], sc, -mu_lo));
+            s[nb][2] = fast_exp2(fmaf(s[nb][2], sc, -mu_hi)); s[nb][3] = fast_exp2(fmaf(s[nb][3], sc, -mu_hi));
             l_lo += s[nb][0] + s[nb][1];
             l_hi += s[nb][2] + s[nb][3];
         }
+        if (__any_sync(0xffffffffu, al_lo != 1.f || al_hi != 1.f)) {      // the running maxima rarely move after the first tiles
 #pragma unroll
-        for (int i = 0; i < NDB; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+            for (int i = 0; i < NDB; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+        }
 
         // ---- O += P V
 #pragma unroll
@@ -341,8 +364,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
 #pragma unroll
             for (int nd2 = 0; nd2 < D / 16; ++nd2) {
                 unsigned b[4];
-                const int key = key_base + j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                ldmatrix_x4_trans(b, Vs + key * LDS + nd2 * 16 + ((lane >> 4) & 1) * 8);
+                ldmatrix_x4_trans_u32(b, vs_a + (unsigned)(j * 16 * LDS + nd2 * 16) * 2u);
                 mma_bf16_16816(o[2 * nd2], a, b[0], b[1]);
                 mma_bf16_16816(o[2 * nd2 + 1], a, b[2], b[3]);
             }
@@ -689,7 +711,7 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned v) {
 }
 __device__ __forceinline__ void mma_bf16_regs(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                               unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
