@@ -736,6 +736,8 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
     __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [NW][ST][16][LDS]  (V only)
     __shared__ int sh_tile[4];
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int G = p.n_q / p.n_kv;
     const int Gc = G <= C ? G : C;
     const int n_chunks = G <= C ? 1 : (G + C - 1) / C;
@@ -1140,6 +1142,8 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
                                     const int* __restrict__ token_req, const int* __restrict__ nsplit,
                                     T* __restrict__ out, int T_, int n_q, int d, int max_split) {
     // one block per (token, head); threads over the head's elements
+    pdl_launch_dependents();
+    pdl_wait();
     const int tok = blockIdx.x, h = blockIdx.y;
     const int req = token_req ? token_req[tok] : tok;
     const int ns = min(max(nsplit[req], 1), max_split);
@@ -1162,6 +1166,10 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
         out[((size_t)tok * n_q + h) * d + c] = from_f32<T>(acc * inv);
     }
 }
+
+#if MSGL_HEAD_DIM == 128
+#include "attention_tc.cuh"
+#endif
 
 // ---------------------------------------------------------------------------------------
 // C entry points
@@ -1273,8 +1281,8 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
                 cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 attr_set = true;
             }
-            if (C == 8) attn_decode_t_kernel<DT, NW, ST, 1><<<grid, NW * 32, smem, stream>>>(p);
-            else attn_decode_t_kernel<DT, NW, ST, 2><<<grid, NW * 32, smem, stream>>>(p);
+            if (C == 8) msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 1>, grid, dim3(NW * 32), smem, stream, p);
+            else msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 2>, grid, dim3(NW * 32), smem, stream, p);
         } else {
             constexpr int ST = (MSGL_HEAD_DIM <= 128) ? MSGL_DEC_STAGES : 2;   // the ring must fit 227 KB
             const size_t smem = sizeof(__nv_bfloat16) * ((size_t)16 * (MSGL_HEAD_DIM + 8) +
@@ -1292,6 +1300,39 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
     return msgl_check_launch();
 }
 
+// tcgen05 prefill attention (head size 128, bfloat16): the requests with qlen_min <= q_len <= qlen_max, no kv
+// splits.  `status` is a device int the kernel sets to 1 if a block gave up waiting (never expected).
+MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, const void* v_cache, const int* q_start,
+                               const int* kv_len, const int* block_table, int B, int T_, int n_q, int n_kv, int d,
+                               int page_size, int bt_stride, int window, float scale, int qlen_min, int qlen_max,
+                               int grid_x, int* status, cudaStream_t stream) {
+#if MSGL_HEAD_DIM == 128
+    if (grid_x <= 0 || B <= 0) return MSGL_OK;
+    if (d != 128 || n_kv <= 0 || n_q % n_kv != 0 || page_size <= 0) return MSGL_ERR_SIZE;
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
+    AttnParams p;
+    p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len;
+    p.block_table = block_table; p.nsplit = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
+    p.B = B; p.T = T_; p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.page_size = page_size; p.bt_stride = bt_stride;
+    p.window = window; p.max_split = 1;
+    p.page_shift = -1;
+    if ((page_size & (page_size - 1)) == 0) { int sh = 0; while ((1 << sh) < page_size) ++sh; p.page_shift = sh; }
+    p.scale = scale; p.qlen_min = qlen_min; p.qlen_max = qlen_max; p.uniform_decode = 0;
+    const int G = n_q / n_kv;
+    const int n_chunks = G <= TC_ROWS ? 1 : (G + TC_ROWS - 1) / TC_ROWS;
+    const size_t smem = (size_t)TC_SMEM_BYTES + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+    }
+    attn_tc_kernel<<<dim3(grid_x, n_kv * n_chunks, 1), TC_THREADS, smem, stream>>>(p, status);
+    return msgl_check_launch();
+#else
+    return MSGL_ERR_SIZE;
+#endif
+}
+
 MSGL_API int msgl_attention_combine(const float* part_o, const float* part_ml, const int* token_req,
                                     const int* nsplit, void* out, int T_, int n_q, int d, int max_split, int dtype,
                                     cudaStream_t stream) {
@@ -1299,10 +1340,10 @@ MSGL_API int msgl_attention_combine(const float* part_o, const float* part_ml, c
     const int threads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
     const dim3 grid(T_, n_q);
     if (dtype == MSGL_F32)
-        attn_combine_kernel<float><<<grid, threads, 0, stream>>>(part_o, part_ml, token_req, nsplit, (float*)out, T_, n_q, d, max_split);
+        msgl_launch_pdl(attn_combine_kernel<float>, grid, dim3(threads), 0, stream, part_o, part_ml, token_req, nsplit, (float*)out, T_, n_q, d, max_split);
     else if (dtype == MSGL_BF16)
-        attn_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(part_o, part_ml, token_req, nsplit,
-                                                                       (__nv_bfloat16*)out, T_, n_q, d, max_split);
+        msgl_launch_pdl(attn_combine_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, part_o, part_ml, token_req, nsplit,
+                        (__nv_bfloat16*)out, T_, n_q, d, max_split);
     else
         return MSGL_ERR_DTYPE;
     return msgl_check_launch();

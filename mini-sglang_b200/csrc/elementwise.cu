@@ -16,6 +16,8 @@
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int H, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -32,9 +34,9 @@ MSGL_API int msgl_embedding(const int* ids, const void* table, float* out, int T
     if (T_ <= 0) return MSGL_OK;
     const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
     if (dtype == MSGL_F32)
-        embedding_kernel<float><<<T_, threads, 0, stream>>>(ids, (const float*)table, out, H, V);
+        msgl_launch_pdl(embedding_kernel<float>, dim3(T_), dim3(threads), 0, stream, ids, (const float*)table, out, H, V);
     else if (dtype == MSGL_BF16)
-        embedding_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, H, V);
+        msgl_launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(T_), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, out, H, V);
     else
         return MSGL_ERR_DTYPE;
     return msgl_check_launch();
@@ -118,6 +120,8 @@ __global__ void rmsnorm_vec_kernel(const T* __restrict__ x, const float* res_in,
                                    const int* __restrict__ row_idx, const void* __restrict__ w, int w_is_f32,
                                    float eps, T* __restrict__ y, int H) {
     __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)(row_idx ? row_idx[r] : r) * H;
     const size_t dst = (size_t)r * H;
@@ -173,9 +177,9 @@ static bool launch_rmsnorm_vec(const void* x, const float* res_in, float* res_ou
     if (vpt > 4) return false;
     const T* xp = (const T*)x;
     T* yp = (T*)y;
-    if (vpt == 1) rmsnorm_vec_kernel<T, 1><<<rows, threads, 0, stream>>>(xp, res_in, res_out, row_idx, w, w_is_f32, eps, yp, H);
-    else if (vpt == 2) rmsnorm_vec_kernel<T, 2><<<rows, threads, 0, stream>>>(xp, res_in, res_out, row_idx, w, w_is_f32, eps, yp, H);
-    else rmsnorm_vec_kernel<T, 4><<<rows, threads, 0, stream>>>(xp, res_in, res_out, row_idx, w, w_is_f32, eps, yp, H);
+    if (vpt == 1) msgl_launch_pdl(rmsnorm_vec_kernel<T, 1>, dim3(rows), dim3(threads), 0, stream, xp, res_in, res_out, row_idx, w, w_is_f32, eps, yp, H);
+    else if (vpt == 2) msgl_launch_pdl(rmsnorm_vec_kernel<T, 2>, dim3(rows), dim3(threads), 0, stream, xp, res_in, res_out, row_idx, w, w_is_f32, eps, yp, H);
+    else msgl_launch_pdl(rmsnorm_vec_kernel<T, 4>, dim3(rows), dim3(threads), 0, stream, xp, res_in, res_out, row_idx, w, w_is_f32, eps, yp, H);
     return true;
 }
 
@@ -348,6 +352,8 @@ __global__ void qknorm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, int qk
                                                T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                                int page_size, int n_q, int n_kv) {
     constexpr int d = 32 * E;
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int warps = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -414,7 +420,7 @@ MSGL_API int msgl_qknorm_rope_kvwrite(const void* qkv, int qkv_stride, const int
     if (aligned && (d == 32 || d == 64 || d == 128 || d == 256) && (table == nullptr || rot == d) &&
         (dtype == MSGL_F32 || dtype == MSGL_BF16)) {
 #define QKR_VEC(TT, EE)                                                                                              \
-    qknorm_rope_kvwrite_vec_kernel<TT, EE><<<grid, warps * 32, 0, stream>>>(                                         \
+    msgl_launch_pdl(qknorm_rope_kvwrite_vec_kernel<TT, EE>, grid, dim3(warps * 32), 0, stream,                       \
         (const TT*)qkv, qkv_stride, positions, out_loc, qw, kw, w_is_f32, eps, table, max_pos, (TT*)q_out,           \
         (TT*)k_cache, (TT*)v_cache, page_size, n_q, n_kv)
         const int E = d / 32;

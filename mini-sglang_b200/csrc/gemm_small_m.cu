@@ -102,17 +102,29 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_small_m_kernel(
     const int n_chunks = K >> 5;
     const int n_my = (n_chunks > warp) ? (n_chunks - warp + GS_WARPS - 1) / GS_WARPS : 0;
 
-    auto fetch = [&](int i) {          // chunk i of this warp -> stage i % GS_PF
+    auto fetch_w = [&](int i) {        // weights of chunk i of this warp -> stage i % GS_PF
         uint4* st = my + (size_t)(i % GS_PF) * SLOTS * 32;
         const size_t k0 = (size_t)(warp + i * GS_WARPS) << 5;
         cp_async16_g(st, w_lo + k0);
         cp_async16_g(st + 32, w_hi + k0);
+    };
+    auto fetch_x = [&](int i) {        // the tokens' part of the same chunk
+        uint4* st = my + (size_t)(i % GS_PF) * SLOTS * 32;
+        const size_t k0 = (size_t)(warp + i * GS_WARPS) << 5;
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) cp_async16_a(st + (2 + nb) * 32, xr[nb] + k0);
     };
+    auto fetch = [&](int i) { fetch_w(i); fetch_x(i); };
+    // The weights do not depend on the kernel before this one: their first chunks are already on the
+    // way while that kernel finishes.  x (its output) is only touched after the wait.
+    pdl_launch_dependents();
+#pragma unroll
+    for (int i = 0; i < GS_PF - 1; ++i)
+        if (i < n_my) fetch_w(i);
+    pdl_wait();
 #pragma unroll
     for (int i = 0; i < GS_PF - 1; ++i) {
-        if (i < n_my) fetch(i);
+        if (i < n_my) fetch_x(i);
         asm volatile("cp.async.commit_group;\n" ::);
     }
     for (int i = 0; i < n_my; ++i) {
@@ -197,19 +209,19 @@ MSGL_API int msgl_gemm_small_m(const void* W, const void* X, const void* bias, v
         const int grid = I / 8;
         if (out_f32) return MSGL_ERR_DTYPE;
         if (M <= 8)
-            gemm_small_m_kernel<1, true, __nv_bfloat16><<<grid, threads, smem1, stream>>>(w, x, nullptr, (__nv_bfloat16*)out, M, N, K, ldx, ldo, I);
+            msgl_launch_pdl(gemm_small_m_kernel<1, true, __nv_bfloat16>, dim3(grid), dim3(threads), smem1, stream, w, x, nullptr, (__nv_bfloat16*)out, M, N, K, ldx, ldo, I);
         else
-            gemm_small_m_kernel<2, true, __nv_bfloat16><<<grid, threads, smem2, stream>>>(w, x, nullptr, (__nv_bfloat16*)out, M, N, K, ldx, ldo, I);
+            msgl_launch_pdl(gemm_small_m_kernel<2, true, __nv_bfloat16>, dim3(grid), dim3(threads), smem2, stream, w, x, nullptr, (__nv_bfloat16*)out, M, N, K, ldx, ldo, I);
         return msgl_check_launch();
     }
     if (N & 15) return MSGL_ERR_SIZE;
     const int grid = N / 16;
     if (out_f32) {
-        if (M <= 8) gemm_small_m_kernel<1, false, float><<<grid, threads, smem1, stream>>>(w, x, b, (float*)out, M, N, K, ldx, ldo, 0);
-        else gemm_small_m_kernel<2, false, float><<<grid, threads, smem2, stream>>>(w, x, b, (float*)out, M, N, K, ldx, ldo, 0);
+        if (M <= 8) msgl_launch_pdl(gemm_small_m_kernel<1, false, float>, dim3(grid), dim3(threads), smem1, stream, w, x, b, (float*)out, M, N, K, ldx, ldo, 0);
+        else msgl_launch_pdl(gemm_small_m_kernel<2, false, float>, dim3(grid), dim3(threads), smem2, stream, w, x, b, (float*)out, M, N, K, ldx, ldo, 0);
     } else {
-        if (M <= 8) gemm_small_m_kernel<1, false, __nv_bfloat16><<<grid, threads, smem1, stream>>>(w, x, b, (__nv_bfloat16*)out, M, N, K, ldx, ldo, 0);
-        else gemm_small_m_kernel<2, false, __nv_bfloat16><<<grid, threads, smem2, stream>>>(w, x, b, (__nv_bfloat16*)out, M, N, K, ldx, ldo, 0);
+        if (M <= 8) msgl_launch_pdl(gemm_small_m_kernel<1, false, __nv_bfloat16>, dim3(grid), dim3(threads), smem1, stream, w, x, b, (__nv_bfloat16*)out, M, N, K, ldx, ldo, 0);
+        else msgl_launch_pdl(gemm_small_m_kernel<2, false, __nv_bfloat16>, dim3(grid), dim3(threads), smem2, stream, w, x, b, (__nv_bfloat16*)out, M, N, K, ldx, ldo, 0);
     }
     return msgl_check_launch();
 }

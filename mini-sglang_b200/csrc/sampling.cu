@@ -57,6 +57,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, long 
                               const int* __restrict__ steps, unsigned long long seed, int* __restrict__ out) {
     __shared__ ArgBest sbest[32];
     __shared__ float sred[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * row_stride;
     const float temp = temperatures ? temperatures[r] : 0.f;
@@ -103,6 +105,6 @@ MSGL_API int msgl_sample(const float* logits, int rows, int vocab, long long row
     if (rows <= 0) return MSGL_OK;
     if (vocab <= 0) return MSGL_ERR_SIZE;
     const int threads = vocab >= 8192 ? 1024 : (vocab >= 1024 ? 256 : 128);
-    sample_kernel<<<rows, threads, 0, stream>>>(logits, vocab, row_stride, temperatures, row_keys, steps, seed, out);
+    msgl_launch_pdl(sample_kernel, dim3(rows), dim3(threads), 0, stream, logits, vocab, row_stride, temperatures, row_keys, steps, seed, out);
     return msgl_check_launch();
 }

@@ -95,6 +95,7 @@ def _attn_lib(head_dim: int):
         lib = _build.attention_library(hd)
         lib.msgl_attention.argtypes = [c_void_p] * 10 + [c_int] * 9 + [c_float] + [c_int] * 6 + [c_void_p]
         lib.msgl_attention_combine.argtypes = [c_void_p] * 5 + [c_int] * 5 + [c_void_p]
+        lib.msgl_attention_tc.argtypes = [c_void_p] * 7 + [c_int] * 8 + [c_float] + [c_int] * 3 + [c_void_p, c_void_p]
         lib.msgl_attention_head_dim.restype = c_int
         _attn[hd] = lib
     return lib
@@ -222,7 +223,39 @@ def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor], row_keys:
 # ---------------------------------------------------------------------------------------
 # attention
 # ---------------------------------------------------------------------------------------
-VARIANT_SIMT, VARIANT_MMA_ROWS, VARIANT_MMA_DECODE = 0, 1, 2
+VARIANT_SIMT, VARIANT_MMA_ROWS, VARIANT_MMA_DECODE, VARIANT_TC = 0, 1, 2, 3
+TC_ROWS = 128                     # query rows per block of the tcgen05 prefill kernel
+USE_TC_ATTENTION = os.environ.get("MSGL_NO_TC_ATTENTION", "") == ""
+_tc_status = None
+
+
+def tc_supported(head_dim: int, dtype: torch.dtype, group: int) -> bool:
+    """The tcgen05 prefill attention kernel takes bfloat16, head size 128."""
+    return USE_TC_ATTENTION and dtype == torch.bfloat16 and head_dim == 128 and group >= 1
+
+
+def check_tc_status() -> None:
+    """Raise if a block of the tcgen05 attention kernel ever gave up waiting (synchronises)."""
+    if _tc_status is not None and int(_tc_status.item()) != 0:
+        raise KernelError("tcgen05 attention: a block timed out waiting for the tensor core; results are invalid")
+
+
+def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *,
+                 q_start: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor, n_kv: int, page_size: int,
+                 window: int, scale: float, qlen_min: int, qlen_max: int, grid_x: int) -> None:
+    """Prefill attention on tcgen05 tensor cores for the requests with q_len in [qlen_min, qlen_max]."""
+    global _tc_status
+    _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table)
+    T, n_q, d = q.shape
+    B = kv_len.numel()
+    assert q.is_contiguous() and out.is_contiguous() and block_table.stride(1) == 1 and q.dtype == torch.bfloat16
+    if _tc_status is None:
+        _tc_status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    code = _attn_lib(d).msgl_attention_tc(
+        _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), B, T, n_q, n_kv,
+        d, page_size, block_table.stride(0), window, float(scale), qlen_min, qlen_max, grid_x, _ptr(_tc_status), _stream())
+    _check(code, "attention_tc")
+
 
 
 def attention_tile_tokens(variant: int, group: int, head_dim: int = 128) -> int:
@@ -231,7 +264,7 @@ def attention_tile_tokens(variant: int, group: int, head_dim: int = 128) -> int:
         lib = _attn_lib(head_dim)
         lib.msgl_attention_decode_tile_tokens.restype = c_int
         return int(lib.msgl_attention_decode_tile_tokens(int(group)))
-    rows = 64 if variant == VARIANT_MMA_ROWS else 16
+    rows = {VARIANT_MMA_ROWS: 64, VARIANT_TC: TC_ROWS}.get(variant, 16)
     return rows // group if group <= rows else 1
 
 
