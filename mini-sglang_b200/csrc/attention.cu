@@ -91,7 +91,9 @@ __device__ __forceinline__ bool find_tile(const AttnParams& p, int tile_tokens, 
                 const int v = __shfl_up_sync(0xffffffffu, inc, o);
                 if (lane >= o) inc += v;
             }
-            const int target = (int)blockIdx.x - base;
+            // heaviest tiles first: with a causal mask the last tiles of a request walk the most keys, and
+            // blocks are handed out in index order
+            const int target = (int)(gridDim.x - 1 - blockIdx.x) - base;
             const unsigned hit = __ballot_sync(0xffffffffu, target < inc);
             if (hit) {
                 const int src = __ffs(hit) - 1;

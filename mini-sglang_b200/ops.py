@@ -236,7 +236,7 @@ def tc_supported(head_dim: int, dtype: torch.dtype, group: int) -> bool:
 
 def check_tc_status() -> None:
     """Raise if a block of the tcgen05 attention kernel ever gave up waiting (synchronises)."""
-    if _tc_status is not None and int(_tc_status.item()) != 0:
+    if _tc_status is not None and int(_tc_status[0].item()) != 0:
         raise KernelError("tcgen05 attention: a block timed out waiting for the tensor core; results are invalid")
 
 
@@ -250,7 +250,7 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_ca
     B = kv_len.numel()
     assert q.is_contiguous() and out.is_contiguous() and block_table.stride(1) == 1 and q.dtype == torch.bfloat16
     if _tc_status is None:
-        _tc_status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        _tc_status = torch.zeros(64, dtype=torch.int32, device=q.device)      # word 0: status; the rest: debug counters
     code = _attn_lib(d).msgl_attention_tc(
         _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), B, T, n_q, n_kv,
         d, page_size, block_table.stride(0), window, float(scale), qlen_min, qlen_max, grid_x, _ptr(_tc_status), _stream())
