@@ -33,7 +33,13 @@
 #define MSGL_DEC_WARPS 4          // warps of the decode kernel
 #endif
 #ifndef MSGL_DEC_STAGES
-#define MSGL_DEC_STAGES 3         // cp.async stages per warp of the decode kernel
+#define MSGL_DEC_STAGES 2         // cp.async stages per warp of the decode kernel (measured best with the L2 prefetch)
+#endif
+#ifndef MSGL_DEC_PFV
+#define MSGL_DEC_PFV 0            // 1: V is prefetched into L2 together with K
+#endif
+#ifndef MSGL_DEC_PFK
+#define MSGL_DEC_PFK 2            // how many units ahead of its use K is prefetched into L2 (beyond the register load)
 #endif
 
 struct AttnParams {
@@ -810,11 +816,16 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
     auto prefetch_k = [&](int i, int pg_row) {
         if (pg_row < 0) return;
         const int key = (u_begin + warp + i * NW) * DEC_WT + v_key;
-        const __nv_bfloat16* row = kc + (((size_t)pg_row * p.n_kv + kvh) * p.page_size + page_slot(p, key)) * D;
+        const size_t off = (((size_t)pg_row * p.n_kv + kvh) * p.page_size + page_slot(p, key)) * D;
 #pragma unroll
         for (int ln = 0; ln < (D + 127) / 128; ++ln) {
             const int e = (2 * ln + v_half) * 64;
-            if (e < D) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(row + e));
+            if (e < D) {
+                asm volatile("prefetch.global.L2 [%0];\n" ::"l"(kc + off + e));
+#if MSGL_DEC_PFV
+                asm volatile("prefetch.global.L2 [%0];\n" ::"l"(vc + off + e));
+#endif
+            }
         }
     };
     uint4 k_lo[KP], k_hi[KP];
@@ -839,6 +850,7 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
         if (i == 0 && n_my > 0) load_k(0, __shfl_sync(0xffffffffu, pg, g), __shfl_sync(0xffffffffu, pg, g + 8));
         if (i > 0 && i < n_my) prefetch_k(i, pg_row);
     }
+    int pg_pf_next = unit_page(MSGL_DEC_PFK);      // for the L2 prefetch issued in iteration 0 (when it has a distance of its own)
     int pg_v_next = unit_page(ST - 1);             // for the V copy issued in iteration 0
     int pg_k_next = unit_page(1);                  // for the K load issued in iteration 0
 
@@ -870,11 +882,15 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
             const int pk = pg_k_next;
             if (i + 1 < n_my) load_k(i + 1, __shfl_sync(0xffffffffu, pk, g), __shfl_sync(0xffffffffu, pk, g + 8));
             const int pv = __shfl_sync(0xffffffffu, pg_v_next, v_key);
-            if (i + ST - 1 < n_my) {
-                load_v(i + ST - 1, pv);
-                prefetch_k(i + ST - 1, pv);
-            }
+            if (i + ST - 1 < n_my) load_v(i + ST - 1, pv);
             cp_async_commit();
+            if (MSGL_DEC_PFK == ST - 1) {
+                if (i + ST - 1 < n_my) prefetch_k(i + ST - 1, pv);
+            } else if (MSGL_DEC_PFK > 0) {
+                const int pf = __shfl_sync(0xffffffffu, pg_pf_next, v_key);
+                if (i + MSGL_DEC_PFK < n_my) prefetch_k(i + MSGL_DEC_PFK, pf);
+                pg_pf_next = unit_page(i + MSGL_DEC_PFK + 1);
+            }
             pg_k_next = unit_page(i + 2);
             pg_v_next = unit_page(i + ST);
         }
