@@ -308,9 +308,11 @@ def main():
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
 
     # ---- end to end through the Python entry point: host tokens in, host tokens out
-    prompt_len = CTX - (W + K) - 2
+    # Prompts are prefilled in portions, so the requests get their first token a few steps apart; max_new_tokens
+    # leaves room for that, so that none of them finishes inside the timed steps.
+    prompt_len = CTX - (W + K) - 16
     reqs = [eng.add_request(input_ids=rand_tokens(prompt_len),
-                            sampling_params={"temperature": 0.0, "max_new_tokens": W + K + 1, "ignore_eos": True})
+                            sampling_params={"temperature": 0.0, "max_new_tokens": W + K + 15, "ignore_eos": True})
             for _ in range(B)]
     while any(r.n_output == 0 for r in reqs):
         eng.step()
@@ -324,6 +326,7 @@ def main():
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     done = sum(r.n_output for r in reqs) - done0
+    assert done == B * K, "a request finished inside the timed steps"
     while not eng.scheduler.idle:
         eng.step()
     key = next(iter(runner._graphs)) if runner._graphs else None
