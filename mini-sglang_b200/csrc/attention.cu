@@ -746,6 +746,7 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
 
     pdl_launch_dependents();
     pdl_wait();
+    pdl_after_wait();
     const int G = p.n_q / p.n_kv;
     const int Gc = G <= C ? G : C;
     const int n_chunks = G <= C ? 1 : (G + C - 1) / C;
@@ -955,6 +956,7 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
         }
         __syncwarp();
     }
+    pdl_late();
     cp_async_wait<0>();
 
     // column sums over the 8 lanes that share a column pair
@@ -1162,6 +1164,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     // one block per (token, head); threads over the head's elements
     pdl_launch_dependents();
     pdl_wait();
+    pdl_after_wait();
     const int tok = blockIdx.x, h = blockIdx.y;
     const int req = token_req ? token_req[tok] : tok;
     const int ns = min(max(nsplit[req], 1), max_split);

@@ -65,14 +65,37 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // pdl_launch_dependents() lets the successor start as soon as every block of this grid has
 // issued it.  Launched the ordinary way both are no-ops.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+// Where a kernel lets its successor start (griddepcontrol.launch_dependents takes effect once every
+// block of the grid has issued it or exited).  MSGL_PDL_MODE: 0 = at pdl_late() (after the main loop of
+// the long kernels, else at exit), 1 = right after the kernel's own pdl_wait() (so at most two kernels
+// overlap), 2 = at the very start (successors of successors pile up on the SMs: measured slower).
+#ifndef MSGL_PDL_MODE
+#define MSGL_PDL_MODE 0
+#endif
+__device__ __forceinline__ void pdl_trigger_() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {          // at a kernel's start, before its wait
+#if MSGL_PDL_MODE == 2
+    pdl_trigger_();
+#endif
+}
+__device__ __forceinline__ void pdl_after_wait() {
+#if MSGL_PDL_MODE == 1
+    pdl_trigger_();
+#endif
+}
+__device__ __forceinline__ void pdl_late() {
+#if MSGL_PDL_MODE == 0
+    pdl_trigger_();
+#endif
+}
 
 #include <stdlib.h>
 static inline bool msgl_pdl_enabled() {
     static int on = -1;
-    // off unless MSGL_PDL=1: measured on B200, the decode graph ran 2-7 % slower with it (the early
-    // blocks of the next kernels take shared memory and issue slots from the running one)
-    if (on < 0) { const char* e = getenv("MSGL_PDL"); on = (e && e[0] && e[0] != '0') ? 1 : 0; }
+    // on unless MSGL_PDL=0.  Measured on B200 (Qwen3-8B layer sizes, decode step in a CUDA graph): batch 8
+    // 4.77 -> 4.57 ms, batch 1 3.77 -> 3.57 ms with the successor released after the main loop
+    // (MSGL_PDL_MODE 0); released at a kernel's start the step was slower than without (4.89 ms).
+    if (on < 0) { const char* e = getenv("MSGL_PDL"); on = (e && e[0] == '0') ? 0 : 1; }
     return on == 1;
 }
 

@@ -18,6 +18,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
                                  float* __restrict__ out, int H, int V) {
     pdl_launch_dependents();
     pdl_wait();
+    pdl_after_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -122,6 +123,7 @@ __global__ void rmsnorm_vec_kernel(const T* __restrict__ x, const float* res_in,
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
+    pdl_after_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)(row_idx ? row_idx[r] : r) * H;
     const size_t dst = (size_t)r * H;
@@ -354,6 +356,7 @@ __global__ void qknorm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, int qk
     constexpr int d = 32 * E;
     pdl_launch_dependents();
     pdl_wait();
+    pdl_after_wait();
     const int t = blockIdx.x;
     const int warps = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;

@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_small_m_kernel(
     for (int i = 0; i < GS_PF - 1; ++i)
         if (i < n_my) fetch_w(i);
     pdl_wait();
+    pdl_after_wait();
 #pragma unroll
     for (int i = 0; i < GS_PF - 1; ++i) {
         if (i < n_my) fetch_x(i);
@@ -141,6 +142,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_small_m_kernel(
             mma_16816(c[nb], wl.z, wh.z, wl.w, wh.w, xv.z, xv.w);
         }
     }
+    pdl_late();         // the stream is read: the next kernel may set itself up beside the reduction
     asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();                      // every warp is done with the ring: reuse it for the sums
     float (*red)[16][8 * NB + 1] = reinterpret_cast<float (*)[16][8 * NB + 1]>(gs_smem);

@@ -59,6 +59,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, long 
     __shared__ float sred[32];
     pdl_launch_dependents();
     pdl_wait();
+    pdl_after_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * row_stride;
     const float temp = temperatures ? temperatures[r] : 0.f;

@@ -155,6 +155,9 @@ class ModelRunner:
         self._pinned_ev = [None, None]
         self._flip = 0
         self._dev_staging = None
+        self._steps_run = 0
+        if self.device.type == "cuda":
+            ops._status_tensor(self.device)          # allocated now, not inside a stream capture
         self.use_cuda_graph = use_cuda_graph and all(getattr(l.mixer, "graph_safe", False) for l in self.model.layers)
         self.max_capture_bs = max_capture_bs
         self._graphs: Dict[Tuple[int, Tuple[int, ...]], _Graph] = {}
@@ -343,8 +346,14 @@ class ModelRunner:
         uniform = all(n == 1 for n in q_lens)
         all_last = uniform and len(want_rows) == B and all(len(e.want) == 1 for e in entries)
 
+        # kernels with bounded waits report through a status word: look at the last copy of it that has
+        # arrived, and queue a fresh one after this step (every step with prompt portions, else now and then)
+        ops.raise_if_failed()
+        self._steps_run += 1
         if self.use_cuda_graph and all_last and B <= self.max_capture_bs:
             logits = self._step_graph(entries, starts, q_lens, kv_lens)
+            if self._steps_run % 32 == 0:
+                ops.poll_status()
         else:
             nsplits = [self._plan_splits(gi, q_lens, kv_lens, MAX_KV_SPLIT) for gi in range(len(self.mgr.groups))]
             max_splits = [max(ns) for ns in nsplits]
@@ -360,6 +369,7 @@ class ModelRunner:
             ctx = self._context(dev, lay, q_lens, kv_lens, [e.slot for e in entries], max_splits, uniform)
             rows = dev[lay.want: lay.want + len(want_rows)]
             logits = self.model.forward(ctx, self._caches(ctx), rows)
+            ops.poll_status()
         for e in entries:
             self.mgr.commit(e.slot, len(e.tokens))
         return logits

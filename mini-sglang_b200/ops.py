@@ -226,7 +226,39 @@ def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor], row_keys:
 VARIANT_SIMT, VARIANT_MMA_ROWS, VARIANT_MMA_DECODE, VARIANT_TC = 0, 1, 2, 3
 TC_ROWS = 128                     # query rows per block of the tcgen05 prefill kernel
 USE_TC_ATTENTION = os.environ.get("MSGL_NO_TC_ATTENTION", "") == ""
-_tc_status = None
+_status = None                    # device int32[64]: word 0 tcgen05 attention; words 4..: debug counters
+_status_host = None               # its pinned mirror, refreshed by poll_status()
+_status_event = None
+
+
+def _status_tensor(device) -> torch.Tensor:
+    global _status, _status_host
+    if _status is None:
+        _status = torch.zeros(64, dtype=torch.int32, device=device)
+        _status_host = torch.zeros(64, dtype=torch.int32).pin_memory()
+    return _status
+
+
+def poll_status() -> None:
+    """Queue a copy of the kernels' status words to the host (no synchronisation).  Not inside a stream capture."""
+    global _status_event
+    if _status is None:
+        return
+    _status_host.copy_(_status, non_blocking=True)
+    _status_event = torch.cuda.Event()
+    _status_event.record()
+
+
+def raise_if_failed(wait: bool = False) -> None:
+    """Raise if a kernel with bounded waits gave up in a launch that the last finished poll_status() saw."""
+    if _status_event is None:
+        return
+    if wait:
+        _status_event.synchronize()
+    elif not _status_event.query():
+        return
+    if int(_status_host[0]) != 0:
+        raise KernelError("tcgen05 attention: a block timed out waiting for the tensor core; results are invalid")
 
 
 def tc_supported(head_dim: int, dtype: torch.dtype, group: int) -> bool:
@@ -234,26 +266,24 @@ def tc_supported(head_dim: int, dtype: torch.dtype, group: int) -> bool:
     return USE_TC_ATTENTION and dtype == torch.bfloat16 and head_dim == 128 and group >= 1
 
 
-def check_tc_status() -> None:
-    """Raise if a block of the tcgen05 attention kernel ever gave up waiting (synchronises)."""
-    if _tc_status is not None and int(_tc_status[0].item()) != 0:
-        raise KernelError("tcgen05 attention: a block timed out waiting for the tensor core; results are invalid")
+def check_kernel_status() -> None:
+    """Raise if a block of a kernel with bounded waits ever gave up waiting (synchronises)."""
+    poll_status()
+    raise_if_failed(wait=True)
 
 
 def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *,
                  q_start: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor, n_kv: int, page_size: int,
                  window: int, scale: float, qlen_min: int, qlen_max: int, grid_x: int) -> None:
     """Prefill attention on tcgen05 tensor cores for the requests with q_len in [qlen_min, qlen_max]."""
-    global _tc_status
     _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table)
     T, n_q, d = q.shape
     B = kv_len.numel()
     assert q.is_contiguous() and out.is_contiguous() and block_table.stride(1) == 1 and q.dtype == torch.bfloat16
-    if _tc_status is None:
-        _tc_status = torch.zeros(64, dtype=torch.int32, device=q.device)      # word 0: status; the rest: debug counters
+    status = _status_tensor(q.device)
     code = _attn_lib(d).msgl_attention_tc(
         _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), B, T, n_q, n_kv,
-        d, page_size, block_table.stride(0), window, float(scale), qlen_min, qlen_max, grid_x, _ptr(_tc_status), _stream())
+        d, page_size, block_table.stride(0), window, float(scale), qlen_min, qlen_max, grid_x, _ptr(status), _stream())
     _check(code, "attention_tc")
 
 
@@ -328,6 +358,10 @@ SMALL_M_MAX = 8           # tokens up to which the weight-streaming kernel repla
 USE_SMALL_M = os.environ.get("MSGL_NO_SMALL_M", "") == ""
 
 
+def _small_m(weight, x, bias, out, M, N, K, ldo, mode, out_f32) -> int:
+    return _lib().msgl_gemm_small_m(_ptr(weight), _ptr(x), _ptr(bias), _ptr(out), M, N, K, x.stride(0), ldo, mode, out_f32, _stream())
+
+
 def _small_m_ok(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:
     return (USE_SMALL_M and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
             and 0 < x.shape[0] <= SMALL_M_MAX and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous()
@@ -346,8 +380,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         M, (N, K) = x.shape[0], weight.shape
         od = out_dtype or torch.bfloat16
         out = torch.empty((M, N), dtype=od, device=x.device)
-        code = _lib().msgl_gemm_small_m(_ptr(weight), _ptr(x), _ptr(bias), _ptr(out), M, N, K, x.stride(0), N, 0,
-                                        int(od == torch.float32), _stream())
+        code = _small_m(weight, x, bias, out, M, N, K, N, 0, int(od == torch.float32))
         _check(code, "gemm_small_m")
         return out
     if out_dtype is not None and out_dtype != x.dtype:
@@ -365,8 +398,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
     if _small_m_ok(x, gate_up, None) and (gate_up.shape[0] // 2) % 8 == 0:
         M, (N, K) = x.shape[0], gate_up.shape
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
-        code = _lib().msgl_gemm_small_m(_ptr(gate_up), _ptr(x), None, _ptr(out), M, N, K, x.stride(0), N // 2, 1, 0,
-                                        _stream())
+        code = _small_m(gate_up, x, None, out, M, N, K, N // 2, 1, 0)
         _check(code, "gemm_small_m (swiglu)")
         return out
     return swiglu(torch.nn.functional.linear(x, gate_up))
