@@ -314,18 +314,18 @@ def main():
     reqs = [eng.add_request(input_ids=rand_tokens(prompt_len),
                             sampling_params={"temperature": 0.0, "max_new_tokens": W + K + 15, "ignore_eos": True})
             for _ in range(B)]
-    while any(r.n_output == 0 for r in reqs):
+    while any(len(r.output) == 0 for r in reqs):
         eng.step()
     for _ in range(W - 1):
         eng.step()
     torch.cuda.synchronize()
-    done0 = sum(r.n_output for r in reqs)
+    done0 = sum(len(r.output) for r in reqs)
     t0 = time.perf_counter()
     for _ in range(K):
         eng.step()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    done = sum(r.n_output for r in reqs) - done0
+    done = sum(len(r.output) for r in reqs) - done0
     assert done == B * K, "a request finished inside the timed steps"
     while not eng.scheduler.idle:
         eng.step()

@@ -30,6 +30,23 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32<T>(row[i]);
 }
 
+// ids[t] < 0 stands for prev[-1 - ids[t]] (a token that an earlier kernel sampled and the host has not read)
+__global__ void resolve_ids_kernel(int* __restrict__ ids, const int* __restrict__ prev, int T_, int n_prev) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T_) return;
+    const int v = ids[t];
+    if (v < 0) {
+        const int r = -1 - v;
+        ids[t] = r < n_prev ? prev[r] : 0;
+    }
+}
+
+MSGL_API int msgl_resolve_ids(void* ids, const void* prev, int T_, int n_prev, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    resolve_ids_kernel<<<(T_ + 255) / 256, 256, 0, stream>>>((int*)ids, (const int*)prev, T_, n_prev);
+    return msgl_check_launch();
+}
+
 MSGL_API int msgl_embedding(const int* ids, const void* table, float* out, int T_, int H, int V,
                             int dtype, cudaStream_t stream) {
     if (T_ <= 0) return MSGL_OK;

@@ -40,6 +40,7 @@ class EngineArgs:
     num_pages: Optional[int] = None          # size of the cache in pages instead of a memory fraction
     chunk_size: int = 8192                   # longest portion of one prompt in one step
     max_context_len: Optional[int] = None    # default: the model's max_position_embeddings
+    disable_overlap: bool = False            # read every step's tokens before the next step is launched
     init_new_token_ratio: float = dataclasses.field(default_factory=lambda: _env("SGLANG_INIT_NEW_TOKEN_RATIO", 0.7))
     min_new_token_ratio_factor: float = dataclasses.field(default_factory=lambda: _env("SGLANG_MIN_NEW_TOKEN_RATIO_FACTOR", 0.14))
     new_token_ratio_decay_steps: int = dataclasses.field(default_factory=lambda: int(_env("SGLANG_NEW_TOKEN_RATIO_DECAY_STEPS", 600)))
@@ -95,6 +96,8 @@ class EngineArgs:
         parser.add_argument("--num_pages", type=int, default=None, help="Cache size in pages (default: from memory).")
         parser.add_argument("--chunk_size", type=int, default=d.chunk_size, help="Longest prompt portion per step.")
         parser.add_argument("--max_context_len", type=int, default=None)
+        parser.add_argument("--disable_overlap", action="store_true",
+                            help="Read a step's tokens before launching the next step (no look-ahead decode).")
 
     @classmethod
     def from_cli_args(cls, ns: argparse.Namespace) -> "EngineArgs":

@@ -63,7 +63,8 @@ class Engine:
             retract_decode_steps=args.retract_decode_steps, enable_prefix_cache=not args.disable_radix_cache,
             eos_ids=spec.eos_token_ids, init_new_token_ratio=args.init_new_token_ratio,
             min_new_token_ratio_factor=args.min_new_token_ratio_factor,
-            new_token_ratio_decay_steps=args.new_token_ratio_decay_steps, seed=args.random_seed)
+            new_token_ratio_decay_steps=args.new_token_ratio_decay_steps, seed=args.random_seed,
+            lookahead=not args.disable_overlap)
         self.tokenizer = _load_tokenizer(args.model)
         self.step_times: List[float] = []
         self._load_seconds = time.time() - t0
@@ -90,7 +91,8 @@ class Engine:
 
     def step(self) -> List[StepOutput]:
         """One scheduler step: the public unit of work (a batch through the model, sampling,
-        bookkeeping).  Returns what each sampled request got."""
+        bookkeeping).  Returns what each sampled request got; unless args.disable_overlap, these are the
+        tokens of the step that the call before launched (they travel to the host while the next step runs)."""
         if self.args.profile:
             t0 = time.perf_counter()
             out = self.scheduler.step()
@@ -100,10 +102,11 @@ class Engine:
         return self.scheduler.step()
 
     def _result(self, req: Req, t_start: float) -> Dict:
-        text = self.tokenizer.decode(req.output) if self.tokenizer is not None else None
-        return {"text": text, "token_ids": list(req.output),
+        out = req.output
+        text = self.tokenizer.decode(out) if self.tokenizer is not None else None
+        return {"text": text, "token_ids": list(out),
                 "meta_info": {"id": req.rid, "finish_reason": req.finish_reason.to_json() if req.finish_reason else None,
-                              "prompt_tokens": req.n_prompt, "completion_tokens": req.n_output,
+                              "prompt_tokens": req.n_prompt, "completion_tokens": len(out),
                               "cached_tokens": req.cached_tokens, "e2e_latency": time.time() - t_start}}
 
     def generate(self, prompt: Union[None, str, List[str]] = None, sampling_params: Union[None, Dict, List[Dict]] = None,
@@ -138,8 +141,8 @@ class Engine:
         while True:
             if not req.finished:
                 self.step()
-            if req.n_output > sent or req.finished:
-                sent = req.n_output
+            if len(req.output) > sent or req.finished:
+                sent = len(req.output)
                 yield self._result(req, t0)
             if req.finished:
                 return

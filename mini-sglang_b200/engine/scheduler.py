@@ -21,6 +21,15 @@ mini_sglang/managers/scheduler_policy.py:47-232, mini_sglang/managers/batch_info
   ratio       new_token_ratio starts at 0.7 * conservativeness, decays to 0.14 of that over 600
               decode steps, and is re-estimated after a retraction.
 
+  overlap     with `lookahead` (and a runner that can take a token from the device) a step's tokens
+              are read one call later: while they travel to the host, the next pure-decode step is
+              already launched with the sampled tokens taken from device memory, so the GPU never
+              waits for the host.  What needs a token's value (a stop token) is seen one step late:
+              the request was fed once more, that result is dropped.  Anything else (a waiting
+              request, a prompt under way, an abort, pages short) first reads the tokens in flight
+              and then plans as usual.  step() then returns the tokens of the step launched by the
+              call before.
+
 The scheduler needs of its runner only `mgr` (a CacheManager), `step(entries) -> logits`, and of
 its sampler `sample(logits, temperatures, row_keys, steps) -> token ids`; tests drive it with
 stand-ins on the CPU.
@@ -82,7 +91,10 @@ class Req:
 
     @property
     def output(self) -> List[int]:
-        return self.tokens[self.n_prompt:]
+        """The generated tokens that the host has seen (the last entry of `tokens` may stand for a token
+        that is still on the device; it is negative then)."""
+        out = self.tokens[self.n_prompt:]
+        return out[:-1] if out and out[-1] < 0 else out
 
     @property
     def finished(self) -> bool:
@@ -101,6 +113,18 @@ class Req:
         return self.finish_reason is not None
 
 
+class _InFlight:
+    """A launched step whose sampled tokens have not been read yet."""
+
+    def __init__(self, reqs, ids, host, event):
+        self.reqs: List[Req] = reqs           # the requests sampled in that step, in row order
+        self.ids = ids                        # their tokens: device tensor (or anything with tolist())
+        self.host = host                      # pinned mirror the copy goes to (None: read `ids` itself)
+        self.event = event
+        self.placeholder: Dict[str, int] = {}  # rid -> index in req.tokens that stands for this step's token
+        self.dead: set = set()                # rids whose token of this step is dropped
+
+
 @dataclasses.dataclass
 class StepOutput:
     req: Req
@@ -113,7 +137,7 @@ class Scheduler:
                  chunk_size: int = 8192, policy: str = "lpm", conservativeness: float = 1.0,
                  retract_decode_steps: int = 20, enable_prefix_cache: bool = True, eos_ids: Sequence[int] = (),
                  init_new_token_ratio: float = 0.7, min_new_token_ratio_factor: float = 0.14,
-                 new_token_ratio_decay_steps: int = 600, seed: int = 0):
+                 new_token_ratio_decay_steps: int = 600, seed: int = 0, lookahead: bool = False):
         if policy == "dfs-weight":
             raise ValueError("schedule policy dfs-weight is not implemented; choose lpm, fcfs, lof or random")
         if policy not in ("lpm", "fcfs", "lof", "random"):
@@ -138,6 +162,10 @@ class Scheduler:
         self.waiting: List[Req] = []
         self.running: List[Req] = []
         self._rand = random.Random(seed)
+        self.lookahead = bool(lookahead) and getattr(runner, "supports_device_tokens", False)
+        self._inflight: Optional[_InFlight] = None
+        self._host_ids = [None, None]         # two pinned buffers for the tokens on their way to the host
+        self._host_flip = 0
         self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "cached_tokens": 0, "retractions": 0,
                       "evicted_pages": 0, "aborted": 0, "finished": 0}
 
@@ -160,7 +188,7 @@ class Scheduler:
 
     @property
     def idle(self) -> bool:
-        return not self.waiting and not self.running
+        return not self.waiting and not self.running and self._inflight is None
 
     # -- accounting ------------------------------------------------------------------------
     def _free_tokens(self) -> int:
@@ -295,6 +323,12 @@ class Scheduler:
     # -- one step ----------------------------------------------------------------------------
     def step(self) -> List[StepOutput]:
         outputs: List[StepOutput] = []
+        if self._inflight is not None:
+            nxt = self._lookahead_rows()
+            if nxt:
+                return self._step_lookahead(nxt)
+            outputs.extend(self._collect(self._inflight, None))
+            self._inflight = None
         # aborted before running
         for r in [r for r in self.waiting if r.to_abort is not None]:
             self.waiting.remove(r)
@@ -412,35 +446,109 @@ class Scheduler:
                 self.stats["prefill_tokens"] += n
         logits = self.runner.step(entries)
         self.stats["steps"] += 1
-        if sampled:
-            ids = self.sampler.sample(logits, [r.params.temperature for r in sampled],
-                                      [r.rng_key for r in sampled], [r.n_output for r in sampled])
-            ids = ids.tolist() if hasattr(ids, "tolist") else list(ids)
-        else:
-            ids = []
-
-        # 5. results
-        now = time.time()
-        for r, tok in zip(sampled, ids):
-            r.tokens.append(int(tok))
-            if r.t_first_token is None:
-                r.t_first_token = now
-            if r.check_finished():
-                self._release(r, insert=True)
-                self.running.remove(r)
-                self.stats["finished"] += 1
-                outputs.append(StepOutput(r, int(tok), True))
-            else:
-                if not r.prompt_inserted and self.tree is not None:
-                    self._insert(r)               # the prompt's pages become shareable
-                r.prompt_inserted = True
-                outputs.append(StepOutput(r, int(tok), False))
+        flight = self._sample(logits, sampled)
+        if self.lookahead:
+            self._inflight = flight          # read at the next call
+        elif flight is not None:
+            outputs.extend(self._collect(flight, None))
         for r in [r for r in self.running if r.to_abort is not None and not r.finished]:
             r.check_finished()
             self._release(r, insert=False)
             self.running.remove(r)
             self.stats["aborted"] += 1
             outputs.append(StepOutput(r, None, True))
+        return outputs
+
+    # -- sampling and results ---------------------------------------------------------------
+    def _sample(self, logits, sampled: List[Req]) -> Optional[_InFlight]:
+        """Sample one token for every request in `sampled` and start its way to the host."""
+        if not sampled:
+            return None
+        ids = self.sampler.sample(logits, [r.params.temperature for r in sampled],
+                                  [r.rng_key for r in sampled], [r.n_output for r in sampled])
+        host = event = None
+        if self.lookahead and getattr(ids, "is_cuda", False):
+            import torch
+            k = self._host_flip
+            self._host_flip ^= 1
+            if self._host_ids[k] is None or self._host_ids[k].numel() < len(sampled):
+                self._host_ids[k] = torch.empty(max(1024, len(sampled)), dtype=ids.dtype, pin_memory=True)
+            host = self._host_ids[k][:len(sampled)]
+            host.copy_(ids, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+        return _InFlight(sampled, ids, host, event)
+
+    def _collect(self, flight: _InFlight, successor: Optional[_InFlight]) -> List[StepOutput]:
+        """Read a launched step's tokens and do what follows from them: append, finish, free.
+        `successor` is the step launched on top of it (its rows of requests that turn out to be
+        finished are dropped)."""
+        outputs: List[StepOutput] = []
+        if flight.host is not None:
+            flight.event.synchronize()
+            ids = flight.host.tolist()
+        else:
+            ids = flight.ids.tolist() if hasattr(flight.ids, "tolist") else list(flight.ids)
+        now = time.time()
+        for r, tok in zip(flight.reqs, ids):
+            if r.rid in flight.dead or r.finished:
+                continue
+            tok = int(tok)
+            at = flight.placeholder.get(r.rid)
+            if at is None:
+                r.tokens.append(tok)
+            else:
+                r.tokens[at] = tok
+            if r.t_first_token is None:
+                r.t_first_token = now
+            if r.check_finished():
+                if successor is not None:
+                    successor.dead.add(r.rid)     # it was fed once more meanwhile: that result is void
+                self._release(r, insert=True)
+                self.running.remove(r)
+                self.stats["finished"] += 1
+                outputs.append(StepOutput(r, tok, True))
+            else:
+                if not r.prompt_inserted and self.tree is not None:
+                    self._insert(r)               # the prompt's pages become shareable
+                r.prompt_inserted = True
+                outputs.append(StepOutput(r, tok, False))
+        return outputs
+
+    def _lookahead_rows(self) -> List[Tuple[int, Req]]:
+        """(row in the step in flight, request) of the requests that the next step can feed before
+        that step's tokens are known; empty if the next step needs the usual planning."""
+        flight = self._inflight
+        if not self.lookahead or flight is None or self.waiting:
+            return []
+        if any(r.to_abort is not None for r in self.running):
+            return []
+        live = [(row, r) for row, r in enumerate(flight.reqs) if r.rid not in flight.dead and not r.finished]
+        if len(live) != len(self.running) or {id(r) for _, r in live} != {id(r) for r in self.running}:
+            return []                             # a prompt is still under way
+        # the token in flight is the last one of those that reach max_new_tokens with it
+        nxt = [(row, r) for row, r in live if r.n_output + 1 < r.params.max_new_tokens]
+        if not nxt or len(nxt) > self.max_step_tokens:
+            return []
+        if not self._make_room(self._decode_pages([r for _, r in nxt], 1)):
+            return []                             # pages short: retraction wants the tokens first
+        return nxt
+
+    def _step_lookahead(self, nxt: List[Tuple[int, Req]]) -> List[StepOutput]:
+        flight = self._inflight
+        self.new_token_ratio = max(self.new_token_ratio - self.ratio_decay, self.min_ratio)
+        entries, sampled = [], []
+        for row, r in nxt:
+            flight.placeholder[r.rid] = len(r.tokens)
+            r.tokens.append(-1 - row)             # stands for row `row` of the tokens in flight
+            entries.append(StepEntry(r.slot, [-1 - row], [0]))
+            sampled.append(r)
+        self.stats["decode_tokens"] += len(nxt)
+        logits = self.runner.step(entries, prev_ids=flight.ids)
+        self.stats["steps"] += 1
+        successor = self._sample(logits, sampled)
+        outputs = self._collect(flight, successor)
+        self._inflight = successor
         return outputs
 
     # -- maintenance -----------------------------------------------------------------------

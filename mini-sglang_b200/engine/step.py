@@ -317,15 +317,21 @@ class ModelRunner:
                 need[gi] += n
         return [max(0, n - g.pool.available) for n, g in zip(need, self.mgr.groups)]
 
+    supports_device_tokens = True
+
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], prev_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Run one batch.  With `prev_ids` (int32 on the device, e.g. the tokens a sampler just wrote), a
+        token id -1 - r in an entry stands for prev_ids[r]: it is put in place on the device, so the host
+        need not have seen it."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         V = self.vocab_size
+        lowest = -int(prev_ids.numel()) if prev_ids is not None else 0        # -1 - r: row r of prev_ids, on the device
         for e in entries:
             toks = np.asarray(e.tokens)
-            if toks.min() < 0 or toks.max() >= V:
+            if toks.min() < lowest or toks.max() >= V:
                 raise ValueError(f"token id outside [0, {V}) in the entry of slot {e.slot}")
             for w in e.want:
                 if not 0 <= w < len(e.tokens):
@@ -351,7 +357,7 @@ class ModelRunner:
         ops.raise_if_failed()
         self._steps_run += 1
         if self.use_cuda_graph and all_last and B <= self.max_capture_bs:
-            logits = self._step_graph(entries, starts, q_lens, kv_lens)
+            logits = self._step_graph(entries, starts, q_lens, kv_lens, prev_ids)
             if self._steps_run % 32 == 0:
                 ops.poll_status()
         else:
@@ -366,6 +372,8 @@ class ModelRunner:
             dev = self._dev_staging
             dev[:lay.size].copy_(host[:lay.size], non_blocking=True)
             self._mark(idx)
+            if prev_ids is not None:
+                ops.resolve_ids(dev[lay.input_ids: lay.input_ids + T], prev_ids)
             ctx = self._context(dev, lay, q_lens, kv_lens, [e.slot for e in entries], max_splits, uniform)
             rows = dev[lay.want: lay.want + len(want_rows)]
             logits = self.model.forward(ctx, self._caches(ctx), rows)
@@ -396,7 +404,7 @@ class ModelRunner:
         blocks = b * n_kv * chunks
         return max(1, min(MAX_KV_SPLIT, (SM_COUNT * per_sm) // blocks))
 
-    def _step_graph(self, entries, starts, q_lens, kv_lens) -> torch.Tensor:
+    def _step_graph(self, entries, starts, q_lens, kv_lens, prev_ids=None) -> torch.Tensor:
         B = len(entries)
         b = self._bucket(B)
         need_pages = [max(int(g.n_pages[e.slot]) for e in entries) for g in self.mgr.groups]
@@ -415,6 +423,8 @@ class ModelRunner:
         self._fill(host.numpy(), lay, entries, starts, list(range(b)), nsplits)
         gr.dev.copy_(host[:lay.size], non_blocking=True)
         self._mark(idx)
+        if prev_ids is not None:
+            ops.resolve_ids(gr.dev[lay.input_ids: lay.input_ids + B], prev_ids)
         gr.graph.replay()
         ops.LAUNCHES += gr.n_kernels
         return gr.logits[:B]

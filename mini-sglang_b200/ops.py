@@ -73,6 +73,7 @@ def _lib():
     if _common is None:
         lib = _build.common_library()
         lib.msgl_embedding.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.msgl_resolve_ids.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.msgl_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p,
                                      c_int, c_int, c_int, c_void_p]
         lib.msgl_qknorm_rope_kvwrite.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -119,6 +120,13 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     _check(_lib().msgl_embedding(_ptr(ids), _ptr(table), _ptr(out), T, H, V, _dt(table), _stream()), "embedding")
     return out
+
+
+def resolve_ids(ids: torch.Tensor, prev: torch.Tensor) -> None:
+    """In place: ids[t] = prev[-1 - ids[t]] where ids[t] < 0 (int32, on the device)."""
+    _need_cuda(ids, prev)
+    assert ids.dtype == torch.int32 and prev.dtype == torch.int32 and ids.is_contiguous() and prev.is_contiguous()
+    _check(_lib().msgl_resolve_ids(_ptr(ids), _ptr(prev), ids.numel(), prev.numel(), _stream()), "resolve_ids")
 
 
 def rmsnorm(weight: torch.Tensor, eps: float, *, x: Optional[torch.Tensor] = None,

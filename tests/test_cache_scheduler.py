@@ -170,10 +170,14 @@ class FakeRunner:
         self.mgr = mgr
         self.history = {}
         self.steps = []
+        self.lookahead_steps = 0
 
-    def step(self, entries):
+    supports_device_tokens = True
+
+    def step(self, entries, prev_ids=None):
         rows = []
         self.steps.append([(e.slot, len(e.tokens)) for e in entries])
+        self.lookahead_steps += prev_ids is not None
         short = [0] * len(self.mgr.groups)
         for e in entries:
             for gi, n in enumerate(self.mgr.pages_needed(e.slot, len(e.tokens))):
@@ -184,8 +188,10 @@ class FakeRunner:
             start = int(self.mgr.length[e.slot])
             # tokens before `start` may sit in pages taken over from the prefix cache: the request knows them
             req = next(r for r in self.sched.running if r.slot == e.slot)
-            hist = list(req.tokens[:start]) + list(e.tokens)
             assert list(req.tokens[start:start + len(e.tokens)]) == list(e.tokens)
+            fed = [int(prev_ids[-1 - t]) if t < 0 else t for t in e.tokens]      # -1 - r: row r of the tokens in flight
+            hist = list(req.tokens[:start]) + fed
+            assert min(hist) >= 0
             self.mgr.reserve(e.slot, len(e.tokens))
             for w in e.want:
                 row = torch.zeros(self.V)
@@ -201,15 +207,15 @@ class ArgmaxSampler:
 
 
 def run_all(page_size, num_pages, prompts, max_new, *, chunk=8192, budget=16384, policy="lpm", max_reqs=8,
-            prefix_cache=True, conservativeness=1.0):
+            prefix_cache=True, conservativeness=1.0, lookahead=False, ignore_eos=True, eos=0):
     mgr = CacheManager({0: PagedKVNeed(2, 16)}, page_size=page_size, num_pages=num_pages, max_reqs=max_reqs,
                        max_context_len=4096, max_step_tokens=budget)
     runner = FakeRunner(mgr)
     sch = Scheduler(runner, ArgmaxSampler(), max_num_reqs=max_reqs, max_step_tokens=budget, chunk_size=chunk,
-                    policy=policy, enable_prefix_cache=prefix_cache, eos_ids=[0], conservativeness=conservativeness,
-                    retract_decode_steps=4)
+                    policy=policy, enable_prefix_cache=prefix_cache, eos_ids=[eos], conservativeness=conservativeness,
+                    retract_decode_steps=4, lookahead=lookahead)
     runner.sched = sch
-    reqs = [Req(f"r{i}", p, SamplingParams(max_new_tokens=m, ignore_eos=True)) for i, (p, m) in enumerate(zip(prompts, max_new))]
+    reqs = [Req(f"r{i}", p, SamplingParams(max_new_tokens=m, ignore_eos=ignore_eos)) for i, (p, m) in enumerate(zip(prompts, max_new))]
     for r in reqs:
         sch.add_request(r)
     guard = 0
@@ -246,6 +252,29 @@ def test_scheduler_outputs_do_not_depend_on_the_schedule():
         budget = kw.get("budget", 16384)
         assert all(sum(n for _, n in st) <= budget for st in runner.steps)
         assert all(n <= kw.get("chunk", 8192) for st in runner.steps for _, n in st)
+
+
+def test_lookahead_decode_gives_the_same_tokens():
+    """Launching the next decode step before the last tokens are read changes nothing but the timing:
+    same outputs and finish reasons, with stop tokens (seen one step late), lengths, tiny pools."""
+    prompts = prompts_for(3, 10, 5, 70, shared=36)
+    max_new = [1 + (i * 5) % 17 for i in range(10)]
+    for eos, ignore in [(0, True), (7, False), (23, False)]:
+        for kw in [dict(page_size=4, num_pages=4000, policy="fcfs", prefix_cache=False),
+                   dict(page_size=16, num_pages=30, chunk=16, budget=48),
+                   dict(page_size=4, num_pages=45, policy="random", max_reqs=3),
+                   dict(page_size=1, num_pages=300, policy="lpm")]:
+            kw = dict(kw)
+            page_size, num_pages = kw.pop("page_size"), kw.pop("num_pages")
+            base, sch0, run0 = run_all(page_size, num_pages, prompts, max_new, eos=eos, ignore_eos=ignore, **kw)
+            look, sch1, run1 = run_all(page_size, num_pages, prompts, max_new, eos=eos, ignore_eos=ignore, lookahead=True, **kw)
+            assert run0.lookahead_steps == 0
+            assert [r.output for r in look] == [r.output for r in base], (eos, kw)
+            assert [r.finish_reason.type for r in look] == [r.finish_reason.type for r in base]
+            assert all(t >= 0 for r in look for t in r.tokens)
+    assert run1.lookahead_steps > 0
+    stops = [r for r in look if r.finish_reason.type == "stop"]
+    assert stops and all(r.tokens[-1] == 23 for r in stops)
 
 
 def test_scheduler_mixes_decode_tokens_with_prompt_portions():

@@ -109,6 +109,48 @@ def test_stream_and_eos_stop():
     assert out["token_ids"] == want[:k + 1] and out["meta_info"]["finish_reason"] == {"type": "stop", "matched": want[k]}
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_decode_gives_the_same_tokens(dtype):
+    """The engine launches a decode step before it has read the tokens of the step before (they are put in
+    place on the device).  Same tokens, stop tokens and counts as with every step read first."""
+    name, cfg = "B", CONFIGS["B"]
+    prompts = [random_tokens(n, cfg["vocab_size"], 1400 + n) for n in (7, 16, 23, 31, 5)]
+    greedy = {"temperature": 0.0, "max_new_tokens": 14, "ignore_eos": True}
+    a = make_engine(name, dtype, disable_overlap=True)
+    b = make_engine(name, dtype)
+    assert not a.scheduler.lookahead and b.scheduler.lookahead
+    base = a.generate(input_ids=prompts, sampling_params=greedy)
+    steps_before = b.scheduler.stats["steps"]
+    look = b.generate(input_ids=prompts, sampling_params=greedy)
+    assert [o["token_ids"] for o in look] == [o["token_ids"] for o in base]
+    assert b.scheduler.stats["steps"] - steps_before == a.scheduler.stats["steps"]
+    # stop tokens are seen one step late: the extra step's result must not leak into the output
+    stop = base[1]["token_ids"][4]
+    sps = [{"temperature": 0.0, "max_new_tokens": 3 + 2 * i, "eos_token_id": stop} for i in range(5)]
+    base = a.generate(input_ids=prompts, sampling_params=sps)
+    look = b.generate(input_ids=prompts, sampling_params=sps)
+    assert [(o["token_ids"], o["meta_info"]["finish_reason"]) for o in look] == \
+           [(o["token_ids"], o["meta_info"]["finish_reason"]) for o in base]
+    assert any(o["meta_info"]["finish_reason"]["type"] == "stop" for o in base)
+    # sampling with temperature draws the same numbers
+    sps = [{"temperature": 0.8, "max_new_tokens": 9, "ignore_eos": True, "seed": 5 + i} for i in range(5)]
+    assert [o["token_ids"] for o in b.generate(input_ids=prompts, sampling_params=sps)] == \
+           [o["token_ids"] for o in a.generate(input_ids=prompts, sampling_params=sps)]
+    # requests that arrive while others decode
+    r1 = b.add_request(input_ids=prompts[0], sampling_params=greedy)
+    for _ in range(4):
+        b.step()
+    r2 = b.add_request(input_ids=prompts[3], sampling_params=greedy)
+    while not (r1.finished and r2.finished):
+        b.step()
+    want = a.generate(input_ids=[prompts[0], prompts[3]], sampling_params=greedy)
+    assert [r1.output, r2.output] == [o["token_ids"] for o in want]
+    while not b.scheduler.idle:
+        b.step()
+    a.scheduler.check_idle_invariants()
+    b.scheduler.check_idle_invariants()
+
+
 def test_command_line():
     name, cfg = "A", CONFIGS["A"]
     p = random_tokens(6, cfg["vocab_size"], 1400)
