@@ -3,40 +3,56 @@
 // A block owns 128 query rows -- (token, head-in-group) pairs of one kv head, so a GQA group shares
 // the keys it reads -- and walks the request's keys in tiles of 128:
 //
-//     S = Q K^T        tcgen05.mma 128x128x16 (x8 over the head size), accumulator in TMEM (fp32)
-//     softmax          thread t owns row t = TMEM lane t: tcgen05.ld, running maximum and sum in
-//                      registers (no shuffles), P = 2^(s*scale - m) rounded to bfloat16 into shared memory
-//     O += P V         tcgen05.mma 128x128x16 (x8 over the keys), accumulator in TMEM; V is used as it
-//                      lies in the cache ([key][d]: MN-major B operand), no transpose
+//     S = Q K^T        tcgen05.mma 128x128x16 (x8 over the head size), Q and K from shared memory,
+//                      accumulator in tensor memory (fp32, 128 columns)
+//     softmax          thread t owns row t = TMEM lane t.  Two passes over S with tcgen05.ld: the row
+//                      maximum, then P = 2^(s*scale - m) rounded to bfloat16 and written back with
+//                      tcgen05.st over the columns of S it has consumed (two keys per 32-bit column)
+//     O += P V         tcgen05.mma 128x128x16 (x8 over the keys): the A operand P comes from tensor
+//                      memory, V from shared memory as it lies in the cache ([key][d]: MN-major B
+//                      operand, no transpose); accumulator in tensor memory (128 columns)
 //
-// Roles: warps 0-3 do the softmax (thread t owns row t), warp 4 gathers K and V rows from the paged
-// cache, one lane of warp 5 issues the tensor-core work.  They meet only at mbarriers, so the
-// tensor core computes the next tile's scores and the loader fetches two tiles ahead while the
-// softmax threads work on the current tile.
+// Reading an operand from shared memory is what bounds the tensor core here (a 128x128x16 step reads
+// 8 KB and takes as long as that read); with P in tensor memory the second product reads half as much,
+// the threads store P without swizzle arithmetic or proxy fence, and S and P share their columns.
 //
-// Operands sit in shared memory in the 128-byte-swizzled layout the tensor core reads through
+// Roles: warps 0-3 do the softmax, warp 4 gathers Q and the K tiles from the paged cache, warp 5 the
+// V tiles, one lane of warp 6 issues the tensor-core work.  They meet only at mbarriers.  A block
+// computes S(i), softmax(i), P V(i) one after the other; two blocks share an SM (256 of its 512
+// TMEM columns and 97 KB of its shared memory each), so one block's softmax runs beside the
+// other's products, and K(i+1), V(i+1) arrive meanwhile.
+//
+// K, V and Q sit in shared memory in the 128-byte-swizzled layout the tensor core reads through
 // matrix descriptors: a [rows x 128] tile is two halves of 64 columns; in a half, row r is 128
-// contiguous bytes at r*128 and its 16-byte chunk c is stored at chunk position c ^ (r & 7).  K and
-// V rows are gathered from the paged cache with cp.async straight into that layout (any page size).
-// S is double-buffered in TMEM, so the tensor core computes the next tile's scores while the
-// threads are busy with this tile's softmax.  When a row's reference maximum moves, O is rescaled in TMEM
-// (load, multiply, store) by the thread that owns the row; the block skips that when no row moved.
+// contiguous bytes at r*128 and its 16-byte chunk c is stored at chunk position c ^ (r & 7).
+// K and V tiles come by TMA (cp.async.bulk.tensor, 2-d tiled, 128-byte swizzle): the cache is one
+// [rows x 128] tensor, a page of a kv head is a run of page_size rows, so a tile is 128 / page_size
+// boxes per half, each issued by one lane and all completing on the stage's mbarrier.  V rows past the
+// last key a block may see are zeroed afterwards (free cache slots may hold anything, and 0 x NaN
+// would spoil O); K rows there only reach masked scores.  Page sizes that are no multiple of 8 (or
+// above 128) fall back to cp.async gathers of single rows.  Q is gathered once by all threads.
+// When a row's reference maximum moves, O is rescaled in TMEM (load, multiply, store) by the thread
+// that owns the row; a warp skips that when none of its rows moved.
 //
 // Every wait on an mbarrier is bounded; a block that gives up writes a code to p.status, frees its
 // TMEM and returns (its output rows are then wrong, which the host reports as an error).
 #pragma once
+#include <cuda.h>          // CUtensorMap and its enums; the encoder itself is looked up at run time (no link to the driver library)
+#include <map>
+#include <mutex>
+#include <tuple>
 
 constexpr int TC_ROWS = 128;      // query rows per block
-constexpr int TC_KT = 64;         // keys per tile
+constexpr int TC_KT = 128;        // keys per tile
 constexpr int TC_D = 128;         // head size
 constexpr int TC_SOFTMAX_THREADS = 128;    // warps 0-3: one thread per query row
-constexpr int TC_THREADS = 192;            // + warp 4: K/V loader, warp 5: tensor-core issuer
+constexpr int TC_THREADS = 224;            // + warp 4: Q/K loader, warp 5: V loader, warp 6: tensor-core issuer
 constexpr unsigned TC_QHALF_BYTES = 128u * 128u;           // one 64-column half of the [128 x 128] Q tile
 constexpr unsigned TC_Q_BYTES = 2u * TC_QHALF_BYTES;       // 32 KB
-constexpr unsigned TC_KHALF_BYTES = (unsigned)TC_KT * 128u;  // one 64-column half of a [64 keys x 128] K or V tile
-constexpr unsigned TC_KV_BYTES = 2u * TC_KHALF_BYTES;      // 16 KB
-constexpr unsigned TC_P_BYTES = 128u * 128u;               // P: [128 rows x 64 keys] = one half, 16 KB
-constexpr unsigned TC_SMEM_BYTES = TC_Q_BYTES + 4u * TC_KV_BYTES + TC_P_BYTES;    // 112 KB: two blocks per SM
+constexpr unsigned TC_KHALF_BYTES = (unsigned)TC_KT * 128u;  // one 64-column half of a [128 keys x 128] K or V tile
+constexpr unsigned TC_KV_BYTES = 2u * TC_KHALF_BYTES;      // 32 KB
+constexpr unsigned TC_SMEM_BYTES = TC_Q_BYTES + 2u * TC_KV_BYTES;    // 96 KB: two blocks per SM
+constexpr float TC_LAZY = 16.f;      // the exponent's reference follows the running maximum only past this many powers of two
 constexpr long long TC_SPIN_LIMIT = 4000000LL;             // polls of an mbarrier before a block gives up (a fraction of a second)
 
 __device__ __forceinline__ void tc_mbar_init(unsigned bar, unsigned count) {
@@ -57,6 +73,14 @@ __device__ __forceinline__ void tc_mbar_arrive(unsigned bar) {
 // arrives on `bar` when all cp.async copies this thread has issued so far have landed
 __device__ __forceinline__ void tc_cp_async_arrive(unsigned bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// one TMA copy of a [rows x 64] box (128 bytes a row, 128-byte swizzle) at column x, row y of a 2-d tensor
+__device__ __forceinline__ void tc_tma_load(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void tc_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
@@ -91,23 +115,28 @@ __device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_des
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the A operand in tensor memory (128 lanes x 8 columns: 16 bfloat16 per row)
+__device__ __forceinline__ void tc_mma_ta(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tc_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
-    unsigned r[32];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]), "=f"(v[16]), "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]), "=f"(v[24]), "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
                  : "r"(taddr) : "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-// the registers of tc_ld32 hold their values only after this
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+// The registers of a tc_ld32 hold their values only after this.  The values pass through the statement, so that
+// the compiler keeps every use of them behind the wait.
+__device__ __forceinline__ void tc_wait_ld(float (&v)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
+                 : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]), "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15]), "+f"(v[16]), "+f"(v[17]), "+f"(v[18]), "+f"(v[19]), "+f"(v[20]), "+f"(v[21]), "+f"(v[22]), "+f"(v[23]), "+f"(v[24]), "+f"(v[25]), "+f"(v[26]), "+f"(v[27]), "+f"(v[28]), "+f"(v[29]), "+f"(v[30]), "+f"(v[31])
+                 :: "memory");
+}
 __device__ __forceinline__ void tc_st32(unsigned taddr, const float (&v)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
                  "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};\n"
@@ -121,6 +150,24 @@ __device__ __forceinline__ void tc_st32(unsigned taddr, const float (&v)[32]) {
                    "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31])),
                    "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_ld16(unsigned taddr, unsigned (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld16(unsigned (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                   "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :: "memory");
+}
+__device__ __forceinline__ void tc_st16(unsigned taddr, const unsigned (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};\n"
+                 ::"r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                   "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 // byte offset of (row, 16-byte chunk c) inside a swizzled tile whose 64-column halves are `half_bytes` apart
@@ -128,10 +175,12 @@ __device__ __forceinline__ unsigned tc_tile_off(int row, int c, unsigned half_by
     return (unsigned)(c >> 3) * half_bytes + (unsigned)row * 128u + (unsigned)(((c & 7) ^ (row & 7)) << 4);
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams p, int* status) {
-    // No static shared memory: two blocks have to fit an SM, and every byte of its 228 KB counts.  The first 256
-    // bytes of the dynamic allocation hold the barriers and scalars, the operand tiles start at the next
-    // 1024-byte boundary: Q | K0 | K1 | V0 | V1 | P.
+// tma_box: rows of one TMA box (min(page_size, 128)) or 0 for the cp.async gathers
+__global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams p, int* status,
+                                                                const __grid_constant__ CUtensorMap kmap,
+                                                                const __grid_constant__ CUtensorMap vmap, int tma_box) {
+    // No static shared memory: two blocks have to fit an SM.  The first 256 bytes of the dynamic allocation
+    // hold the barriers and scalars, the operand tiles start at the next 1024-byte boundary: Q | K | V.
     extern __shared__ __align__(16) unsigned char tc_smem[];
     unsigned& tmem_base_s = *reinterpret_cast<unsigned*>(tc_smem + 128);
     int* sh_tile = reinterpret_cast<int*>(tc_smem + 144);
@@ -142,18 +191,17 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
         if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 2);
         return;
     }
-    const unsigned q_s = smem0, k_s = q_s + TC_Q_BYTES, v_s = k_s + 2 * TC_KV_BYTES, p_s = v_s + 2 * TC_KV_BYTES;
-    // mbarriers (8 bytes each)
-    const unsigned bar_s0 = smem_base, bar_s1 = smem_base + 8;            // scores of a tile are in TMEM (tensor core commits)
-    const unsigned bar_o = smem_base + 16;                                  // a P V product is done (tensor core commits)
-    const unsigned bar_kf0 = smem_base + 24, bar_kf1 = smem_base + 32;      // K stage holds a tile (32 loader lanes)
-    const unsigned bar_vf0 = smem_base + 40, bar_vf1 = smem_base + 48;      // V stage holds a tile
-    const unsigned bar_sf0 = smem_base + 56, bar_sf1 = smem_base + 64;      // S buffer has been read (128 softmax threads)
-    const unsigned bar_pf = smem_base + 72;                                 // P is in shared memory, O rescaled (128 threads)
-    // A stage's "free" barrier is separate from bar_s / bar_o although the same tensor-core work completes it: a
-    // waiter must never fall two phases behind a barrier, and the loader could, behind bar_o.
-    const unsigned bar_kr0 = smem_base + 80, bar_kr1 = smem_base + 88;      // K stage may be overwritten
-    const unsigned bar_vr0 = smem_base + 96, bar_vr1 = smem_base + 104;     // V stage may be overwritten
+    const unsigned q_s = smem0, k_s = q_s + TC_Q_BYTES, v_s = k_s + TC_KV_BYTES;
+    // mbarriers (8 bytes each); tile i completes phase i of each, so its parity is i & 1
+    const unsigned bar_s = smem_base;              // S(i) is in TMEM (tensor core commits)
+    const unsigned bar_o = smem_base + 8;          // P V(i) is done: O holds tiles 0..i, P may be overwritten (tensor core commits)
+    const unsigned bar_p = smem_base + 16;         // P(i) is in TMEM and O is rescaled (128 softmax threads)
+    const unsigned bar_kf = smem_base + 24;        // the K stage holds tile i (32 loader lanes; tile 0: Q too)
+    const unsigned bar_vf = smem_base + 32;        // the V stage holds tile i (32 loader lanes)
+    const unsigned bar_kr = smem_base + 40;        // S(i) has read the K stage (tensor core commits)
+    const unsigned bar_vr = smem_base + 48;        // P V(i) has read the V stage (tensor core commits)
+    const unsigned bar_q = smem_base + 56;         // Q is in shared memory (all threads)
+    const unsigned bar_vt = smem_base + 64;        // TMA copies of a V tile whose tail rows are zeroed afterwards
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const int G = p.n_q / p.n_kv;
@@ -173,14 +221,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
     const int n_tiles = kt_end - kt_begin;
 
     if (tid == 0) {
-        tc_mbar_init(bar_s0, 1); tc_mbar_init(bar_s1, 1); tc_mbar_init(bar_o, 1);
-        tc_mbar_init(bar_kf0, 32); tc_mbar_init(bar_kf1, 32); tc_mbar_init(bar_vf0, 32); tc_mbar_init(bar_vf1, 32);
-        tc_mbar_init(bar_sf0, TC_SOFTMAX_THREADS); tc_mbar_init(bar_sf1, TC_SOFTMAX_THREADS);
-        tc_mbar_init(bar_pf, TC_SOFTMAX_THREADS);
-        tc_mbar_init(bar_kr0, 1); tc_mbar_init(bar_kr1, 1); tc_mbar_init(bar_vr0, 1); tc_mbar_init(bar_vr1, 1);
+        tc_mbar_init(bar_s, 1); tc_mbar_init(bar_o, 1); tc_mbar_init(bar_p, TC_SOFTMAX_THREADS);
+        tc_mbar_init(bar_kf, 32); tc_mbar_init(bar_vf, 32); tc_mbar_init(bar_kr, 1); tc_mbar_init(bar_vr, 1);
+        tc_mbar_init(bar_q, TC_THREADS); tc_mbar_init(bar_vt, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 0) {   // 256 columns of tensor memory: S0 (64) | S1 (64) | O (128); two blocks share an SM's 512
+    if (warp == 0) {   // 256 columns of tensor memory: S / P (128) | O (128); two blocks share an SM's 512
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;\n" ::"r"(smem_u32(&tmem_base_s)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
@@ -188,79 +234,125 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = tmem_base_s;
-    const unsigned t_s0 = tmem, t_s1 = tmem + 64, t_o = tmem + 128;
+    const unsigned t_s = tmem, t_o = tmem + 128;
     int fail = 0;
 
-    if (warp == 4) {
-        // =========================== loader: Q once, then K(j), V(j) two tiles ahead of their use
+    {   // Q: 128 rows x 16 chunks of 16 bytes, spread over all threads; rows without a query are zero-filled
         const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(p.q);
-        const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(p.k_cache);
-        const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(p.v_cache);
-        const int* bt = p.block_table + (size_t)ti.req * p.bt_stride;
-#pragma unroll 1
-        for (int rr = 0; rr < 4; ++rr) {                                 // Q: 128 rows, 4 per lane
-            const int r = rr * 32 + lane;
+        for (int idx = tid; idx < TC_ROWS * 16; idx += TC_THREADS) {
+            const int r = idx >> 4, c = idx & 15;
             const int tl = r / Gc, hl = r - tl * Gc, hg = chunk * TC_ROWS + hl;
             const bool valid = tl < ti.n_tok && tl < QT && hg < G;
             const __nv_bfloat16* src = qg + ((size_t)(ti.q_base + ti.t0 + (valid ? tl : 0)) * p.n_q + (size_t)kvh * G + (valid ? hg : 0)) * TC_D;
-#pragma unroll
-            for (int c = 0; c < 16; ++c) cp_async16_u32(q_s + tc_tile_off(r, c, TC_QHALF_BYTES), src + c * 8, valid);
+            cp_async16_u32(q_s + tc_tile_off(r, c, TC_QHALF_BYTES), src + c * 8, valid);
         }
-        auto row_page = [&](int kt, int row) -> int {
-            const int key = kt * TC_KT + row;
-            return (kt < kt_end && key <= p_max) ? bt[page_index(p, key)] : -1;
-        };
-        auto load_tile = [&](unsigned dst_tile, const __nv_bfloat16* cache, int kt, int pg0, int pg1) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {                                // 64 rows, 2 per lane
-                const int row = h * 32 + lane;
-                const int pg = h ? pg1 : pg0;
-                const int key = kt * TC_KT + row;
-                const bool valid = pg >= 0;
-                size_t off = 0;
-                if (valid) off = (((size_t)pg * p.n_kv + kvh) * p.page_size + page_slot(p, key)) * TC_D;
-#pragma unroll
-                for (int c = 0; c < 16; ++c) cp_async16_u32(dst_tile + tc_tile_off(row, c, TC_KHALF_BYTES), cache + off + c * 8, valid);
+        tc_cp_async_arrive(bar_q);
+    }
+
+    if (warp == 4 || warp == 5) {
+        // =========================== loaders: warp 4 brings Q once and the K tiles, warp 5 the V tiles
+        const bool is_k = warp == 4;
+        const __nv_bfloat16* cache = reinterpret_cast<const __nv_bfloat16*>(is_k ? p.k_cache : p.v_cache);
+        const unsigned dst_tile = is_k ? k_s : v_s;
+        const unsigned bar_full = is_k ? bar_kf : bar_vf, bar_free = is_k ? bar_kr : bar_vr;
+        const int* bt = p.block_table + (size_t)ti.req * p.bt_stride;
+#ifdef MSGL_TC_PROFILE
+        long long lp[2] = {0, 0};
+        long long l0 = clock64(), l1;
+#define TC_LMARK(i) { l1 = clock64(); lp[i] += l1 - l0; l0 = l1; }
+#else
+#define TC_LMARK(i)
+#endif
+        if (tma_box > 0) {
+            // ---- TMA: lane b brings box b (tma_box rows, both 64-column halves) of the tile
+            const CUtensorMap* map = is_k ? &kmap : &vmap;
+            const int n_box = TC_KT / tma_box;
+            unsigned vt_phase = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int key0 = (kt_begin + j) * TC_KT;
+                const int key_b = key0 + lane * tma_box;
+                const bool active = lane < n_box && key_b <= p_max;      // boxes past the last visible key are not fetched
+                int y = 0;
+                if (active) y = (bt[page_index(p, key_b)] * p.n_kv + kvh) * p.page_size + page_slot(p, key_b);
+                const unsigned n_act = __popc(__ballot_sync(0xffffffffu, active));
+                const bool ragged = !is_k && p_max < key0 + TC_KT - 1;   // V rows past p_max have to be zero
+                if (j >= 1 && !tc_mbar_wait(bar_free, (j - 1) & 1)) { fail = 1; break; }    // the tensor core has read tile j-1
+                TC_LMARK(0)
+                const unsigned bar = ragged ? bar_vt : bar_full;
+                if (lane == 0) tc_mbar_expect_tx(bar, n_act * 2u * (unsigned)tma_box * 128u);
+                else if (!ragged) tc_mbar_arrive(bar_full);
+                if (active) {
+                    const unsigned dst = dst_tile + (unsigned)(lane * tma_box) * 128u;
+                    tc_tma_load(dst, map, 0, y, bar);
+                    tc_tma_load(dst + TC_KHALF_BYTES, map, 64, y, bar);
+                }
+                if (ragged) {
+                    if (!tc_mbar_wait(bar_vt, vt_phase)) { fail = 1; break; }
+                    vt_phase ^= 1u;
+                    const int r0 = p_max + 1 - key0;                     // first row without a visible key
+                    for (int idx = r0 * 16 + lane; idx < TC_KT * 16; idx += 32) {
+                        const unsigned a = dst_tile + (unsigned)((idx >> 3) & 1) * TC_KHALF_BYTES + (unsigned)(idx >> 4) * 128u + (unsigned)(idx & 7) * 16u;
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(a), "r"(0u) : "memory");
+                    }
+                    tc_fence_async_smem();
+                    tc_mbar_arrive(bar_full);
+                }
+                TC_LMARK(1)
             }
-        };
-        int pg0 = row_page(kt_begin, lane), pg1 = row_page(kt_begin, 32 + lane);
-        for (int j = 0; j < n_tiles; ++j) {
-            const int kt = kt_begin + j, st = j & 1;
-            const int npg0 = row_page(kt + 1, lane), npg1 = row_page(kt + 1, 32 + lane);     // next tile's pages, ahead of need
-            if (j >= 2 && !tc_mbar_wait(st ? bar_kr1 : bar_kr0, ((j - 2) >> 1) & 1)) { fail = 1; break; }   // S(j-2) has read this K stage
-            load_tile(k_s + (unsigned)st * TC_KV_BYTES, kc, kt, pg0, pg1);
-            tc_cp_async_arrive(st ? bar_kf1 : bar_kf0);                   // (for j == 0 this also covers Q)
-            if (j >= 2 && !tc_mbar_wait(st ? bar_vr1 : bar_vr0, ((j - 2) >> 1) & 1)) { fail = 1; break; }   // P V(j-2) has read this V stage
-            load_tile(v_s + (unsigned)st * TC_KV_BYTES, vc, kt, pg0, pg1);
-            tc_cp_async_arrive(st ? bar_vf1 : bar_vf0);
-            pg0 = npg0; pg1 = npg1;
+        } else {
+            // ---- cp.async: lane l gathers rows l, l + 32, l + 64, l + 96 of the tile, sixteen 16-byte chunks each
+            auto row_page = [&](int kt, int row) -> int {
+                const int key = kt * TC_KT + row;
+                return (kt < kt_end && key <= p_max) ? bt[page_index(p, key)] : -1;
+            };
+            int pg[4], npg[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) pg[h] = row_page(kt_begin, h * 32 + lane);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int kt = kt_begin + j;
+#pragma unroll
+                for (int h = 0; h < 4; ++h) npg[h] = row_page(kt + 1, h * 32 + lane);   // next tile's pages, ahead of need
+                if (j >= 1 && !tc_mbar_wait(bar_free, (j - 1) & 1)) { fail = 1; break; }
+                TC_LMARK(0)
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const int row = h * 32 + lane;
+                    const bool valid = pg[h] >= 0;                       // rows past the end are zero-filled
+                    size_t off = 0;
+                    if (valid) off = (((size_t)pg[h] * p.n_kv + kvh) * p.page_size + page_slot(p, kt * TC_KT + row)) * TC_D;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) cp_async16_u32(dst_tile + tc_tile_off(row, c, TC_KHALF_BYTES), cache + off + c * 8, valid);
+                }
+                tc_cp_async_arrive(bar_full);
+#pragma unroll
+                for (int h = 0; h < 4; ++h) pg[h] = npg[h];
+                TC_LMARK(1)
+            }
         }
+#ifdef MSGL_TC_PROFILE
+        if (status != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && is_k) {
+            long long* out_p = reinterpret_cast<long long*>(status) + 30;
+            out_p[0] = lp[0]; out_p[1] = lp[1];
+        }
+#endif
         cp_async_commit();
         cp_async_wait<0>();
-    } else if (warp == 5) {
+    } else if (warp == 6) {
         // =========================== issuer: one lane feeds the tensor core
         if (lane == 0 && n_tiles > 0) {
             const unsigned idesc_s = tc_idesc(false, TC_KT), idesc_o = tc_idesc(true, TC_D);
-            auto issue_s = [&](int j) {                                   // S(j) = Q K(j)^T: 8 steps of 16 along the head size
-                const unsigned kb = k_s + (unsigned)(j & 1) * TC_KV_BYTES;
+            // Every operand has one place for the whole block, so the descriptors are built once: a single thread
+            // building them between the products would take longer than the products themselves.
+            unsigned long long dq[8], dk[8], dv[8];
+            unsigned tp_[8];
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const unsigned qo = (unsigned)(kk >> 2) * TC_QHALF_BYTES + (unsigned)(kk & 3) * 32u;
-                    const unsigned ko = (unsigned)(kk >> 2) * TC_KHALF_BYTES + (unsigned)(kk & 3) * 32u;
-                    tc_mma((j & 1) ? t_s1 : t_s0, tc_desc(q_s + qo, 16, 1024), tc_desc(kb + ko, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-                }
-                tc_commit((j & 1) ? bar_s1 : bar_s0);
-                tc_commit((j & 1) ? bar_kr1 : bar_kr0);
-            };
-            auto issue_o = [&](int j) {                                   // O += P V(j): 4 steps of 16 keys; V as stored (MN-major)
-                const unsigned vb = v_s + (unsigned)(j & 1) * TC_KV_BYTES;
-#pragma unroll
-                for (int kk = 0; kk < TC_KT / 16; ++kk)
-                    tc_mma(t_o, tc_desc(p_s + (unsigned)kk * 32u, 16, 1024), tc_desc(vb + (unsigned)kk * 2048u, TC_KHALF_BYTES, 1024),
-                           idesc_o, (j == 0 && kk == 0) ? 0u : 1u);
-                tc_commit(bar_o);
-                tc_commit((j & 1) ? bar_vr1 : bar_vr0);
-            };
+            for (int kk = 0; kk < 8; ++kk) {
+                dq[kk] = tc_desc(q_s + (unsigned)(kk >> 2) * TC_QHALF_BYTES + (unsigned)(kk & 3) * 32u, 16, 1024);
+                dk[kk] = tc_desc(k_s + (unsigned)(kk >> 2) * TC_KHALF_BYTES + (unsigned)(kk & 3) * 32u, 16, 1024);
+                dv[kk] = tc_desc(v_s + (unsigned)kk * 2048u, TC_KHALF_BYTES, 1024);
+                tp_[kk] = t_s + (unsigned)kk * 8u;
+            }
+            bool ok = true;
 #ifdef MSGL_TC_PROFILE
             long long ip[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             long long i0 = clock64(), i1;
@@ -268,29 +360,31 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
 #else
 #define TC_IMARK(i)
 #endif
-            bool ok = tc_mbar_wait(bar_kf0, 0);
-            if (ok) { tc_fence_async_smem(); tc_fence_after(); issue_s(0); }
-            TC_IMARK(7)
+            ok = tc_mbar_wait(bar_q, 0);
             for (int it = 0; it < n_tiles && ok; ++it) {
-                if (it + 1 < n_tiles) {                                   // the next tile's scores run under this tile's softmax
-                    const int j = it + 1;
-                    ok = tc_mbar_wait((j & 1) ? bar_kf1 : bar_kf0, (j >> 1) & 1);
-                    TC_IMARK(0)
-                    if (ok && j >= 2) ok = tc_mbar_wait((j & 1) ? bar_sf1 : bar_sf0, ((j - 2) >> 1) & 1);   // S buffer read by softmax(j-2)
-                    if (!ok) break;
-                    TC_IMARK(1)
-                    tc_fence_async_smem(); tc_fence_after();
-                    issue_s(j);
-                    TC_IMARK(2)
-                }
-                ok = tc_mbar_wait(bar_pf, it & 1);
-                TC_IMARK(3)
-                ok = ok && tc_mbar_wait((it & 1) ? bar_vf1 : bar_vf0, (it >> 1) & 1);
+                ok = tc_mbar_wait(bar_kf, it & 1);
                 if (!ok) break;
-                TC_IMARK(4)
+                TC_IMARK(0)
                 tc_fence_async_smem(); tc_fence_after();
-                issue_o(it);
-                TC_IMARK(5)
+                // S(it) = Q K(it)^T: 8 steps of 16 along the head size.  The tensor core works in order, so these run
+                // after P V(it-1), which reads P from the columns that S(it) overwrites.
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) tc_mma(t_s, dq[kk], dk[kk], idesc_s, kk > 0 ? 1u : 0u);
+                tc_commit(bar_s);
+                tc_commit(bar_kr);
+                TC_IMARK(1)
+                ok = tc_mbar_wait(bar_p, it & 1);
+                TC_IMARK(2)
+                ok = ok && tc_mbar_wait(bar_vf, it & 1);
+                if (!ok) break;
+                TC_IMARK(3)
+                tc_fence_async_smem(); tc_fence_after();
+                // O += P V(it): 8 steps of 16 keys; P from tensor memory (8 columns a step), V as stored (MN-major)
+#pragma unroll
+                for (int kk = 0; kk < TC_KT / 16; ++kk) tc_mma_ta(t_o, tp_[kk], dv[kk], idesc_o, (it == 0 && kk == 0) ? 0u : 1u);
+                tc_commit(bar_o);
+                tc_commit(bar_vr);
+                TC_IMARK(4)
             }
             if (!ok) fail = 1;
 #ifdef MSGL_TC_PROFILE
@@ -316,95 +410,98 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
 #define TC_MARK(i)
 #endif
         for (int it = 0; it < n_tiles; ++it) {
-            const int buf = it & 1;
-            if (!tc_mbar_wait(buf ? bar_s1 : bar_s0, (it >> 1) & 1)) { fail = 1; break; }
+            if (!tc_mbar_wait(bar_s, it & 1)) { fail = 1; break; }
             tc_fence_after();
             TC_MARK(0)
-            const unsigned ts = (buf ? t_s1 : t_s0) + lane_sel;
-            float sv[2][32];
-            tc_ld32(ts, sv[0]);
-            tc_ld32(ts + 32, sv[1]);
-            tc_wait_ld();
-            tc_fence_before();
-            tc_mbar_arrive(buf ? bar_sf1 : bar_sf0);                      // the buffer may take the scores of tile it+2
-            TC_MARK(1)
+            const unsigned ts = t_s + lane_sel;
             const int key0 = (kt_begin + it) * TC_KT;
             const bool need_mask = (key0 + TC_KT - 1 > p_min) || (p.window > 0 && key0 <= p_max - p.window);
-            if (need_mask) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
+            // ---- one pass over S in chunks of 32 columns (the next chunk is on its way while this one is worked on):
+            // P = 2^(s*scale - m) against the reference m of the row, which follows the running maximum only when a
+            // chunk exceeds it by more than 2^TC_LAZY.  P and the sums then stay far inside the range of bfloat16 and
+            // float32, the result is the same softmax, and neither a pass for the maximum nor, after the first
+            // chunks, a rescaling is needed.  When the reference does move, the row's sum, its part of O (at the end of
+            // the tile) and the chunks of P already written for this tile are scaled by 2^(m_old - m_new).
+            float o_scale = 1.f;
+            float sa[32], sb[32];
+            auto chunk = [&](float (&sv)[32], int cb) {
+                if (need_mask) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int key = key0 + h * 32 + j;
+                        const int key = key0 + cb * 32 + j;
                         bool okk = key <= my_pos;
                         if (p.window > 0) okk = okk && (key > my_pos - p.window);
-                        if (!okk) sv[h][j] = -INFINITY;
+                        if (!okk) sv[j] = -INFINITY;
                     }
-            }
-            float mx8[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) mx8[j] = -INFINITY;               // eight chains: the maximum is not one long dependency
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int j = 0; j < 32; ++j) mx8[j & 7] = fmaxf(mx8[j & 7], sv[h][j]);
-            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-            // The exponent's reference only follows the running maximum when that has grown by more than 2^8: P then
-            // stays below 256 (no trouble for bfloat16 or the float32 sums), the result is the same softmax, and O is
-            // rescaled a handful of times per row instead of once per tile.
-            const float m_new = fmaxf(m_run, mx * sc);
-            const float m_use = (m_new > m_run + 8.f) ? m_new : m_run;
-            const float mu = (m_use == -INFINITY) ? 0.f : m_use;
-            const float alpha = fast_exp2(m_run - mu);
-            m_run = m_use;
-            float sum8[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) sum8[j] = 0.f;
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    sv[h][j] = fast_exp2(fmaf(sv[h][j], sc, -mu));
-                    sum8[j & 7] += sv[h][j];
                 }
-            l_run = l_run * alpha + (((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7])));
-            TC_MARK(2)
-            // the previous tile's P V product is done: P and O may be touched
-            if (it >= 1) {
-                if (!tc_mbar_wait(bar_o, (it - 1) & 1)) { fail = 1; break; }
-                tc_fence_after();
-            }
-            TC_MARK(3)
-            // P -> shared memory (bfloat16, swizzled, K-major over the keys): 8 chunks of 8 keys
+                float c4[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+                for (int j = 4; j < 32; ++j) c4[j & 3] = fmaxf(c4[j & 3], sv[j]);
+                const float cm = fmaxf(fmaxf(c4[0], c4[1]), fmaxf(c4[2], c4[3])) * sc;
+                const bool bump = cm > m_run + TC_LAZY;                  // also the first finite chunk of a row (m_run = -inf)
+                if (__any_sync(0xffffffffu, bump)) {                     // TMEM accesses are warp-wide: all lanes go along
+                    const float a = bump ? fast_exp2(m_run - cm) : 1.f;  // 0 for the first chunk
+                    if (bump) m_run = cm;
+                    l_run *= a;
+                    o_scale *= a;
+                    if (cb > 0) {
+                        tc_wait_st();
+#pragma unroll 1
+                        for (int pc = 0; pc < cb; ++pc) {
+                            unsigned pk[16];
+                            tc_ld16(ts + pc * 16, pk);
+                            tc_wait_ld16(pk);
 #pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    const unsigned dst = p_s + tc_tile_off(tid, h * 4 + c4, TC_P_BYTES);
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst),
-                                 "r"(pack_bf16(sv[h][c4 * 8 + 0], sv[h][c4 * 8 + 1])), "r"(pack_bf16(sv[h][c4 * 8 + 2], sv[h][c4 * 8 + 3])),
-                                 "r"(pack_bf16(sv[h][c4 * 8 + 4], sv[h][c4 * 8 + 5])), "r"(pack_bf16(sv[h][c4 * 8 + 6], sv[h][c4 * 8 + 7])) : "memory");
+                            for (int j = 0; j < 16; ++j)
+                                pk[j] = pack_bf16(__uint_as_float(pk[j] << 16) * a, __uint_as_float(pk[j] & 0xffff0000u) * a);
+                            tc_st16(ts + pc * 16, pk);
+                        }
+                    }
                 }
-            // rescale O where a reference maximum moved.  A warp owns its 32 rows (TMEM lanes), so it decides alone.
-            if (it >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                const float mu = (m_run == -INFINITY) ? 0.f : m_run;
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+                unsigned pk[16];
 #pragma unroll
-                for (int cb = 0; cb < 4; cb += 2) {
-                    float v0[32], v1[32];
+                for (int j = 0; j < 32; j += 2) {
+                    const float e0 = fast_exp2(fmaf(sv[j], sc, -mu)), e1 = fast_exp2(fmaf(sv[j + 1], sc, -mu));
+                    sum4[(j >> 1) & 3] += e0 + e1;
+                    pk[j >> 1] = pack_bf16(e0, e1);
+                }
+                l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                tc_st16(ts + cb * 16, pk);             // columns [16 cb, 16 cb + 16): S columns below 32 (cb + 1) are consumed
+            };
+            tc_ld32(ts, sa);
+            tc_wait_ld(sa);
+            tc_ld32(ts + 32, sb);
+            chunk(sa, 0);
+            tc_wait_ld(sb);
+            tc_ld32(ts + 64, sa);
+            chunk(sb, 1);                              // writes columns 16..31: chunk 1 is in registers, chunk 2 (64..95) on its way
+            tc_wait_ld(sa);
+            tc_ld32(ts + 96, sb);
+            chunk(sa, 2);
+            tc_wait_ld(sb);
+            chunk(sb, 3);
+            TC_MARK(1)
+            // ---- O of the tiles before: rescale where a reference moved.  A warp owns its 32 rows (TMEM lanes), so
+            // it decides alone.  (P V(it-1) is done: S(it) came after it.)
+            if (it >= 1 && __any_sync(0xffffffffu, o_scale != 1.f)) {
+#pragma unroll 1
+                for (int cb = 0; cb < 4; ++cb) {
+                    float v0[32];
                     tc_ld32(t_o + lane_sel + cb * 32, v0);
-                    tc_ld32(t_o + lane_sel + cb * 32 + 32, v1);
-                    tc_wait_ld();
+                    tc_wait_ld(v0);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) { v0[j] *= alpha; v1[j] *= alpha; }
+                    for (int j = 0; j < 32; ++j) v0[j] *= o_scale;
                     tc_st32(t_o + lane_sel + cb * 32, v0);
-                    tc_st32(t_o + lane_sel + cb * 32 + 32, v1);
                 }
-                tc_wait_st();
             }
-            TC_MARK(4)
-            tc_fence_async_smem();                                        // P: generic-proxy writes -> visible to the tensor core
+            TC_MARK(2)
+            TC_MARK(3)
+            tc_wait_st();
             tc_fence_before();
-            tc_mbar_arrive(bar_pf);
-            TC_MARK(5)
+            tc_mbar_arrive(bar_p);
+            TC_MARK(4)
         }
 #ifdef MSGL_TC_PROFILE
         if (status != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (tid == 0 || tid == 37)) {
@@ -423,11 +520,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
             const int hl = tid - my_tl * Gc;
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) +
                                  ((size_t)(ti.q_base + ti.t0 + (my_valid ? my_tl : 0)) * p.n_q + (size_t)kvh * G + (my_valid ? chunk * TC_ROWS + hl : 0)) * TC_D;
-#pragma unroll
+#pragma unroll 1
             for (int cb = 0; cb < 4; ++cb) {
                 float v[32];
                 tc_ld32(t_o + lane_sel + cb * 32, v);                    // every thread of the warp takes part
-                tc_wait_ld();
+                tc_wait_ld(v);
                 if (my_valid) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {

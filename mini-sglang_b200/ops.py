@@ -96,7 +96,7 @@ def _attn_lib(head_dim: int):
         lib = _build.attention_library(hd)
         lib.msgl_attention.argtypes = [c_void_p] * 10 + [c_int] * 9 + [c_float] + [c_int] * 6 + [c_void_p]
         lib.msgl_attention_combine.argtypes = [c_void_p] * 5 + [c_int] * 5 + [c_void_p]
-        lib.msgl_attention_tc.argtypes = [c_void_p] * 7 + [c_int] * 8 + [c_float] + [c_int] * 3 + [c_void_p, c_void_p]
+        lib.msgl_attention_tc.argtypes = [c_void_p] * 7 + [c_int] * 8 + [c_float] + [c_int] * 4 + [c_void_p, c_void_p]
         lib.msgl_attention_head_dim.restype = c_int
         _attn[hd] = lib
     return lib
@@ -291,7 +291,9 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_ca
     status = _status_tensor(q.device)
     code = _attn_lib(d).msgl_attention_tc(
         _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), B, T, n_q, n_kv,
-        d, page_size, block_table.stride(0), window, float(scale), qlen_min, qlen_max, grid_x, _ptr(status), _stream())
+        d, page_size, block_table.stride(0), window, float(scale), qlen_min, qlen_max, grid_x,
+        k_cache.shape[0] if (k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape == v_cache.shape) else 0,
+        _ptr(status), _stream())
     _check(code, "attention_tc")
 
 
