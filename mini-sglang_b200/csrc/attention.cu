@@ -1190,6 +1190,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
 
 #if MSGL_HEAD_DIM == 128
 #include "attention_tc.cuh"
+#include "attention_tc2.cuh"
 #endif
 
 // ---------------------------------------------------------------------------------------
@@ -1360,10 +1361,13 @@ static const CUtensorMap* tc_cache_map(const void* base, long long rows, int box
 // tcgen05 prefill attention (head size 128, bfloat16): the requests with qlen_min <= q_len <= qlen_max, no kv
 // splits.  `status` is a device int the kernel sets to 1 if a block gave up waiting (never expected).
 // cache_pages: pages in the cache arrays (their first dimension), for the tensor maps of the TMA path.
+// version 1: 128 query rows per block, two blocks per SM, any page size; version 2: 256 rows per block in
+// ping-pong, TMA page sizes only (MSGL_ERR_SIZE otherwise: the caller then uses version 1).  grid_x counts
+// tiles of 128 / group (version 1) or 256 / group (version 2) tokens.
 MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, const void* v_cache, const int* q_start,
                                const int* kv_len, const int* block_table, int B, int T_, int n_q, int n_kv, int d,
                                int page_size, int bt_stride, int window, float scale, int qlen_min, int qlen_max,
-                               int grid_x, int cache_pages, int* status, cudaStream_t stream) {
+                               int grid_x, int cache_pages, int version, int* status, cudaStream_t stream) {
 #if MSGL_HEAD_DIM == 128
     if (grid_x <= 0 || B <= 0) return MSGL_OK;
     if (d != 128 || n_kv <= 0 || n_q % n_kv != 0 || page_size <= 0) return MSGL_ERR_SIZE;
@@ -1378,11 +1382,12 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
     p.scale = scale; p.qlen_min = qlen_min; p.qlen_max = qlen_max; p.uniform_decode = 0;
     const int G = n_q / n_kv;
     const int n_chunks = G <= TC_ROWS ? 1 : (G + TC_ROWS - 1) / TC_ROWS;
-    size_t smem = (size_t)TC_SMEM_BYTES + 1024;
-    if (getenv("MSGL_TC_ONE_BLOCK")) smem = 120 * 1024;          // experiment: one block per SM
+    const size_t smem = (size_t)TC_SMEM_BYTES + 1024;
     static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (!attr_set) {      // first call, never inside a stream capture
+        if (cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM_ALLOC) != cudaSuccess)
+            return msgl_check_launch();
         attr_set = true;
     }
     // TMA boxes are whole pages (or 128-row pieces of larger ones): page sizes 8, 16, 32, 64, 128, 256, ...; the cache
@@ -1396,6 +1401,11 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
         const CUtensorMap* km = tc_cache_map(k_cache, rows, box);
         const CUtensorMap* vm = tc_cache_map(v_cache, rows, box);
         if (km != nullptr && vm != nullptr) { kmap = *km; vmap = *vm; tma_box = box; }
+    }
+    if (version == 2) {
+        if (tma_box == 0) return MSGL_ERR_SIZE;
+        attn_tc2_kernel<<<dim3(grid_x, n_kv * n_chunks, 1), TC2_THREADS, TC2_SMEM_ALLOC, stream>>>(p, status, kmap, vmap, tma_box);
+        return msgl_check_launch();
     }
     attn_tc_kernel<<<dim3(grid_x, n_kv * n_chunks, 1), TC_THREADS, smem, stream>>>(p, status, kmap, vmap, tma_box);
     return msgl_check_launch();

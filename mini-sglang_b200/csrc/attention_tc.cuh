@@ -195,9 +195,9 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
     // mbarriers (8 bytes each); tile i completes phase i of each, so its parity is i & 1
     const unsigned bar_s = smem_base;              // S(i) is in TMEM (tensor core commits)
     const unsigned bar_o = smem_base + 8;          // P V(i) is done: O holds tiles 0..i, P may be overwritten (tensor core commits)
-    const unsigned bar_p = smem_base + 16;         // P(i) is in TMEM and O is rescaled (128 softmax threads)
-    const unsigned bar_kf = smem_base + 24;        // the K stage holds tile i (32 loader lanes; tile 0: Q too)
-    const unsigned bar_vf = smem_base + 32;        // the V stage holds tile i (32 loader lanes)
+    const unsigned bar_p = smem_base + 16;         // P(i) is in TMEM and O is rescaled (one arrival per softmax warp)
+    const unsigned bar_kf = smem_base + 24;        // the K stage holds tile i (TMA: one arrival + bytes; cp.async: 32 lanes)
+    const unsigned bar_vf = smem_base + 32;        // the V stage holds tile i
     const unsigned bar_kr = smem_base + 40;        // S(i) has read the K stage (tensor core commits)
     const unsigned bar_vr = smem_base + 48;        // P V(i) has read the V stage (tensor core commits)
     const unsigned bar_q = smem_base + 56;         // Q is in shared memory (all threads)
@@ -221,8 +221,9 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
     const int n_tiles = kt_end - kt_begin;
 
     if (tid == 0) {
-        tc_mbar_init(bar_s, 1); tc_mbar_init(bar_o, 1); tc_mbar_init(bar_p, TC_SOFTMAX_THREADS);
-        tc_mbar_init(bar_kf, 32); tc_mbar_init(bar_vf, 32); tc_mbar_init(bar_kr, 1); tc_mbar_init(bar_vr, 1);
+        tc_mbar_init(bar_s, 1); tc_mbar_init(bar_o, 1); tc_mbar_init(bar_p, TC_SOFTMAX_THREADS / 32);
+        tc_mbar_init(bar_kf, tma_box > 0 ? 1 : 32); tc_mbar_init(bar_vf, tma_box > 0 ? 1 : 32);
+        tc_mbar_init(bar_kr, 1); tc_mbar_init(bar_vr, 1);
         tc_mbar_init(bar_q, TC_THREADS); tc_mbar_init(bar_vt, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -280,7 +281,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
                 TC_LMARK(0)
                 const unsigned bar = ragged ? bar_vt : bar_full;
                 if (lane == 0) tc_mbar_expect_tx(bar, n_act * 2u * (unsigned)tma_box * 128u);
-                else if (!ragged) tc_mbar_arrive(bar_full);
                 if (active) {
                     const unsigned dst = dst_tile + (unsigned)(lane * tma_box) * 128u;
                     tc_tma_load(dst, map, 0, y, bar);
@@ -295,7 +295,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
                         asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(a), "r"(0u) : "memory");
                     }
                     tc_fence_async_smem();
-                    tc_mbar_arrive(bar_full);
+                    __syncwarp();
+                    if (lane == 0) tc_mbar_arrive(bar_full);
                 }
                 TC_LMARK(1)
             }
@@ -500,7 +501,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
             TC_MARK(3)
             tc_wait_st();
             tc_fence_before();
-            tc_mbar_arrive(bar_p);
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(bar_p);
             TC_MARK(4)
         }
 #ifdef MSGL_TC_PROFILE

@@ -61,8 +61,8 @@ def build_dir() -> str:
 
 
 # files a source pulls in with #include: an edit of any of them rebuilds the library
-INCLUDED = {"attention.cu": ["attention_tc.cuh"],
-            "attention_noalloc.cu": ["attention.cu", "attention_tc.cuh", "attention_noalloc.h"]}
+INCLUDED = {"attention.cu": ["attention_tc.cuh", "attention_tc2.cuh"],
+            "attention_noalloc.cu": ["attention.cu", "attention_tc.cuh", "attention_tc2.cuh", "attention_noalloc.h"]}
 
 
 def _digest(sources: Sequence[str], flags: Sequence[str]) -> str:

@@ -115,6 +115,10 @@ static inline void msgl_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 blo
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+#include <stdio.h>
 static inline int msgl_check_launch() {
-    return cudaGetLastError() == cudaSuccess ? MSGL_OK : MSGL_ERR_LAUNCH;
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return MSGL_OK;
+    fprintf(stderr, "[mini_sglang_b200] kernel launch failed: %s\n", cudaGetErrorString(e));
+    return MSGL_ERR_LAUNCH;
 }

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -96,7 +96,7 @@ def _attn_lib(head_dim: int):
         lib = _build.attention_library(hd)
         lib.msgl_attention.argtypes = [c_void_p] * 10 + [c_int] * 9 + [c_float] + [c_int] * 6 + [c_void_p]
         lib.msgl_attention_combine.argtypes = [c_void_p] * 5 + [c_int] * 5 + [c_void_p]
-        lib.msgl_attention_tc.argtypes = [c_void_p] * 7 + [c_int] * 8 + [c_float] + [c_int] * 4 + [c_void_p, c_void_p]
+        lib.msgl_attention_tc.argtypes = [c_void_p] * 7 + [c_int] * 8 + [c_float] + [c_int] * 5 + [c_void_p, c_void_p]
         lib.msgl_attention_head_dim.restype = c_int
         _attn[hd] = lib
     return lib
@@ -280,22 +280,39 @@ def check_kernel_status() -> None:
     raise_if_failed(wait=True)
 
 
+TC_VERSION = int(os.environ.get("MSGL_TC_VERSION", "2"))      # 2: two query tiles per block in ping-pong (needs TMA page sizes); 1: one tile
+_tc2_usable = True
+
+
 def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *,
                  q_start: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor, n_kv: int, page_size: int,
-                 window: int, scale: float, qlen_min: int, qlen_max: int, grid_x: int) -> None:
-    """Prefill attention on tcgen05 tensor cores for the requests with q_len in [qlen_min, qlen_max]."""
+                 window: int, scale: float, qlen_min: int, qlen_max: int, q_lens: Sequence[int]) -> None:
+    """Prefill attention on tcgen05 tensor cores for the requests with q_len in [qlen_min, qlen_max];
+    q_lens: the host's copy of every request's number of query tokens (to size the grid)."""
+    global _tc2_usable
     _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table)
     T, n_q, d = q.shape
     B = kv_len.numel()
     assert q.is_contiguous() and out.is_contiguous() and block_table.stride(1) == 1 and q.dtype == torch.bfloat16
     status = _status_tensor(q.device)
-    code = _attn_lib(d).msgl_attention_tc(
-        _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), B, T, n_q, n_kv,
-        d, page_size, block_table.stride(0), window, float(scale), qlen_min, qlen_max, grid_x,
-        k_cache.shape[0] if (k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape == v_cache.shape) else 0,
-        _ptr(status), _stream())
-    _check(code, "attention_tc")
-
+    group = n_q // n_kv
+    whole = k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape == v_cache.shape
+    pages = k_cache.shape[0] if whole else 0
+    tma_pages = whole and page_size >= 8 and (page_size & (page_size - 1)) == 0
+    versions = [2, 1] if (TC_VERSION == 2 and _tc2_usable and tma_pages) else [1]
+    for version in versions:
+        rows = TC_ROWS * version
+        qt = rows // group if group <= TC_ROWS else version
+        grid_x = sum(-(-n // qt) for n in q_lens if qlen_min <= n <= qlen_max)
+        code = _attn_lib(d).msgl_attention_tc(
+            _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), B, T, n_q,
+            n_kv, d, page_size, block_table.stride(0), window, float(scale), qlen_min, qlen_max, grid_x, pages, version,
+            _ptr(status), _stream())
+        if code == 2 and version == 2:        # no tensor maps here (driver without the encoder, unaligned cache): one-tile kernel
+            _tc2_usable = False
+            continue
+        _check(code, "attention_tc")
+        return
 
 
 def attention_tile_tokens(variant: int, group: int, head_dim: int = 128) -> int:

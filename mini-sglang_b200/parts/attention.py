@@ -124,11 +124,9 @@ class PagedAttention(Mixer):
                     ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=qt_dec,
                                   variant=ops.VARIANT_MMA_DECODE, grid_x=n_dec, **common)
                 if n_row and ops.tc_supported(self.d, q.dtype, G):
-                    qt_tc = ops.attention_tile_tokens(ops.VARIANT_TC, G)
-                    n_tc = sum(-(-n // qt_tc) for n in ctx.host_q_lens if n > qt_dec)
                     ops.attention_tc(q, out, cache.k, cache.v, q_start=ctx.q_start, kv_len=ctx.kv_len,
                                      block_table=g.block_table, n_kv=self.n_kv, page_size=cache.page_size, window=window,
-                                     scale=self.scale, qlen_min=qt_dec + 1, qlen_max=big, grid_x=n_tc)
+                                     scale=self.scale, qlen_min=qt_dec + 1, qlen_max=big, q_lens=ctx.host_q_lens)
                 elif n_row:
                     ops.attention(q, out, cache.k, cache.v, qlen_min=qt_dec + 1, qlen_max=big,
                                   variant=ops.VARIANT_MMA_ROWS, grid_x=n_row, **common)
