@@ -74,9 +74,12 @@ struct TileInfo {
 };
 
 // Map blockIdx.x to (request, tile) by walking the per-request tile counts with one warp.
-__device__ __forceinline__ bool find_tile(const AttnParams& p, int tile_tokens, TileInfo& ti, int* sh /* >= 4 ints */) {
+// tile_idx / n_tile_idx: this block's index among the launch's query tiles (default: blockIdx.x of gridDim.x)
+__device__ __forceinline__ bool find_tile(const AttnParams& p, int tile_tokens, TileInfo& ti, int* sh /* >= 4 ints */,
+                                          int tile_idx = -1, int n_tile_idx = 0) {
+    if (tile_idx < 0) { tile_idx = (int)blockIdx.x; n_tile_idx = (int)gridDim.x; }
     if (p.uniform_decode) {
-        const int r = blockIdx.x;
+        const int r = tile_idx;
         if (r >= p.B) return false;
         ti.req = r; ti.t0 = 0; ti.n_tok = 1; ti.q_len = 1; ti.kv_len = p.kv_len[r]; ti.q_base = p.q_start[r];
         return true;
@@ -99,7 +102,7 @@ __device__ __forceinline__ bool find_tile(const AttnParams& p, int tile_tokens, 
             }
             // heaviest tiles first: with a causal mask the last tiles of a request walk the most keys, and
             // blocks are handed out in index order
-            const int target = (int)(gridDim.x - 1 - blockIdx.x) - base;
+            const int target = (n_tile_idx - 1 - tile_idx) - base;
             const unsigned hit = __ballot_sync(0xffffffffu, target < inc);
             if (hit) {
                 const int src = __ffs(hit) - 1;
@@ -1370,7 +1373,7 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
                                int grid_x, int cache_pages, int version, int* status, cudaStream_t stream) {
 #if MSGL_HEAD_DIM == 128
     if (grid_x <= 0 || B <= 0) return MSGL_OK;
-    if (d != 128 || n_kv <= 0 || n_q % n_kv != 0 || page_size <= 0) return MSGL_ERR_SIZE;
+    if (d != 128 || n_kv <= 0 || n_q % n_kv != 0 || page_size <= 0 || grid_x > 65535) return MSGL_ERR_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
     AttnParams p;
     p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len;
@@ -1404,10 +1407,10 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
     }
     if (version == 2) {
         if (tma_box == 0) return MSGL_ERR_SIZE;
-        attn_tc2_kernel<<<dim3(grid_x, n_kv * n_chunks, 1), TC2_THREADS, TC2_SMEM_ALLOC, stream>>>(p, status, kmap, vmap, tma_box);
+        attn_tc2_kernel<<<dim3(n_kv * n_chunks, grid_x, 1), TC2_THREADS, TC2_SMEM_ALLOC, stream>>>(p, status, kmap, vmap, tma_box);
         return msgl_check_launch();
     }
-    attn_tc_kernel<<<dim3(grid_x, n_kv * n_chunks, 1), TC_THREADS, smem, stream>>>(p, status, kmap, vmap, tma_box);
+    attn_tc_kernel<<<dim3(n_kv * n_chunks, grid_x, 1), TC_THREADS, smem, stream>>>(p, status, kmap, vmap, tma_box);
     return msgl_check_launch();
 #else
     return MSGL_ERR_SIZE;

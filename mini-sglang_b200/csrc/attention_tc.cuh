@@ -208,11 +208,13 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const AttnParams
     const int Gc = G <= TC_ROWS ? G : TC_ROWS;
     const int n_chunks = G <= TC_ROWS ? 1 : (G + TC_ROWS - 1) / TC_ROWS;
     const int QT = G <= TC_ROWS ? TC_ROWS / G : 1;
-    const int kvh = blockIdx.y / n_chunks;
-    const int chunk = blockIdx.y - kvh * n_chunks;
+    // The grid is (kv heads, query tiles): blocks are handed out head-first, so all heads of the heaviest tile
+    // start before any lighter tile (with one tile index per blockIdx.x the first heads would take every SM).
+    const int kvh = blockIdx.x / n_chunks;
+    const int chunk = blockIdx.x - kvh * n_chunks;
 
     TileInfo ti;
-    if (!find_tile(p, QT, ti, sh_tile)) return;
+    if (!find_tile(p, QT, ti, sh_tile, (int)blockIdx.y, (int)gridDim.y)) return;
     // key tiles of TC_KT anchored at absolute positions
     const int p_min = ti.kv_len - ti.q_len + ti.t0;
     const int p_max = p_min + ti.n_tok - 1;
