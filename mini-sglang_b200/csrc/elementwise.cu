@@ -363,18 +363,21 @@ template <typename T, int E> struct Pack {
     }
 };
 
+// A warp owns one head of QKR_TOK consecutive tokens: their rows are fetched first, then worked on one after the
+// other, so that several loads are in flight per lane (one token a warp leaves the kernel bound by block turnover).
+constexpr int QKR_TOK = 4;
 template <typename T, int E>
 __global__ void qknorm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, int qkv_stride,
                                                const int* __restrict__ positions, const int* __restrict__ out_loc,
                                                const void* __restrict__ qw, const void* __restrict__ kw, int w_is_f32,
                                                float eps, const float* __restrict__ table, int max_pos,
                                                T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                                               int page_size, int n_q, int n_kv) {
+                                               int page_size, int n_q, int n_kv, int T_) {
     constexpr int d = 32 * E;
     pdl_launch_dependents();
     pdl_wait();
     pdl_after_wait();
-    const int t = blockIdx.x;
+    const int t0 = blockIdx.x * QKR_TOK;
     const int warps = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.y * warps + (threadIdx.x >> 5);
@@ -385,43 +388,56 @@ __global__ void qknorm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, int qk
     const bool writes_cache = (k_cache != nullptr) && (out_loc != nullptr);
     if (!is_q && !writes_cache) return;
 
-    const T* src = qkv + (size_t)t * qkv_stride + (size_t)head * d + lane * E;
-    float v[E];
-    Pack<T, E>::load(src, v);
+    float v[QKR_TOK][E];
+    int pos[QKR_TOK], slot[QKR_TOK];
+#pragma unroll
+    for (int i = 0; i < QKR_TOK; ++i) {
+        const int t = t0 + i < T_ ? t0 + i : T_ - 1;                     // past the end: the last token again, not stored
+        Pack<T, E>::load(qkv + (size_t)t * qkv_stride + (size_t)head * d + lane * E, v[i]);
+        pos[i] = (table != nullptr && (is_q || is_k)) ? positions[t] : 0;
+        slot[i] = is_q ? 0 : out_loc[t];
+    }
     const void* nw = is_q ? qw : (is_k ? kw : nullptr);
+    float w[E];
     if (nw != nullptr) {
-        float ss = 0.f;
 #pragma unroll
-        for (int j = 0; j < E; ++j) ss += v[j] * v[j];
-        ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)d + eps);
-#pragma unroll
-        for (int j = 0; j < E; ++j) v[j] = v[j] * inv * load_weight(nw, lane * E + j, w_is_f32);
+        for (int j = 0; j < E; ++j) w[j] = load_weight(nw, lane * E + j, w_is_f32);
     }
-    if (table != nullptr && (is_q || is_k)) {
-        int pos = positions[t];
-        pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-        const float* cs = table + (size_t)pos * d;
-        const int pi = (lane & 15) * E;               // index of the pair within the half
-        const bool upper = lane >= 16;
 #pragma unroll
-        for (int j = 0; j < E; ++j) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-            const float c = cs[pi + j], sn = cs[d / 2 + pi + j];
-            v[j] = upper ? (other * sn + v[j] * c) : (v[j] * c - other * sn);
+    for (int i = 0; i < QKR_TOK; ++i) {
+        if (t0 + i >= T_) break;
+        if (nw != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < E; ++j) ss += v[i][j] * v[i][j];
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+            for (int j = 0; j < E; ++j) v[i][j] = v[i][j] * inv * w[j];
         }
+        if (table != nullptr && (is_q || is_k)) {
+            const int ps = pos[i] < 0 ? 0 : (pos[i] >= max_pos ? max_pos - 1 : pos[i]);
+            const float* cs = table + (size_t)ps * d;
+            const int pi = (lane & 15) * E;           // index of the pair within the half
+            const bool upper = lane >= 16;
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[i][j], 16);
+                const float c = cs[pi + j], sn = cs[d / 2 + pi + j];
+                v[i][j] = upper ? (other * sn + v[i][j] * c) : (v[i][j] * c - other * sn);
+            }
+        }
+        T* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)(t0 + i) * n_q + head) * d;
+        } else {
+            const int page = slot[i] / page_size, off = slot[i] - page * page_size;
+            const int kvh = is_k ? head - n_q : head - n_q - n_kv;
+            T* base = is_k ? k_cache : v_cache;
+            dst = base + (((size_t)page * n_kv + kvh) * page_size + off) * d;
+        }
+        Pack<T, E>::store(dst + lane * E, v[i]);
     }
-    T* dst;
-    if (is_q) {
-        dst = q_out + ((size_t)t * n_q + head) * d;
-    } else {
-        const int slot = out_loc[t];
-        const int page = slot / page_size, off = slot - page * page_size;
-        const int kvh = is_k ? head - n_q : head - n_q - n_kv;
-        T* base = is_k ? k_cache : v_cache;
-        dst = base + (((size_t)page * n_kv + kvh) * page_size + off) * d;
-    }
-    Pack<T, E>::store(dst + lane * E, v);
 }
 
 MSGL_API int msgl_qknorm_rope_kvwrite(const void* qkv, int qkv_stride, const int* positions, const int* out_loc,
@@ -440,9 +456,9 @@ MSGL_API int msgl_qknorm_rope_kvwrite(const void* qkv, int qkv_stride, const int
     if (aligned && (d == 32 || d == 64 || d == 128 || d == 256) && (table == nullptr || rot == d) &&
         (dtype == MSGL_F32 || dtype == MSGL_BF16)) {
 #define QKR_VEC(TT, EE)                                                                                              \
-    msgl_launch_pdl(qknorm_rope_kvwrite_vec_kernel<TT, EE>, grid, dim3(warps * 32), 0, stream,                       \
+    msgl_launch_pdl(qknorm_rope_kvwrite_vec_kernel<TT, EE>, dim3((T_ + QKR_TOK - 1) / QKR_TOK, grid.y), dim3(warps * 32), 0, stream, \
         (const TT*)qkv, qkv_stride, positions, out_loc, qw, kw, w_is_f32, eps, table, max_pos, (TT*)q_out,           \
-        (TT*)k_cache, (TT*)v_cache, page_size, n_q, n_kv)
+        (TT*)k_cache, (TT*)v_cache, page_size, n_q, n_kv, T_)
         const int E = d / 32;
         if (dtype == MSGL_F32) {
             if (E == 1) QKR_VEC(float, 1); else if (E == 2) QKR_VEC(float, 2); else if (E == 4) QKR_VEC(float, 4); else QKR_VEC(float, 8);
@@ -481,14 +497,11 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
-// 8 bfloat16 per thread when the row width allows it
-__global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, int I8, size_t total8) {
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
-         idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = idx / I8;
-        const int i = (int)(idx - t * I8);
-        uint4 a = gu[t * 2 * I8 + i];
-        uint4 b = gu[t * 2 * I8 + I8 + i];
+// 8 bfloat16 per thread and step when the row width allows it; a block walks one token row, two steps' loads ahead
+__global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, int I8) {
+    const uint4* row = gu + (size_t)blockIdx.x * 2 * I8;
+    uint4* orow = out + (size_t)blockIdx.x * I8;
+    auto act = [](const uint4& a, const uint4& b) -> uint4 {
         const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
         const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
         uint4 o;
@@ -499,8 +512,16 @@ __global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gu, uint4* __rest
             const float2 bf = __bfloat1622float2(bp[k]);
             op[k] = __floats2bfloat162_rn(af.x / (1.f + expf(-af.x)) * bf.x, af.y / (1.f + expf(-af.y)) * bf.y);
         }
-        out[idx] = o;
+        return o;
+    };
+    int i = threadIdx.x;
+    for (; i + (int)blockDim.x < I8; i += 2 * blockDim.x) {
+        const int i2 = i + blockDim.x;
+        const uint4 a0 = row[i], b0 = row[I8 + i], a1 = row[i2], b1 = row[I8 + i2];
+        orow[i] = act(a0, b0);
+        orow[i2] = act(a1, b1);
     }
+    if (i < I8) orow[i] = act(row[i], row[I8 + i]);
 }
 
 MSGL_API int msgl_swiglu(const void* gu, void* out, int T_, int I, int dtype, cudaStream_t stream) {
@@ -509,10 +530,7 @@ MSGL_API int msgl_swiglu(const void* gu, void* out, int T_, int I, int dtype, cu
     const size_t total = (size_t)T_ * I;
     const int threads = 256;
     if (dtype == MSGL_BF16 && (I % 8) == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0) {
-        const size_t total8 = total / 8;
-        size_t blocks = (total8 + threads - 1) / threads;
-        if (blocks > 148 * 16) blocks = 148 * 16;
-        swiglu_bf16x8_kernel<<<(unsigned)blocks, threads, 0, stream>>>((const uint4*)gu, (uint4*)out, I / 8, total8);
+        swiglu_bf16x8_kernel<<<(unsigned)T_, threads, 0, stream>>>((const uint4*)gu, (uint4*)out, I / 8);
         return msgl_check_launch();
     }
     size_t blocks = (total + threads - 1) / threads;
