@@ -339,3 +339,20 @@ def test_attention_far_key_and_page_edges(dtype):
     kv_lens = [17 + 480, 1023, 16 + 16 * 7, 1025]
     out, ref = run_attention_case(dtype, 8, 2, 64, 16, q_lens, kv_lens, seed=11, spike=True)
     torch.testing.assert_close(out, ref.to(dtype).float(), **ATT_TOL[dtype])
+
+
+@pytest.mark.parametrize("version", [1, 2])
+@pytest.mark.parametrize("n_q,n_kv,P,window", [(32, 8, 16, None), (8, 8, 8, None), (16, 1, 64, None), (12, 4, 256, None),
+                                               (32, 8, 4, None), (6, 2, 16, 100), (8, 2, 32, 300)])
+def test_attention_tcgen05_kernels(version, n_q, n_kv, P, window, monkeypatch):
+    """The two tcgen05 prefill kernels (one query tile per block; two in ping-pong) at head size 128: page sizes
+    that TMA fetches and one that it cannot (4: rows gathered, one-tile kernel), groups of 1, 3, 4 and 16 heads,
+    prompts that start at an offset, end inside a key tile or fill only part of a query tile, windows, and a far
+    key that must dominate.  Unwritten cache slots hold NaN."""
+    from mini_sglang_b200 import ops
+    monkeypatch.setattr(ops, "TC_VERSION", version)
+    q_lens = [300, 33, 1, 130, 64, 17]
+    kv_lens = [300, 33 + 700, 90, 130 + 129, 64 + 1024, 17 + 480]
+    out, ref = run_attention_case(torch.bfloat16, n_q, n_kv, 128, P, q_lens, kv_lens, window=window, seed=3 + P, spike=True)
+    ops.check_kernel_status()
+    torch.testing.assert_close(out, ref.to(torch.bfloat16).float(), **ATT_TOL[torch.bfloat16])
