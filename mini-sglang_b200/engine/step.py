@@ -158,7 +158,8 @@ class ModelRunner:
         self._steps_run = 0
         if self.device.type == "cuda":
             ops._status_tensor(self.device)          # allocated now, not inside a stream capture
-        self.use_cuda_graph = use_cuda_graph and all(getattr(l.mixer, "graph_safe", False) for l in self.model.layers)
+        self.use_cuda_graph = use_cuda_graph and all(getattr(l.mixer, "graph_safe", False) and getattr(l.ffn, "graph_safe", True)
+                                                     for l in self.model.layers)
         self.max_capture_bs = max_capture_bs
         self._graphs: Dict[Tuple[int, Tuple[int, ...]], _Graph] = {}
         self._graph_pool = None

@@ -61,6 +61,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    # False if forward() reads device data on the host or launches work whose shapes depend on the
+    # tokens (routing by gathered rows, say): a decode step with such a part is not captured in a CUDA graph.
+    graph_safe = True
+
     def forward(self, x, ctx):
         raise NotImplementedError
 

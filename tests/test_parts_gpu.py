@@ -313,3 +313,169 @@ def test_toy_architecture_with_state_is_registered_built_and_stepped(dtype):
         torch.testing.assert_close(out, ref_b, **TOL[dtype])
     finally:
         ARCHITECTURES.pop("ToyStateLM", None)
+
+
+# ---------------------------------------------------------------------------------------
+# a second toy architecture, again defined entirely in this test: a feed-forward that routes
+# every token to one of three experts, and a rotary position encoding of another kind
+# (frequencies that grow linearly, over the first 8 of 16 head elements only)
+# ---------------------------------------------------------------------------------------
+def _register_routed_toy():
+    from mini_sglang_b200.config import LayerSpec, ModelSpec, PartSpec, Run, register_architecture
+    from mini_sglang_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding
+    from mini_sglang_b200.parts import register_feed_forward, register_position_encoding
+    from mini_sglang_b200.weights import TensorDecl
+
+    if "toy_top1_experts" not in FEED_FORWARDS:
+        @register_feed_forward("toy_top1_experts")
+        class Top1Experts(FeedForward):
+            """router logits in float32 -> the best expert of E for every token -> gelu MLP of that expert,
+            weighted by the router's softmax probability of the chosen expert."""
+
+            graph_safe = False               # gathers the rows of each expert: shapes depend on the tokens
+
+            def __init__(self, spec, prefix, env):
+                super().__init__(spec, prefix, env)
+                self.H, self.I, self.E = spec["hidden_size"], spec["intermediate_size"], spec["experts"]
+
+            def tensors(self):
+                t = {self.name("router.weight"): TensorDecl((self.E, self.H))}
+                for e in range(self.E):
+                    t[self.name(f"experts.{e}.up.weight")] = TensorDecl((self.I, self.H))
+                    t[self.name(f"experts.{e}.down.weight")] = TensorDecl((self.H, self.I))
+                return t
+
+            def load(self, src):
+                self.router = src.fetch(self.name("router.weight")).float()
+                self.up = [src.fetch(self.name(f"experts.{e}.up.weight")) for e in range(self.E)]
+                self.down = [src.fetch(self.name(f"experts.{e}.down.weight")) for e in range(self.E)]
+
+            def forward(self, x, ctx):
+                logits = x.float() @ self.router.T                        # routing in 32-bit
+                prob, best = torch.softmax(logits, -1).max(-1)
+                out = torch.zeros_like(x)
+                for e in range(self.E):
+                    rows = (best == e).nonzero().flatten()
+                    if rows.numel():
+                        h = torch.nn.functional.gelu(x[rows] @ self.up[e].T)
+                        out[rows] = ((h @ self.down[e].T).float() * prob[rows, None]).to(x.dtype)
+                return out
+
+    if "toy_linear_rotary" not in POSITION_ENCODINGS:
+        @register_position_encoding("toy_linear_rotary")
+        class LinearRotary(PositionEncoding):
+            """angle(p, i) = p * step * (i + 1) over the first `rot` elements of a head (NeoX halves)."""
+
+            def __init__(self, spec, prefix, env):
+                super().__init__(spec, prefix, env)
+                p = torch.arange(spec["max_positions"], dtype=torch.float32)[:, None]
+                ang = p * spec["step"] * torch.arange(1, spec["rot"] // 2 + 1, dtype=torch.float32)[None, :]
+                self.table = torch.cat((ang.cos(), ang.sin()), -1).contiguous().to(env.device)
+
+            def rotary_table(self):
+                return self.table
+
+    class Cfg:
+        def __init__(self, raw):
+            self.raw = raw
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw)
+
+    def build(cfg):
+        r = cfg.raw
+        H, V = r["width"], r["vocab"]
+        norm = PartSpec("rmsnorm", {"size": H, "eps": r["eps"]})
+        routed = PartSpec("toy_top1_experts", {"hidden_size": H, "intermediate_size": r["ffn"], "experts": 3})
+        dense = PartSpec("swiglu_mlp", {"hidden_size": H, "intermediate_size": r["ffn"]})
+        pos = PartSpec("toy_linear_rotary", {"rot": 8, "step": r["step"], "max_positions": 128})
+        att = lambda window: PartSpec("paged_attention", {"hidden_size": H, "num_heads": 6, "num_kv_heads": 3, "head_dim": 16,  # noqa: E731
+                                                          "qk_norm": True, "qk_norm_eps": r["eps"], "window": window})
+        layers = [LayerSpec("toy.layers.0", att(None), routed, {"input": norm, "post_mixer": norm}, position=pos),
+                  LayerSpec("toy.layers.1", att(6), dense, {"input": norm, "post_mixer": norm}, position=pos)]
+        return ModelSpec("ToyRoutedLM", H, V, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "name": "toy.embed.weight"}),
+                         PartSpec("rmsnorm", {"size": H, "eps": r["eps"], "name": "toy.norm.weight"}),
+                         PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": False, "name": "toy.head.weight"}),
+                         layers, [Run(0, cache=0), Run(1, cache=1)], max_context_len=128)
+
+    register_architecture("ToyRoutedLM", Cfg, build)
+    return build, Cfg
+
+
+def routed_toy_plain(w, tokens, eps, step):
+    f = {k: v.float() for k, v in w.items()}
+    S = len(tokens)
+    res = f["toy.embed.weight"][torch.tensor(tokens)]
+    pos = torch.arange(S, dtype=torch.float32)[:, None]
+    ang = pos * step * torch.arange(1, 5, dtype=torch.float32)[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+    def rotate(x):                                   # first 8 elements of every head, halves of 4 against each other
+        a, b, rest = x[..., :4], x[..., 4:8], x[..., 8:]
+        return torch.cat((a * cos - b * sin, b * cos + a * sin, rest), -1)
+
+    def attention(y, p, window):
+        q = P.rms_norm((y @ f[p + "q_proj.weight"].T).reshape(S, 6, 16), f[p + "q_norm.weight"], eps)
+        k = P.rms_norm((y @ f[p + "k_proj.weight"].T).reshape(S, 3, 16), f[p + "k_norm.weight"], eps)
+        v = (y @ f[p + "v_proj.weight"].T).reshape(S, 3, 16)
+        q, k = rotate(q), rotate(k)
+        k, v = k.repeat_interleave(2, 1), v.repeat_interleave(2, 1)
+        s = torch.einsum("qhd,khd->hqk", q, k) * 16 ** -0.5
+        i, j = torch.arange(S)[:, None], torch.arange(S)[None, :]
+        ok = (j <= i) if window is None else ((j <= i) & (j > i - window))
+        s = s.masked_fill(~ok, float("-inf"))
+        return torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(S, 96) @ f[p + "o_proj.weight"].T
+
+    def experts(y, p):
+        prob, best = torch.softmax(y @ f[p + "router.weight"].T, -1).max(-1)
+        out = torch.zeros_like(y)
+        for e in range(3):
+            rows = (best == e).nonzero().flatten()
+            out[rows] = (torch.nn.functional.gelu(y[rows] @ f[p + f"experts.{e}.up.weight"].T) @ f[p + f"experts.{e}.down.weight"].T) * prob[rows, None]
+        return out, best
+
+    y = P.rms_norm(res, f["toy.layers.0.input_layernorm.weight"], eps)
+    res = res + attention(y, "toy.layers.0.self_attn.", None)
+    y = P.rms_norm(res, f["toy.layers.0.post_attention_layernorm.weight"], eps)
+    moe, best = experts(y, "toy.layers.0.mlp.")
+    res = res + moe
+    y = P.rms_norm(res, f["toy.layers.1.input_layernorm.weight"], eps)
+    res = res + attention(y, "toy.layers.1.self_attn.", 6)
+    y = P.rms_norm(res, f["toy.layers.1.post_attention_layernorm.weight"], eps)
+    res = res + P.mlp_block(y, f, "toy.layers.1.mlp.")
+    return P.rms_norm(res, f["toy.norm.weight"], eps) @ f["toy.head.weight"].T, best
+
+
+def test_toy_architecture_with_routed_experts_and_another_rotary_encoding():
+    """Registered, built and stepped without a change to the framework's files: a feed-forward with routing, a
+    rotary encoding of another kind with partial rotation, layers that differ in feed-forward and window."""
+    from mini_sglang_b200.config import ARCHITECTURES
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    from mini_sglang_b200.weights import RandomSource
+
+    build, Cfg = _register_routed_toy()
+    try:
+        spec = build(Cfg({"width": 48, "vocab": 83, "ffn": 40, "eps": 1e-5, "step": 0.07}))
+        spec.validate()
+        holder = {}
+
+        def factory(expected, dt, dev):
+            src = RandomSource(expected, 23, dt, dev, std=0.15)
+            holder["w"] = {n: src.draw(n).cpu() for n in expected if src.has(n)}
+            return src
+
+        runner = ModelRunner(spec, factory, dtype="float32", page_size=4, num_pages=24, max_reqs=2, max_step_tokens=64)
+        assert len(runner.mgr.groups) == 2                    # all keys / a window of 6: pages of their own
+        assert not runner.use_cuda_graph
+        g = torch.Generator().manual_seed(8)
+        toks = torch.randint(0, 83, (37,), generator=g).tolist()
+        ref, best = routed_toy_plain(holder["w"], toks, 1e-5, 0.07)
+        assert len(set(best.tolist())) == 3                   # every expert gets tokens
+        s = runner.open()
+        got = []
+        for lo, hi in [(0, 9), (9, 11), (11, 30), (30, 31), (31, 37)]:
+            got.append(runner.step([StepEntry(s, toks[lo:hi], list(range(hi - lo)))]).float().cpu())
+        torch.testing.assert_close(torch.cat(got), ref, **TOL["float32"])
+    finally:
+        ARCHITECTURES.pop("ToyRoutedLM", None)
