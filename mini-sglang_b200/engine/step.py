@@ -217,8 +217,9 @@ class ModelRunner:
         return buf, i
 
     def _plan_splits(self, gi: int, q_lens: Sequence[int], kv_lens: Sequence[int], cap: int) -> List[int]:
-        """kv splits per request: only short query runs over long contexts are split, and only
-        while the launch would otherwise leave most of the 148 SMs idle."""
+        """kv splits per request: only query runs that fit one tile of the decode kernel are split (the
+        prefill kernels take whole key ranges), over long contexts, and only while the launch would
+        otherwise leave most of the 148 SMs idle."""
         n_kv, G, per_sm, qt = self._group_geom[gi]
         chunks = 1 if G <= 16 else -(-G // 16)
         blocks = sum(-(-q // qt) for q in q_lens) * n_kv * chunks
@@ -229,7 +230,7 @@ class ModelRunner:
         out = []
         for q, kv in zip(q_lens, kv_lens):
             keys = min(kv, window + q) if window else kv
-            out.append(1 if q > 16 else max(1, min(want, keys // MIN_KEYS_PER_SPLIT, cap)))
+            out.append(1 if q > qt else max(1, min(want, keys // MIN_KEYS_PER_SPLIT, cap)))      # one decode tile at most
         return out
 
     def _fill(self, host: np.ndarray, lay: _Layout, entries: Sequence[StepEntry], starts: Sequence[int],
@@ -284,7 +285,8 @@ class ModelRunner:
         host[lay.q_start + B] = t
         host[lay.want: lay.want + len(want_rows)] = want_rows
 
-    def _context(self, dev: torch.Tensor, lay: _Layout, q_lens, kv_lens, slots, max_splits, uniform: bool) -> StepContext:
+    def _context(self, dev: torch.Tensor, lay: _Layout, q_lens, kv_lens, slots, max_splits, uniform: bool,
+                 nsplits=None) -> StepContext:
         def v(off, n):
             return dev[off: off + n]
 
@@ -294,7 +296,8 @@ class ModelRunner:
             groups.append(GroupContext(block_table=v(lay.table[gi], lay.B * mp).view(lay.B, mp),
                                        out_loc=v(lay.out_loc[gi], lay.T),
                                        nsplit=v(lay.nsplit[gi], lay.B) if max_splits[gi] > 1 else None,
-                                       max_split=max_splits[gi], window=g.window))
+                                       max_split=max_splits[gi], window=g.window,
+                                       host_nsplit=nsplits[gi] if nsplits is not None else None))
         return StepContext(T=lay.T, B=lay.B, page_size=self.page_size, input_ids=v(lay.input_ids, lay.T),
                            positions=v(lay.positions, lay.T), q_start=v(lay.q_start, lay.B + 1),
                            kv_len=v(lay.kv_len, lay.B), token_req=v(lay.token_req, lay.T), slots=v(lay.slots, lay.B),
@@ -375,7 +378,7 @@ class ModelRunner:
             self._mark(idx)
             if prev_ids is not None:
                 ops.resolve_ids(dev[lay.input_ids: lay.input_ids + T], prev_ids)
-            ctx = self._context(dev, lay, q_lens, kv_lens, [e.slot for e in entries], max_splits, uniform)
+            ctx = self._context(dev, lay, q_lens, kv_lens, [e.slot for e in entries], max_splits, uniform, nsplits)
             rows = dev[lay.want: lay.want + len(want_rows)]
             logits = self.model.forward(ctx, self._caches(ctx), rows)
             ops.poll_status()

@@ -123,7 +123,10 @@ class PagedAttention(Mixer):
                 if n_dec:
                     ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=qt_dec,
                                   variant=ops.VARIANT_MMA_DECODE, grid_x=n_dec, **common)
-                if n_row and ops.tc_supported(self.d, q.dtype, G):
+                # the tcgen05 kernels take whole key ranges: only if no longer request has kv splits
+                unsplit = max_split == 1 or (g.host_nsplit is not None and
+                                             all(ns == 1 for n, ns in zip(ctx.host_q_lens, g.host_nsplit) if n > qt_dec))
+                if n_row and unsplit and ops.tc_supported(self.d, q.dtype, G):
                     ops.attention_tc(q, out, cache.k, cache.v, q_start=ctx.q_start, kv_len=ctx.kv_len,
                                      block_table=g.block_table, n_kv=self.n_kv, page_size=cache.page_size, window=window,
                                      scale=self.scale, qlen_min=qt_dec + 1, qlen_max=big, q_lens=ctx.host_q_lens)

@@ -9,7 +9,7 @@ step's tokens are written, so its first new token sits at position kv_len[r] - q
 from __future__ import annotations
 
 import dataclasses
-from typing import Dict, List, Optional, Tuple
+from typing import Sequence, Dict, List, Optional, Tuple
 
 import torch
 
@@ -21,6 +21,7 @@ class GroupContext:
     nsplit: Optional[torch.Tensor]     # [B] int32, kv splits per request (None: 1)
     max_split: int
     window: Optional[int]
+    host_nsplit: Optional[Sequence[int]] = None     # the host's copy of nsplit (None: not known here)
 
 
 @dataclasses.dataclass

@@ -95,3 +95,37 @@ def test_full_width_all_cuts(setup, dtype):
             top2 = ref[rid][pos].topk(2).values
             if top2[0] - top2[1] > 1e-2:
                 assert int(row.argmax()) == int(ref[rid][pos].argmax())
+
+
+def test_full_width_short_portions_after_a_long_context():
+    """A long context, then portions of 5, 2 and 12 tokens and single tokens: few blocks over many keys, so
+    the step function splits the keys of the runs that fit one decode tile, while runs above that go whole to
+    the prefill kernel.  bfloat16, against the plain
+    implementation."""
+    from mini_sglang_b200.config import Qwen3Config
+    from mini_sglang_b200.config.qwen3 import build_qwen3_spec
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    from mini_sglang_b200.parts import expected_tensors
+    from mini_sglang_b200.weights import RandomSource
+    spec = build_qwen3_spec(Qwen3Config.from_dict(CFG))
+    src = RandomSource(expected_tensors(spec), 7, torch.bfloat16, "cuda")
+    weights = {n: src.draw(n) for n in expected_tensors(spec) if src.has(n)}
+    g = torch.Generator().manual_seed(13)
+    toks = torch.randint(0, CFG["vocab_size"], (1100,), generator=g).tolist()
+    with torch.no_grad():
+        ref = P.forward_sequence(CFG, weights, toks, device="cuda").cpu()
+    runner = ModelRunner.from_random(spec, 7, dtype="bfloat16", page_size=16, num_pages=80, max_reqs=2)
+    s = runner.open()
+    got = {}
+    cuts = [(0, 1040), (1040, 1045), (1045, 1047), (1047, 1059)] + [(i, i + 1) for i in range(1059, 1100)]
+    for lo, hi in cuts:
+        want = [0, hi - lo - 1] if hi - lo > 1 else [0]
+        out = runner.step([StepEntry(s, toks[lo:hi], want)]).float().cpu()
+        for w, row in zip(want, out):
+            got[lo + w] = row
+    assert runner.use_cuda_graph
+    for pos, row in sorted(got.items()):
+        try:
+            check_row(row, ref[pos], "bfloat16")
+        except AssertionError as e:
+            raise AssertionError(f"position {pos}: {e}") from None

@@ -356,3 +356,11 @@ def test_attention_tcgen05_kernels(version, n_q, n_kv, P, window, monkeypatch):
     out, ref = run_attention_case(torch.bfloat16, n_q, n_kv, 128, P, q_lens, kv_lens, window=window, seed=3 + P, spike=True)
     ops.check_kernel_status()
     torch.testing.assert_close(out, ref.to(torch.bfloat16).float(), **ATT_TOL[torch.bfloat16])
+
+
+def test_attention_split_requests_never_reach_the_whole_range_kernels():
+    """kv splits asked for a request of 5 and of 12 tokens at head size 128: the tcgen05 kernels take whole key
+    ranges, so these requests must go to the kernel that writes split partials (else the merge would read what
+    nobody wrote)."""
+    out, ref = run_attention_case(torch.bfloat16, 32, 8, 128, 16, [5, 1, 12, 1], [3000, 2000, 2500, 700], force_split=4, seed=21)
+    torch.testing.assert_close(out, ref.to(torch.bfloat16).float(), **ATT_TOL[torch.bfloat16])
