@@ -270,8 +270,8 @@ def raise_if_failed(wait: bool = False) -> None:
 
 
 def tc_supported(head_dim: int, dtype: torch.dtype, group: int) -> bool:
-    """The tcgen05 prefill attention kernel takes bfloat16, head size 128."""
-    return USE_TC_ATTENTION and dtype == torch.bfloat16 and head_dim == 128 and group >= 1
+    """The tcgen05 prefill attention kernels take bfloat16, head size 128, up to 128 query heads per kv head."""
+    return USE_TC_ATTENTION and dtype == torch.bfloat16 and head_dim == 128 and 1 <= group <= TC_ROWS
 
 
 def check_kernel_status() -> None:
