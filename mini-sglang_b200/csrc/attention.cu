@@ -15,13 +15,17 @@
 // nsplit[r] > 1 spreads its key tiles over that many blocks, which write unnormalised partial
 // sums to scratch memory; msgl_attention_combine merges them in split order.
 //
-// Three kernels:
-//   attn_mma_kernel<D, false>   bfloat16, tensor cores (mma.sync m16n8k16), 64 rows per block,
-//                               each warp owns 16 rows and walks all keys of a tile
-//   attn_mma_kernel<D, true>    bfloat16, 16 rows per block (decode), each warp owns 16 of the
-//                               tile's 64 keys; the four warps are merged at the end
+// Kernels:
+//   attn_tc2_kernel / attn_tc_kernel   bfloat16, head size 128, query runs longer than a decode tile: tcgen05
+//                               tensor cores with accumulators in tensor memory (attention_tc2.cuh, attention_tc.cuh)
+//   attn_mma_kernel<D>          bfloat16, the same runs at other head sizes (16..256 in steps of 16): mma.sync
+//                               m16n8k16, 64 rows per block, each warp owns 16 rows and walks all keys of a tile
+//   attn_decode_t_kernel<D,...> bfloat16, short query runs (decode), head sizes in steps of 32: keys on the M
+//                               dimension of the mma, K straight from global memory into registers, kv splits
+//   attn_decode_kernel<D,...>   the same for head sizes 16 mod 32: heads on the M dimension
 //   attn_simt_kernel<T>         any head size up to 512, float32 arithmetic throughout; this is
 //                               the true 32-bit path and the fallback for odd head sizes
+//   attn_combine_kernel<T>      merge of the kv splits
 // Scores, softmax and the accumulation are float32 in all of them.
 #include "common.cuh"
 #include <math.h>
@@ -198,11 +202,11 @@ constexpr int MMA_KT = 64;        // keys per tile
 constexpr int MMA_WARPS = 4;
 constexpr int MMA_THREADS = MMA_WARPS * 32;
 
-template <int D, bool KEY_SPLIT>
+template <int D>
 __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams p) {
-    constexpr int R = KEY_SPLIT ? 16 : 64;          // rows per block
+    constexpr int R = 64;                           // rows per block
     constexpr int LDS = D + 8;                      // padded row of a shared-memory tile (elements)
-    constexpr int WK = KEY_SPLIT ? 16 : 64;         // keys of a tile that one warp handles
+    constexpr int WK = 64;                          // keys of a tile that one warp handles
     constexpr int NKB = WK / 8;                     // 8-key blocks per warp
     constexpr int NDB = D / 8;                      // 8-wide output column blocks
     constexpr int CH = D / 8;                       // 16-byte chunks per row
@@ -271,8 +275,8 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
     };
 
     // per-thread rows: g = lane / 4 (and g + 8) of this warp's 16 rows
-    const int row_base = KEY_SPLIT ? 0 : warp * 16;
-    const int key_base = KEY_SPLIT ? warp * 16 : 0;
+    const int row_base = warp * 16;
+    const int key_base = 0;
     const int r_lo = row_base + (lane >> 2), r_hi = r_lo + 8;
     const int pos_lo = p_min + r_lo / Gc, pos_hi = p_min + r_hi / Gc;   // position of each row's query
     const float sc = p.scale * 1.4426950408889634f;                     // scores in log2 units
@@ -391,7 +395,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
     __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(p.out);
     const bool direct = ns == 1;
 
-    if (!KEY_SPLIT) {
+    {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int r = half ? r_hi : r_lo;
@@ -418,50 +422,6 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
                     *reinterpret_cast<float2*>(dst + col) = make_float2(o[nd][half * 2], o[nd][half * 2 + 1]);
                 }
                 if ((lane & 3) == 0) { p.part_ml[prow * 2] = m; p.part_ml[prow * 2 + 1] = l; }
-            }
-        }
-    } else {
-        // merge the four warps (same rows, disjoint keys) through shared memory
-        float* Om = reinterpret_cast<float*>(KVs);              // [4][16][D]
-        float* Mm = Om + MMA_WARPS * 16 * D;                    // [4][16]
-        float* Lm = Mm + MMA_WARPS * 16;                        // [4][16]
-        __syncthreads();
-#pragma unroll
-        for (int nd = 0; nd < NDB; ++nd) {
-            const int col = nd * 8 + (lane & 3) * 2;
-            float* d0 = Om + ((size_t)warp * 16 + (lane >> 2)) * D + col;
-            float* d1 = d0 + 8 * D;
-            d0[0] = o[nd][0]; d0[1] = o[nd][1];
-            d1[0] = o[nd][2]; d1[1] = o[nd][3];
-        }
-        if ((lane & 3) == 0) {
-            Mm[warp * 16 + (lane >> 2)] = m_lo; Mm[warp * 16 + (lane >> 2) + 8] = m_hi;
-            Lm[warp * 16 + (lane >> 2)] = l_lo; Lm[warp * 16 + (lane >> 2) + 8] = l_hi;
-        }
-        __syncthreads();
-        for (int idx = tid; idx < 16 * D; idx += MMA_THREADS) {
-            const int r = idx / D, col = idx - r * D;
-            const int tl = r / Gc, hl = r - tl * Gc, hg = chunk * R + hl;
-            if (!(tl < ti.n_tok && hg < G && tl < QT)) continue;
-            float M = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < MMA_WARPS; ++w) M = fmaxf(M, Mm[w * 16 + r]);
-            const float Mu = (M == -INFINITY) ? 0.f : M;
-            float acc = 0.f, L = 0.f;
-#pragma unroll
-            for (int w = 0; w < MMA_WARPS; ++w) {
-                const float f = fast_exp2(Mm[w * 16 + r] - Mu);
-                acc += f * Om[((size_t)w * 16 + r) * D + col];
-                L += f * Lm[w * 16 + r];
-            }
-            const size_t tok = (size_t)(ti.q_base + ti.t0 + tl);
-            const int head = kvh * G + hg;
-            if (direct) {
-                og[(tok * p.n_q + head) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-            } else {
-                const size_t prow = ((size_t)split * p.T + tok) * p.n_q + head;
-                p.part_o[prow * D + col] = acc;
-                if (col == 0) { p.part_ml[prow * 2] = M; p.part_ml[prow * 2 + 1] = L; }
             }
         }
     }
@@ -1232,8 +1192,8 @@ static size_t simt_smem_bytes(int d) {
     return sizeof(float) * ((size_t)2 * SIMT_R * d + (size_t)SIMT_KT * (2 * d + 1) + SIMT_R * SIMT_KT + 3 * SIMT_R);
 }
 
-template <int D, bool KS> static size_t mma_smem_bytes() {
-    constexpr int R = KS ? 16 : 64;
+template <int D> static size_t mma_smem_bytes() {
+    constexpr int R = 64;
     return sizeof(__nv_bfloat16) * ((size_t)R * (D + 8) + (size_t)4 * MMA_KT * (D + 8));
 }
 
@@ -1284,13 +1244,13 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
     if (d != MSGL_HEAD_DIM) return MSGL_ERR_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
     if (variant == 1) {
-        const size_t smem = mma_smem_bytes<MSGL_HEAD_DIM, false>();
+        const size_t smem = mma_smem_bytes<MSGL_HEAD_DIM>();
         static bool attr_set = false;   // set once, outside any stream capture (the first launch is never captured)
         if (!attr_set) {
-            cudaFuncSetAttribute(attn_mma_kernel<MSGL_HEAD_DIM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(attn_mma_kernel<MSGL_HEAD_DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             attr_set = true;
         }
-        attn_mma_kernel<MSGL_HEAD_DIM, false><<<grid, MMA_THREADS, smem, stream>>>(p);
+        attn_mma_kernel<MSGL_HEAD_DIM><<<grid, MMA_THREADS, smem, stream>>>(p);
     } else if (variant == 2) {
         constexpr int NW = MSGL_DEC_WARPS;
         if (MSGL_HEAD_DIM % 32 == 0 && G <= 16) {
