@@ -20,7 +20,7 @@ def _env(name: str, default: float) -> float:
 @dataclasses.dataclass
 class EngineArgs:
     model: str
-    page_size: int = 1
+    page_size: int = 16                      # the reference's default is 1 (accepted here too); the kernels are tuned for 16
     max_num_reqs: int = 1024
     max_capture_bs: int = 128
     schedule_policy: str = "lpm"

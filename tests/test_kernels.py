@@ -343,10 +343,10 @@ def test_attention_far_key_and_page_edges(dtype):
 
 @pytest.mark.parametrize("version", [1, 2])
 @pytest.mark.parametrize("n_q,n_kv,P,window", [(32, 8, 16, None), (8, 8, 8, None), (16, 1, 64, None), (12, 4, 256, None),
-                                               (32, 8, 4, None), (6, 2, 16, 100), (8, 2, 32, 300)])
+                                               (32, 8, 4, None), (4, 2, 1, None), (6, 2, 16, 100), (8, 2, 32, 300)])
 def test_attention_tcgen05_kernels(version, n_q, n_kv, P, window, monkeypatch):
     """The two tcgen05 prefill kernels (one query tile per block; two in ping-pong) at head size 128: page sizes
-    that TMA fetches and one that it cannot (4: rows gathered, one-tile kernel), groups of 1, 3, 4 and 16 heads,
+    that TMA fetches and two that it cannot (4 and 1: rows gathered, one-tile kernel), groups of 1, 3, 4 and 16 heads,
     prompts that start at an offset, end inside a key tile or fill only part of a query tile, windows, and a far
     key that must dominate.  Unwritten cache slots hold NaN."""
     from mini_sglang_b200 import ops
