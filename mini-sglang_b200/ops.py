@@ -381,7 +381,7 @@ def set_true_fp32() -> None:
     torch.set_float32_matmul_precision("highest")
 
 
-SMALL_M_MAX = 8           # tokens up to which the weight-streaming kernel replaces the library GEMM (measured: faster up to 8)
+SMALL_M_MAX = int(os.environ.get("MSGL_SMALL_M_MAX", "8"))      # tokens up to which the weight-streaming kernel replaces the library GEMM (measured: faster up to 8)
 USE_SMALL_M = os.environ.get("MSGL_NO_SMALL_M", "") == ""
 
 
