@@ -80,8 +80,6 @@ class PagedAttention(Mixer):
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: KVCacheView, writes_cache: bool = True) -> torch.Tensor:
         qkv = ops.linear(x, self.qkv, self.qkv_b)
         table = self.position.rotary_table() if self.position is not None else None
-        if self.position is not None and table is None:
-            raise NotImplementedError("position encodings without a rotary table are applied by their own kernels")
         q = ops.qknorm_rope_kvwrite(
             qkv, ctx.positions, self.n_q, self.n_kv, self.d,
             q_weight=self.q_norm, k_weight=self.k_norm, eps=self.qk_norm_eps, rope_table=table,

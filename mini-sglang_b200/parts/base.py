@@ -75,12 +75,14 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    def rotary_table(self) -> Optional[torch.Tensor]:
-        """float32 [max_positions, rotary_dim] = cos | sin if this encoding is a NeoX-style rotation
-        that the fused q/k kernel can apply; None otherwise (then `apply` is called)."""
-        return None
+    """A position encoding that the attention mixer applies to q and k: a rotation of the first
+    `rotary_dim` elements of every head (NeoX halves) by angles that depend on the position and the
+    element pair in any way the encoding likes.  (An encoding that is added to the hidden state instead
+    belongs to an embedding part.)"""
 
-    def apply(self, q, k, positions):
+    def rotary_table(self) -> Optional[torch.Tensor]:
+        """float32 [max_positions, rotary_dim] = cos | sin of the angles; rotary_dim may be smaller than
+        the head size (partial rotation).  The fused q/k kernel applies it."""
         raise NotImplementedError
 
 
