@@ -28,7 +28,7 @@
 #define MSGL_GS_WARPS 8
 #endif
 #ifndef MSGL_GS_PF
-#define MSGL_GS_PF 6
+#define MSGL_GS_PF 5
 #endif
 constexpr int GS_WARPS = MSGL_GS_WARPS;
 constexpr int GS_PF = MSGL_GS_PF;      // chunks in flight per warp (ring depth)
