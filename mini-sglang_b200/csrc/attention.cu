@@ -707,9 +707,10 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
     __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [NW][ST][16][LDS]  (V only)
     __shared__ int sh_tile[4];
 
+    // What the kernel before this one writes are q and the new tokens' cache rows.  Lengths, splits and block
+    // tables come from the step's staging copy, so the block finds its work and asks for its first keys to be
+    // brought into L2 while that kernel still runs, and waits for it only then.
     pdl_launch_dependents();
-    pdl_wait();
-    pdl_after_wait();
     const int G = p.n_q / p.n_kv;
     const int Gc = G <= C ? G : C;
     const int n_chunks = G <= C ? 1 : (G + C - 1) / C;
@@ -735,18 +736,6 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
     const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(p.v_cache);
     const int* bt = p.block_table + (size_t)ti.req * p.bt_stride;
 
-    // Q as B operand: lane (g, t) holds Q[column nb*8 + g][32 j + 8 t .. + 7]
-    uint4 qf[NBH][KP];
-#pragma unroll
-    for (int nb = 0; nb < NBH; ++nb) {
-        const int c = nb * 8 + g;
-        const int tl = c / Gc, hl = c - tl * Gc, hg = chunk * C + hl;
-        const bool valid = tl < ti.n_tok && tl < QT && hg < G;
-        const __nv_bfloat16* src = qg + ((size_t)(ti.q_base + ti.t0 + (valid ? tl : 0)) * p.n_q + (size_t)kvh * G + (valid ? hg : 0)) * D + 8 * t;
-#pragma unroll
-        for (int j = 0; j < KP; ++j)
-            qf[nb][j] = valid ? *reinterpret_cast<const uint4*>(src + 32 * j) : make_uint4(0u, 0u, 0u, 0u);
-    }
     // the columns this lane sees in the accumulators: nb*8 + 2t and + 1
     int pos_c[NBH][2];
 #pragma unroll
@@ -804,6 +793,27 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
         }
     };
 
+    // first keys towards L2, then wait for the kernel before this one
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int pg = unit_page(i);
+        prefetch_k(i, __shfl_sync(0xffffffffu, pg, v_key));
+    }
+    pdl_wait();
+    pdl_after_wait();
+
+    // Q as B operand: lane (g, t) holds Q[column nb*8 + g][32 j + 8 t .. + 7]
+    uint4 qf[NBH][KP];
+#pragma unroll
+    for (int nb = 0; nb < NBH; ++nb) {
+        const int c = nb * 8 + g;
+        const int tl = c / Gc, hl = c - tl * Gc, hg = chunk * C + hl;
+        const bool valid = tl < ti.n_tok && tl < QT && hg < G;
+        const __nv_bfloat16* src = qg + ((size_t)(ti.q_base + ti.t0 + (valid ? tl : 0)) * p.n_q + (size_t)kvh * G + (valid ? hg : 0)) * D + 8 * t;
+#pragma unroll
+        for (int j = 0; j < KP; ++j)
+            qf[nb][j] = valid ? *reinterpret_cast<const uint4*>(src + 32 * j) : make_uint4(0u, 0u, 0u, 0u);
+    }
     // prologue: V of the first ST-1 units, K of unit 0, page of the next unit to fetch
 #pragma unroll
     for (int i = 0; i < ST - 1; ++i) {
@@ -1128,6 +1138,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     pdl_launch_dependents();
     pdl_wait();
     pdl_after_wait();
+    pdl_small();
     const int tok = blockIdx.x, h = blockIdx.y;
     const int req = token_req ? token_req[tok] : tok;
     const int ns = min(max(nsplit[req], 1), max_split);

@@ -83,6 +83,16 @@ __device__ __forceinline__ void pdl_after_wait() {
     pdl_trigger_();
 #endif
 }
+// a short kernel (norm, rotation, merge) releases its successor as soon as it runs itself: the product that
+// follows then launches and fetches its first weights beside it (MSGL_PDL_SMALL=0: at exit instead)
+#ifndef MSGL_PDL_SMALL
+#define MSGL_PDL_SMALL 1
+#endif
+__device__ __forceinline__ void pdl_small() {
+#if MSGL_PDL_MODE == 0 && MSGL_PDL_SMALL
+    pdl_trigger_();
+#endif
+}
 __device__ __forceinline__ void pdl_late() {
 #if MSGL_PDL_MODE == 0
     pdl_trigger_();

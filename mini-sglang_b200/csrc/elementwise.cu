@@ -19,6 +19,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     pdl_launch_dependents();
     pdl_wait();
     pdl_after_wait();
+    pdl_small();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -141,6 +142,7 @@ __global__ void rmsnorm_vec_kernel(const T* __restrict__ x, const float* res_in,
     pdl_launch_dependents();
     pdl_wait();
     pdl_after_wait();
+    pdl_small();
     const int r = blockIdx.x;
     const size_t src = (size_t)(row_idx ? row_idx[r] : r) * H;
     const size_t dst = (size_t)r * H;
@@ -377,6 +379,7 @@ __global__ void qknorm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, int qk
     pdl_launch_dependents();
     pdl_wait();
     pdl_after_wait();
+    pdl_small();
     const int t0 = blockIdx.x * QKR_TOK;
     const int warps = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
