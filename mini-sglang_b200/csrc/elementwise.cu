@@ -140,13 +140,23 @@ __global__ void rmsnorm_vec_kernel(const T* __restrict__ x, const float* res_in,
                                    float eps, T* __restrict__ y, int H) {
     __shared__ float red[32];
     pdl_launch_dependents();
-    pdl_wait();
-    pdl_after_wait();
-    pdl_small();
     const int r = blockIdx.x;
     const size_t src = (size_t)(row_idx ? row_idx[r] : r) * H;
     const size_t dst = (size_t)r * H;
     const int nvec = H >> 3;
+    // the norm's weights (and the row index) are nobody's output: fetched while the kernel before this one finishes
+    float wv[VPT][8];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) << 3;
+        if ((i >> 3) < nvec) {
+            if (w_is_f32) Vec8<float>::load(reinterpret_cast<const float*>(w) + i, wv[j]);
+            else Vec8<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(w) + i, wv[j]);
+        }
+    }
+    pdl_wait();
+    pdl_after_wait();
+    pdl_small();
     float v[VPT][8];
     float ss = 0.f;
 #pragma unroll
@@ -175,12 +185,9 @@ __global__ void rmsnorm_vec_kernel(const T* __restrict__ x, const float* res_in,
     for (int j = 0; j < VPT; ++j) {
         const int i = (threadIdx.x + j * blockDim.x) << 3;
         if ((i >> 3) < nvec) {
-            float wv[8];
-            if (w_is_f32) Vec8<float>::load(reinterpret_cast<const float*>(w) + i, wv);
-            else Vec8<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(w) + i, wv);
             float o[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) o[k] = v[j][k] * inv * wv[k];
+            for (int k = 0; k < 8; ++k) o[k] = v[j][k] * inv * wv[j][k];
             Vec8<T>::store(y + dst + i, o);
         }
     }
@@ -377,9 +384,6 @@ __global__ void qknorm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, int qk
                                                int page_size, int n_q, int n_kv, int T_) {
     constexpr int d = 32 * E;
     pdl_launch_dependents();
-    pdl_wait();
-    pdl_after_wait();
-    pdl_small();
     const int t0 = blockIdx.x * QKR_TOK;
     const int warps = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -391,12 +395,12 @@ __global__ void qknorm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, int qk
     const bool writes_cache = (k_cache != nullptr) && (out_loc != nullptr);
     if (!is_q && !writes_cache) return;
 
+    // positions, cache slots and norm weights are nobody's output: fetched while the kernel before this one finishes
     float v[QKR_TOK][E];
     int pos[QKR_TOK], slot[QKR_TOK];
 #pragma unroll
     for (int i = 0; i < QKR_TOK; ++i) {
         const int t = t0 + i < T_ ? t0 + i : T_ - 1;                     // past the end: the last token again, not stored
-        Pack<T, E>::load(qkv + (size_t)t * qkv_stride + (size_t)head * d + lane * E, v[i]);
         pos[i] = (table != nullptr && (is_q || is_k)) ? positions[t] : 0;
         slot[i] = is_q ? 0 : out_loc[t];
     }
@@ -405,6 +409,14 @@ __global__ void qknorm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, int qk
     if (nw != nullptr) {
 #pragma unroll
         for (int j = 0; j < E; ++j) w[j] = load_weight(nw, lane * E + j, w_is_f32);
+    }
+    pdl_wait();
+    pdl_after_wait();
+    pdl_small();
+#pragma unroll
+    for (int i = 0; i < QKR_TOK; ++i) {
+        const int t = t0 + i < T_ ? t0 + i : T_ - 1;
+        Pack<T, E>::load(qkv + (size_t)t * qkv_stride + (size_t)head * d + lane * E, v[i]);
     }
 #pragma unroll
     for (int i = 0; i < QKR_TOK; ++i) {
