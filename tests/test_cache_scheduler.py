@@ -277,6 +277,50 @@ def test_lookahead_decode_gives_the_same_tokens():
     assert stops and all(r.tokens[-1] == 23 for r in stops)
 
 
+def test_lookahead_with_requests_arriving_and_aborted_while_others_decode():
+    """Random arrival times, lengths, stop tokens, aborts and pool sizes: the overlapped schedule gives every
+    request the tokens and the finish reason of the read-first schedule, and leaves the cache idle."""
+    rnd = random.Random(11)
+    for trial in range(12):
+        n = rnd.randrange(3, 9)
+        prompts = prompts_for(100 + trial, n, 3, 60, shared=rnd.choice([0, 33]))
+        max_new = [rnd.randrange(1, 25) for _ in range(n)]
+        arrive = sorted(rnd.randrange(0, 30) for _ in range(n))
+        abort_at = {rnd.randrange(n): rnd.randrange(5, 40)} if trial % 3 == 0 else {}
+        page_size, num_pages = rnd.choice([(1, 400), (4, 60), (16, 24), (4, 4000)])
+        eos, ignore = rnd.choice([(0, True), (7, False), (23, False)])
+        results = []
+        for lookahead in (False, True):
+            mgr = CacheManager({0: PagedKVNeed(2, 16)}, page_size=page_size, num_pages=num_pages, max_reqs=4,
+                               max_context_len=4096, max_step_tokens=64)
+            runner = FakeRunner(mgr)
+            sch = Scheduler(runner, ArgmaxSampler(), max_num_reqs=4, max_step_tokens=64, chunk_size=16, policy="fcfs",
+                            eos_ids=[eos], retract_decode_steps=4, lookahead=lookahead)
+            runner.sched = sch
+            reqs = [Req(f"r{i}", p, SamplingParams(max_new_tokens=m, ignore_eos=ignore)) for i, (p, m) in enumerate(zip(prompts, max_new))]
+            step, nxt = 0, 0
+            while nxt < n or not sch.idle:
+                while nxt < n and arrive[nxt] <= step:
+                    sch.add_request(reqs[nxt])
+                    nxt += 1
+                for i, at in abort_at.items():
+                    if at == step:
+                        sch.abort(f"r{i}")
+                sch.step()
+                step += 1
+                assert step < 5000
+            sch.check_idle_invariants()
+            assert all(t >= 0 for r in reqs for t in r.tokens)
+            results.append([(r.output, r.finish_reason.type) for r in reqs])
+        base, look = results
+        for i, (b, l) in enumerate(zip(base, look)):
+            if i in abort_at:                    # an abort lands a step apart in the two schedules: a prefix either way
+                k = min(len(b[0]), len(l[0]))
+                assert b[0][:k] == l[0][:k]
+            else:
+                assert b == l, (trial, i)
+
+
 def test_scheduler_mixes_decode_tokens_with_prompt_portions():
     prompts = [[3] * 10, [4] * 50]
     reqs, sch, runner = run_all(4, 100, prompts, [30, 5], chunk=16, budget=24, policy="fcfs", prefix_cache=False)
