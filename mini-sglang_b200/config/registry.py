@@ -1,5 +1,8 @@
 """One registry from the architecture's name (config.json `architectures[0]`) to its model.
 
+(The reference builds Qwen3ForCausalLM unconditionally, mini_sglang/utils/loader.py:13-15, and reads the
+configuration through transformers' AutoConfig, mini_sglang/utils/model_config.py.)
+
 An architecture contributes two things: a typed configuration class that reads its own
 config.json keys, and a function from that configuration to a ModelSpec.  Adding an
 architecture is one `register_architecture` call; nothing else in the engine names it.

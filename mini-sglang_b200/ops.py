@@ -3,8 +3,12 @@
 Every function here launches hand-written sm_100a kernels from `csrc/` on the current CUDA
 stream of torch and returns torch tensors.  There is no other implementation behind them: a
 tensor that is not on a CUDA device, a missing compiler or an unsupported size raises.
-Matrix products are the one exception to "hand-written": `linear` calls the library GEMM that
-torch binds (cuBLAS), in bfloat16 with float32 accumulation or in true float32 (TF32 off).
+Matrix products with more than a few rows are the one exception to "hand-written": `linear` then calls
+the library GEMM that torch binds (cuBLAS), in bfloat16 with float32 accumulation or in true float32
+(TF32 off), as the reference does for every projection (F.linear in mini_sglang/layers/linear.py).  Up to
+SMALL_M_MAX rows go to this engine's weight-streaming kernel.  The reference's own kernels for the
+other operations come from sgl_kernel / flash-attn (mini_sglang/layers/layernorm.py:39-50,
+mini_sglang/layers/rotary_embedding.py, mini_sglang/layers/attention/fa3_attn_backend.py).
 """
 
 from __future__ import annotations

@@ -1,5 +1,10 @@
 """The model: embedding, the layers run in the order the description gives, final norm on the
-rows whose logits are wanted, output head."""
+rows whose logits are wanted, output head.
+
+The reference's counterpart is mini_sglang/models/qwen3.py:181-236 (Qwen3Model.forward: embedding,
+layers passing (hidden, residual), final norm; Qwen3ForCausalLM.forward: the head on the last row of
+every request through mini_sglang/layers/logits_processor.py:47-67).  Here the layer list and its order
+come from the ModelSpec, and the rows are whatever places the step asks for."""
 
 from __future__ import annotations
 

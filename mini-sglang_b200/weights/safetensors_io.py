@@ -1,4 +1,5 @@
-"""Reader and writer of the safetensors container, by tensor name.
+"""Reader and writer of the safetensors container, by tensor name (the reference reads the same files
+with the safetensors package, mini_sglang/utils/loader.py:17-23).
 
 File layout: 8 bytes little-endian header length N, N bytes of JSON
 {name: {"dtype", "shape", "data_offsets": [begin, end]}, "__metadata__": {...}}, then the raw
