@@ -8,7 +8,7 @@ the library GEMM that torch binds (cuBLAS), in bfloat16 with float32 accumulatio
 (TF32 off), as the reference does for every projection (F.linear in mini_sglang/layers/linear.py).  Up to
 SMALL_M_MAX rows go to this engine's weight-streaming kernel.  The reference's own kernels for the
 other operations come from sgl_kernel / flash-attn (mini_sglang/layers/layernorm.py:39-50,
-mini_sglang/layers/rotary_embedding.py, mini_sglang/layers/attention/fa3_attn_backend.py).
+mini_sglang/layers/rotary_embedding.py, mini_sglang/layers/attn/fa3_attn_backend.py).
 """
 
 from __future__ import annotations
