@@ -1296,42 +1296,6 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
     return msgl_check_launch();
 }
 
-#if MSGL_HEAD_DIM == 128
-// Tensor maps of the caches ([rows x 128] bfloat16, boxes of box_rows x 64 with 128-byte swizzle), made once per
-// (cache, size) and kept.  The driver's encoder is looked up at run time; nullptr if this driver has none.
-typedef CUresult (*tc_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static const CUtensorMap* tc_cache_map(const void* base, long long rows, int box_rows) {
-    static std::mutex mu;
-    static std::map<std::tuple<const void*, long long, int>, CUtensorMap> maps;
-    static tc_encode_fn encode = nullptr;
-    static bool looked = false;
-    std::lock_guard<std::mutex> lock(mu);
-    if (!looked) {
-        looked = true;
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult qr;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) == cudaSuccess &&
-            qr == cudaDriverEntryPointSuccess)
-            encode = (tc_encode_fn)fn;
-    }
-    if (encode == nullptr) return nullptr;
-    const auto key = std::make_tuple(base, rows, box_rows);
-    auto it = maps.find(key);
-    if (it != maps.end()) return &it->second;
-    CUtensorMap m;
-    const cuuint64_t dims[2] = {128, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {256};                       // bytes between rows
-    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    if (encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return nullptr;
-    return &maps.emplace(key, m).first->second;
-}
-#endif
-
 // tcgen05 prefill attention (head size 128, bfloat16): the requests with qlen_min <= q_len <= qlen_max, no kv
 // splits.  `status` is a device int the kernel sets to 1 if a block gave up waiting (never expected).
 // cache_pages: pages in the cache arrays (their first dimension), for the tensor maps of the TMA path.
@@ -1372,8 +1336,8 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
     if (pow2 && page_size >= 8 && cache_pages > 0 && ((((uintptr_t)k_cache | (uintptr_t)v_cache) & 127) == 0)) {
         const int box = page_size < TC_KT ? page_size : TC_KT;
         const long long rows = (long long)cache_pages * n_kv * page_size;
-        const CUtensorMap* km = tc_cache_map(k_cache, rows, box);
-        const CUtensorMap* vm = tc_cache_map(v_cache, rows, box);
+        const CUtensorMap* km = tc_matrix_map(k_cache, rows, 128, 256, box);
+        const CUtensorMap* vm = tc_matrix_map(v_cache, rows, 128, 256, box);
         if (km != nullptr && vm != nullptr) { kmap = *km; vmap = *vm; tma_box = box; }
     }
     if (version == 2) {

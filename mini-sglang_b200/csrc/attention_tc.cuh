@@ -37,10 +37,7 @@
 // Every wait on an mbarrier is bounded; a block that gives up writes a code to p.status, frees its
 // TMEM and returns (its output rows are then wrong, which the host reports as an error).
 #pragma once
-#include <cuda.h>          // CUtensorMap and its enums; the encoder itself is looked up at run time (no link to the driver library)
-#include <map>
-#include <mutex>
-#include <tuple>
+#include "tc_common.cuh"
 
 constexpr int TC_ROWS = 128;      // query rows per block
 constexpr int TC_KT = 128;        // keys per tile
@@ -53,122 +50,6 @@ constexpr unsigned TC_KHALF_BYTES = (unsigned)TC_KT * 128u;  // one 64-column ha
 constexpr unsigned TC_KV_BYTES = 2u * TC_KHALF_BYTES;      // 32 KB
 constexpr unsigned TC_SMEM_BYTES = TC_Q_BYTES + 2u * TC_KV_BYTES;    // 96 KB: two blocks per SM
 constexpr float TC_LAZY = 16.f;      // the exponent's reference follows the running maximum only past this many powers of two
-constexpr long long TC_SPIN_LIMIT = 4000000LL;             // polls of an mbarrier before a block gives up (a fraction of a second)
-
-__device__ __forceinline__ void tc_mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ bool tc_mbar_wait(unsigned bar, unsigned parity) {
-    for (long long it = 0; it < TC_SPIN_LIMIT; ++it) {
-        unsigned done;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tc_mbar_arrive(unsigned bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-// arrives on `bar` when all cp.async copies this thread has issued so far have landed
-__device__ __forceinline__ void tc_cp_async_arrive(unsigned bar) {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-// one TMA copy of a [rows x 64] box (128 bytes a row, 128-byte swizzle) at column x, row y of a 2-d tensor
-__device__ __forceinline__ void tc_tma_load(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-                 ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-// shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4), version 1, 128-byte swizzle
-__device__ __forceinline__ unsigned long long tc_desc(unsigned saddr, unsigned lbo_bytes, unsigned sbo_bytes) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((saddr & 0x3FFFFu) >> 4);
-    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= 1ull << 46;                     // descriptor version of sm_100
-    d |= 2ull << 61;                     // SWIZZLE_128B
-    return d;
-}
-
-// instruction descriptor, kind::f16: D fp32, A and B bfloat16, M = 128, N = n; b_mn: B is MN-major
-__device__ __forceinline__ unsigned tc_idesc(bool b_mn, unsigned n) {
-    unsigned d = 0;
-    d |= 1u << 4;                        // D format: F32
-    d |= 1u << 7;                        // A format: BF16
-    d |= 1u << 10;                       // B format: BF16
-    d |= (b_mn ? 1u : 0u) << 16;         // B major: 0 = K, 1 = MN
-    d |= (n >> 3) << 17;                 // N
-    d |= (128u >> 4) << 24;              // M
-    return d;
-}
-
-__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                       unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// the same with the A operand in tensor memory (128 lanes x 8 columns: 16 bfloat16 per row)
-__device__ __forceinline__ void tc_mma_ta(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc,
-                                          unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]), "=f"(v[16]), "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]), "=f"(v[24]), "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
-                 : "r"(taddr) : "memory");
-}
-// The registers of a tc_ld32 hold their values only after this.  The values pass through the statement, so that
-// the compiler keeps every use of them behind the wait.
-__device__ __forceinline__ void tc_wait_ld(float (&v)[32]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
-                 : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]), "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15]), "+f"(v[16]), "+f"(v[17]), "+f"(v[18]), "+f"(v[19]), "+f"(v[20]), "+f"(v[21]), "+f"(v[22]), "+f"(v[23]), "+f"(v[24]), "+f"(v[25]), "+f"(v[26]), "+f"(v[27]), "+f"(v[28]), "+f"(v[29]), "+f"(v[30]), "+f"(v[31])
-                 :: "memory");
-}
-__device__ __forceinline__ void tc_st32(unsigned taddr, const float (&v)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};\n"
-                 ::"r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-                   "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
-                   "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-                   "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
-                   "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
-                   "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
-                   "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
-                   "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31])),
-                   "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld16(unsigned taddr, unsigned (&v)[16]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld16(unsigned (&v)[16]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
-                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
-                   "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
-                 :: "memory");
-}
-__device__ __forceinline__ void tc_st16(unsigned taddr, const unsigned (&v)[16]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};\n"
-                 ::"r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
-                   "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 // byte offset of (row, 16-byte chunk c) inside a swizzled tile whose 64-column halves are `half_bytes` apart
 __device__ __forceinline__ unsigned tc_tile_off(int row, int c, unsigned half_bytes) {

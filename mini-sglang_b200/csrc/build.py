@@ -61,8 +61,9 @@ def build_dir() -> str:
 
 
 # files a source pulls in with #include: an edit of any of them rebuilds the library
-INCLUDED = {"attention.cu": ["attention_tc.cuh", "attention_tc2.cuh"],
-            "attention_noalloc.cu": ["attention.cu", "attention_tc.cuh", "attention_tc2.cuh", "attention_noalloc.h"]}
+INCLUDED = {"attention.cu": ["tc_common.cuh", "attention_tc.cuh", "attention_tc2.cuh"],
+            "attention_noalloc.cu": ["attention.cu", "tc_common.cuh", "attention_tc.cuh", "attention_tc2.cuh", "attention_noalloc.h"],
+            "gemm_tc.cu": ["tc_common.cuh"]}
 
 
 def _digest(sources: Sequence[str], flags: Sequence[str]) -> str:
@@ -132,7 +133,7 @@ def load_library(name: str, sources: Sequence[str], defines: Optional[Dict[str, 
 
 # the libraries of the engine -----------------------------------------------------------
 
-COMMON_SOURCES = ["elementwise.cu", "sampling.cu", "gemm_small_m.cu"]
+COMMON_SOURCES = ["elementwise.cu", "sampling.cu", "gemm_small_m.cu", "gemm_tc.cu"]
 ATTENTION_SOURCES = ["attention.cu"]
 MMA_HEAD_DIMS = tuple(range(16, 257, 16))   # head sizes the tensor-core attention kernel is built for
 

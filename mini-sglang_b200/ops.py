@@ -87,6 +87,8 @@ def _lib():
         lib.msgl_cast_from_f32.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_void_p]
         lib.msgl_gemm_small_m.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_int,
                                           c_int, c_void_p]
+        lib.msgl_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_int, c_void_p,
+                                     c_void_p]
         lib.msgl_sample.argtypes = [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_ull, c_void_p,
                                     c_void_p]
         _common = lib
@@ -238,7 +240,7 @@ def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor], row_keys:
 VARIANT_SIMT, VARIANT_MMA_ROWS, VARIANT_MMA_DECODE, VARIANT_TC = 0, 1, 2, 3
 TC_ROWS = 128                     # query rows per block of the tcgen05 prefill kernel
 USE_TC_ATTENTION = os.environ.get("MSGL_NO_TC_ATTENTION", "") == ""
-_status = None                    # device int32[64]: word 0 tcgen05 attention; words 4..: debug counters
+_status = None                    # device int32[64]: word 0 tcgen05 attention, word 2 tcgen05 GEMM; words 4..: debug counters
 _status_host = None               # its pinned mirror, refreshed by poll_status()
 _status_event = None
 
@@ -271,6 +273,8 @@ def raise_if_failed(wait: bool = False) -> None:
         return
     if int(_status_host[0]) != 0:
         raise KernelError("tcgen05 attention: a block timed out waiting for the tensor core; results are invalid")
+    if int(_status_host[2]) != 0:
+        raise KernelError("tcgen05 GEMM: a block timed out waiting for its pipeline; results are invalid")
 
 
 def tc_supported(head_dim: int, dtype: torch.dtype, group: int) -> bool:
@@ -400,6 +404,36 @@ def _small_m_ok(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
             and (bias is None or bias.dtype == torch.bfloat16))
 
 
+# This engine's tcgen05 GEMM (csrc/gemm_tc.cu) against the library's, measured on B200 at Qwen3-8B's sizes: with SwiGLU in
+# its epilogue it beats library GEMM + activation kernel from about a thousand rows on (2,048 rows: 291 against 310 us,
+# 8,192 rows: 1.17 against 1.35 ms); the plain products reach 88-100 % of the library's speed, so those stay with the
+# library unless MSGL_TC_GEMM=all.  MSGL_TC_GEMM=0 switches the kernel off.
+TC_GEMM = os.environ.get("MSGL_TC_GEMM", "swiglu")            # "swiglu" | "all" | "0"
+TC_GEMM_MIN_M = int(os.environ.get("MSGL_TC_GEMM_MIN_M", "1024"))
+_tc_gemm_usable = True
+
+
+def _tc_gemm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], mode: int) -> Optional[torch.Tensor]:
+    """x @ weight^T (mode 0) or SwiGLU of it (mode 1) by the tcgen05 kernel; None where it does not apply."""
+    global _tc_gemm_usable
+    if not ((TC_GEMM == "all" or (TC_GEMM == "swiglu" and mode == 1)) and _tc_gemm_usable and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+            and x.shape[0] >= TC_GEMM_MIN_M and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous()
+            and weight.shape[1] % 8 == 0 and (bias is None or bias.dtype == torch.bfloat16)):
+        return None
+    M, (N, K) = x.shape[0], weight.shape
+    n_out = N // 2 if mode == 1 else N
+    if n_out % 8 or (mode == 1 and N % 2):
+        return None
+    out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    code = _lib().msgl_gemm_tc(_ptr(weight), _ptr(x), _ptr(bias), _ptr(out), M, N, K, x.stride(0), n_out, mode,
+                               _ptr(_status_tensor(x.device)), _stream())
+    if code == 2:             # no tensor maps on this driver
+        _tc_gemm_usable = False
+        return None
+    _check(code, "gemm_tc")
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y = x @ weight^T (+ bias); weight is [out, in] as stored in the checkpoint.
@@ -414,6 +448,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         code = _small_m(weight, x, bias, out, M, N, K, N, 0, int(od == torch.float32))
         _check(code, "gemm_small_m")
         return out
+    if out_dtype in (None, torch.bfloat16):
+        y = _tc_gemm(x, weight, bias, 0)
+        if y is not None:
+            return y
     if out_dtype is not None and out_dtype != x.dtype:
         y = torch.mm(x, weight.t(), out_dtype=out_dtype)
         if bias is not None:
@@ -432,4 +470,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
         code = _small_m(gate_up, x, None, out, M, N, K, N // 2, 1, 0)
         _check(code, "gemm_small_m (swiglu)")
         return out
+    y = _tc_gemm(x, gate_up, None, 1)
+    if y is not None:
+        return y
     return swiglu(torch.nn.functional.linear(x, gate_up))
