@@ -34,6 +34,8 @@ DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.f
 SM_COUNT = 148
 MAX_KV_SPLIT = 16
 MIN_KEYS_PER_SPLIT = 256
+LONG_REQUEST_FACTOR = 1.25        # a request beyond this many times the mean load per block is cut up
+WIDE_KV_SPLIT = 8                 # cap of the decode graphs that are captured for batches with such requests
 
 
 @dataclasses.dataclass
@@ -161,7 +163,7 @@ class ModelRunner:
         self.use_cuda_graph = use_cuda_graph and all(getattr(l.mixer, "graph_safe", False) and getattr(l.ffn, "graph_safe", True)
                                                      for l in self.model.layers)
         self.max_capture_bs = max_capture_bs
-        self._graphs: Dict[Tuple[int, Tuple[int, ...]], _Graph] = {}
+        self._graphs: Dict[Tuple[int, Tuple[int, ...], bool], _Graph] = {}
         self._graph_pool = None
         self.kernel_launches = 0
         self._group_geom = []
@@ -216,21 +218,35 @@ class ModelRunner:
             self._pinned[i] = buf
         return buf, i
 
-    def _plan_splits(self, gi: int, q_lens: Sequence[int], kv_lens: Sequence[int], cap: int) -> List[int]:
-        """kv splits per request: only query runs that fit one tile of the decode kernel are split (the
-        prefill kernels take whole key ranges), over long contexts, and only while the launch would
-        otherwise leave most of the 148 SMs idle."""
+    def _plan_splits(self, gi: int, q_lens: Sequence[int], kv_lens: Sequence[int], cap: int,
+                     long_cap: Optional[int] = None) -> List[int]:
+        """kv splits per request.  Only query runs that fit one tile of the decode kernel are split (the
+        prefill kernels take whole key ranges).  Two reasons to split: the launch would otherwise leave
+        most of the SMs idle (few requests: every request is cut alike), or one request is much longer
+        than the launch's mean load per resident block, so that its single block would still run when all
+        others are done (it is cut into pieces of about that load).  `cap` bounds the first kind of cut,
+        `long_cap` (default: the same) the second."""
         n_kv, G, per_sm, qt = self._group_geom[gi]
-        chunks = 1 if G <= 16 else -(-G // 16)
-        blocks = sum(-(-q // qt) for q in q_lens) * n_kv * chunks
-        want = (SM_COUNT * per_sm) // max(blocks, 1)      # fill the SMs once, not more
-        if want <= 1 or cap <= 1:
+        long_cap = cap if long_cap is None else long_cap
+        if cap <= 1 and long_cap <= 1:
             return [1] * len(q_lens)
+        chunks = 1 if G <= 16 else -(-G // 16)
+        heads = n_kv * chunks
+        slots = SM_COUNT * per_sm
+        blocks = sum(-(-q // qt) for q in q_lens) * heads
+        want = slots // max(blocks, 1)                    # fill the SMs once, not more
         window = self.mgr.groups[gi].window
+        keys = [min(kv, window + q) if window else kv for q, kv in zip(q_lens, kv_lens)]
+        load = sum(k for q, k in zip(q_lens, keys) if q <= qt) * heads / slots      # keys per resident block, dealt out evenly
+        piece = max(MIN_KEYS_PER_SPLIT, int(load * LONG_REQUEST_FACTOR))
         out = []
-        for q, kv in zip(q_lens, kv_lens):
-            keys = min(kv, window + q) if window else kv
-            out.append(1 if q > qt else max(1, min(want, keys // MIN_KEYS_PER_SPLIT, cap)))      # one decode tile at most
+        for q, k in zip(q_lens, keys):
+            if q > qt:
+                out.append(1)                             # one decode tile at most
+                continue
+            even = min(want, k // MIN_KEYS_PER_SPLIT, cap)
+            long_one = min(-(-k // piece), long_cap) if k > piece else 1
+            out.append(max(1, even, long_one))
         return out
 
     def _fill(self, host: np.ndarray, lay: _Layout, entries: Sequence[StepEntry], starts: Sequence[int],
@@ -413,16 +429,17 @@ class ModelRunner:
         b = self._bucket(B)
         need_pages = [max(int(g.n_pages[e.slot]) for e in entries) for g in self.mgr.groups]
         mp = tuple(max(8, 1 << (n - 1).bit_length()) for n in need_pages)
-        key = (b, mp)
+        # the graph fixes the launch's split dimension: the narrow one suits requests of like length; a batch
+        # with a request far longer than the rest takes a second graph with room for more pieces
+        narrow = [self._graph_max_split(gi, b) for gi in range(len(self.mgr.groups))]
+        nsplits = [self._plan_splits(gi, q_lens, kv_lens, narrow[gi], max(narrow[gi], WIDE_KV_SPLIT)) for gi in range(len(self.mgr.groups))]
+        wide = any(max(ns) > cap for ns, cap in zip(nsplits, narrow))
+        key = (b, mp, wide)
         gr = self._graphs.get(key)
         if gr is None:
-            gr = self._capture(b, mp)
+            gr = self._capture(b, mp, [max(c, WIDE_KV_SPLIT) for c in narrow] if wide else narrow)
             self._graphs[key] = gr
         lay = gr.layout
-        nsplits = []
-        for gi in range(len(self.mgr.groups)):
-            ns = self._plan_splits(gi, q_lens, kv_lens, gr.max_split[gi])
-            nsplits.append(ns)
         host, idx = self._pinned_buffer(lay.size)
         self._fill(host.numpy(), lay, entries, starts, list(range(b)), nsplits)
         gr.dev.copy_(host[:lay.size], non_blocking=True)
@@ -433,12 +450,12 @@ class ModelRunner:
         ops.LAUNCHES += gr.n_kernels
         return gr.logits[:B]
 
-    def _capture(self, b: int, mp: Tuple[int, ...]) -> _Graph:
+    def _capture(self, b: int, mp: Tuple[int, ...], max_split: Sequence[int]) -> _Graph:
         gr = _Graph()
         lay = _Layout(b, b, b, mp)
         gr.layout = lay
         gr.dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
-        gr.max_split = [self._graph_max_split(gi, b) for gi in range(len(self.mgr.groups))]
+        gr.max_split = list(max_split)
         host = np.zeros(lay.size, dtype=np.int32)
         self._fill(host, lay, [], [], list(range(b)), [[1] * b for _ in self.mgr.groups])
         gr.dev.copy_(torch.from_numpy(host))

@@ -129,3 +129,41 @@ def test_full_width_short_portions_after_a_long_context():
             check_row(row, ref[pos], "bfloat16")
         except AssertionError as e:
             raise AssertionError(f"position {pos}: {e}") from None
+
+
+def test_full_width_one_long_request_among_many_short_ones():
+    """64 requests of 18 tokens and one of 1,190 decode together: the blocks of the short ones fill the GPU, so
+    nothing would be split for want of blocks, but the long request's keys are many times the mean load of a
+    block; the step function cuts them up and replays the graph that has room for the pieces.  bfloat16, the
+    long request and two of the short ones against the plain implementation."""
+    from mini_sglang_b200.config import Qwen3Config
+    from mini_sglang_b200.config.qwen3 import build_qwen3_spec
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    from mini_sglang_b200.parts import expected_tensors
+    from mini_sglang_b200.weights import RandomSource
+    spec = build_qwen3_spec(Qwen3Config.from_dict(CFG))
+    src = RandomSource(expected_tensors(spec), 7, torch.bfloat16, "cuda")
+    weights = {n: src.draw(n) for n in expected_tensors(spec) if src.has(n)}
+    g = torch.Generator().manual_seed(29)
+    n_short, short_len, long_len, n_dec = 64, 18, 1190, 6
+    long_toks = torch.randint(0, CFG["vocab_size"], (long_len + n_dec,), generator=g).tolist()
+    short_toks = [torch.randint(0, CFG["vocab_size"], (short_len + n_dec,), generator=g).tolist() for _ in range(n_short)]
+    with torch.no_grad():
+        ref_long = P.forward_sequence(CFG, weights, long_toks, device="cuda").cpu()
+        ref_short = {i: P.forward_sequence(CFG, weights, short_toks[i], device="cuda").cpu() for i in (0, n_short - 1)}
+    runner = ModelRunner.from_random(spec, 7, dtype="bfloat16", page_size=16, num_pages=2 * n_short + 80, max_reqs=n_short + 2)
+    s_long = runner.open()
+    runner.step([StepEntry(s_long, long_toks[:long_len], [])])
+    shorts = [runner.open() for _ in range(n_short)]
+    runner.step([StepEntry(s, t[:short_len], []) for s, t in zip(shorts, short_toks)])
+    for i in range(n_dec):
+        ents = [StepEntry(s_long, [long_toks[long_len + i]], [0])]
+        ents += [StepEntry(s, [t[short_len + i]], [0]) for s, t in zip(shorts, short_toks)]
+        out = runner.step(ents).float().cpu()
+        for row, want, name in ((out[0], ref_long[long_len + i], "long"), (out[1], ref_short[0][short_len + i], "short 0"),
+                                (out[n_short], ref_short[n_short - 1][short_len + i], "last short")):
+            try:
+                check_row(row, want, "bfloat16")
+            except AssertionError as e:
+                raise AssertionError(f"decode step {i}, {name} request: {e}") from None
+    assert any(wide for _, _, wide in runner._graphs), "the batch should have taken the graph with room for more pieces"
