@@ -89,6 +89,7 @@ def _lib():
                                           c_int, c_void_p]
         lib.msgl_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_int, c_void_p,
                                      c_void_p]
+        lib.msgl_gemm_tc2.argtypes = lib.msgl_gemm_tc.argtypes
         lib.msgl_sample.argtypes = [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_ull, c_void_p,
                                     c_void_p]
         _common = lib
@@ -404,12 +405,15 @@ def _small_m_ok(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
             and (bias is None or bias.dtype == torch.bfloat16))
 
 
-# This engine's tcgen05 GEMM (csrc/gemm_tc.cu) against the library's, measured on B200 at Qwen3-8B's sizes: with SwiGLU in
-# its epilogue it beats library GEMM + activation kernel from about a thousand rows on (2,048 rows: 291 against 310 us,
-# 8,192 rows: 1.17 against 1.35 ms); the plain products reach 88-100 % of the library's speed, so those stay with the
-# library unless MSGL_TC_GEMM=all.  MSGL_TC_GEMM=0 switches the kernel off.
+# This engine's tcgen05 GEMM (csrc/gemm_tc.cu) against the library's, measured on B200 at Qwen3-8B's sizes.  With SwiGLU in
+# its epilogue the kernel on pairs of SMs (cta_group::2) beats library GEMM + activation kernel from about 256 rows on
+# (512 rows: 83 against 86 us, 2,048 rows: 285 against 310 us, 4,096 rows: 0.52 against 0.72 ms; 2,048-token prefill step
+# 27.4 -> 26.4 ms).  Its plain products reach 92-95 % of the library's speed at 2,048 rows (the one-block kernel: 88 %), so
+# those stay with the library unless MSGL_TC_GEMM=all (prefill step + 1.3 ms).  MSGL_TC_GEMM=0 switches the kernel off,
+# MSGL_TC_GEMM_CTAS=1 takes the one-block kernel.
 TC_GEMM = os.environ.get("MSGL_TC_GEMM", "swiglu")            # "swiglu" | "all" | "0"
-TC_GEMM_MIN_M = int(os.environ.get("MSGL_TC_GEMM_MIN_M", "1024"))
+TC_GEMM_MIN_M = int(os.environ.get("MSGL_TC_GEMM_MIN_M", "256"))
+TC_GEMM_CTAS = int(os.environ.get("MSGL_TC_GEMM_CTAS", "2"))   # 2: the kernel on pairs of SMs (tcgen05 cta_group::2)
 _tc_gemm_usable = True
 
 
@@ -425,8 +429,8 @@ def _tc_gemm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]
     if n_out % 8 or (mode == 1 and N % 2):
         return None
     out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
-    code = _lib().msgl_gemm_tc(_ptr(weight), _ptr(x), _ptr(bias), _ptr(out), M, N, K, x.stride(0), n_out, mode,
-                               _ptr(_status_tensor(x.device)), _stream())
+    fn = _lib().msgl_gemm_tc2 if TC_GEMM_CTAS == 2 else _lib().msgl_gemm_tc
+    code = fn(_ptr(weight), _ptr(x), _ptr(bias), _ptr(out), M, N, K, x.stride(0), n_out, mode, _ptr(_status_tensor(x.device)), _stream())
     if code == 2:             # no tensor maps on this driver
         _tc_gemm_usable = False
         return None

@@ -111,11 +111,14 @@ def test_small_m_gemm(M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(1, 16, 8), (128, 256, 64), (129, 24, 72), (300, 520, 200), (700, 1040, 328),
                                    (1500, 6144, 4096), (2048, 4096, 12288), (257, 264, 4104)])
-def test_tcgen05_gemm(M, N, K, monkeypatch):
-    """The tcgen05 GEMM alone: tiles that end inside the matrices in all three directions, a bias, a row
-    stride, and SwiGLU in the epilogue, against float32 products of the same bfloat16 operands."""
+@pytest.mark.parametrize("ctas", [1, 2])
+def test_tcgen05_gemm(M, N, K, ctas, monkeypatch):
+    """The tcgen05 GEMM alone, on single SMs and on pairs of them: tiles that end inside the matrices in all
+    three directions, a bias, a row stride, and SwiGLU in the epilogue, against float32 products of the same
+    bfloat16 operands."""
     o = ops()
     monkeypatch.setattr(o, "TC_GEMM", "all")
+    monkeypatch.setattr(o, "TC_GEMM_CTAS", ctas)
     monkeypatch.setattr(o, "TC_GEMM_MIN_M", 1)
     g = torch.Generator(device="cpu").manual_seed(M + N + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
