@@ -140,7 +140,7 @@ MMA_HEAD_DIMS = tuple(range(16, 257, 16))   # head sizes the tensor-core attenti
 
 def common_library() -> ctypes.CDLL:
     defines = {}
-    for knob in ("MSGL_GS_WARPS", "MSGL_GS_PF", "MSGL_PDL_MODE", "MSGL_PDL_SMALL"):                 # tuning knobs of the small-M GEMM
+    for knob in ("MSGL_GS_WARPS", "MSGL_GS_PF", "MSGL_PDL_MODE", "MSGL_PDL_SMALL", "MSGL_GT2_STAGES"):      # tuning knobs of the GEMM kernels
         if os.environ.get(knob):
             defines[knob] = int(os.environ[knob])
     return load_library("common", COMMON_SOURCES, defines or None)
