@@ -34,7 +34,7 @@ DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.f
 SM_COUNT = 148
 MAX_KV_SPLIT = 16
 MIN_KEYS_PER_SPLIT = 256
-LONG_REQUEST_FACTOR = 1.25        # a request beyond this many times the mean load per block is cut up
+LONG_REQUEST_FACTOR = 1.5         # a request beyond this many times the mean load per block is cut up (1.0, 1.25, 1.5 measured: 1.5 best)
 WIDE_KV_SPLIT = 8                 # cap of the decode graphs that are captured for batches with such requests
 
 
@@ -112,6 +112,36 @@ class _Graph:
         self.logits = None
         self.max_split = None
         self.n_kernels = 0     # this engine's kernels inside the captured graph
+
+
+def plan_kv_splits(q_lens: Sequence[int], kv_lens: Sequence[int], *, n_kv: int, group: int, blocks_per_sm: int,
+                   tile_tokens: int, window: Optional[int], cap: int, long_cap: Optional[int] = None) -> List[int]:
+    """kv splits per request of one attention launch.  Only query runs that fit one tile of the decode kernel
+    (`tile_tokens`) are split (the prefill kernels take whole key ranges).  Two reasons to split: the launch
+    would otherwise leave most of the SMs idle (few requests: every request is cut alike), or one request is
+    much longer than the launch's mean load per resident block, so that its single block would still run when
+    all others are done (it is cut into pieces of about that load).  `cap` bounds the first kind of cut,
+    `long_cap` (default: the same) the second."""
+    long_cap = cap if long_cap is None else long_cap
+    if cap <= 1 and long_cap <= 1:
+        return [1] * len(q_lens)
+    chunks = 1 if group <= 16 else -(-group // 16)
+    heads = n_kv * chunks
+    slots = SM_COUNT * blocks_per_sm
+    blocks = sum(-(-q // tile_tokens) for q in q_lens) * heads
+    want = slots // max(blocks, 1)                    # fill the SMs once, not more
+    keys = [min(kv, window + q) if window else kv for q, kv in zip(q_lens, kv_lens)]
+    load = sum(k for q, k in zip(q_lens, keys) if q <= tile_tokens) * heads / slots      # keys per resident block, dealt out evenly
+    piece = max(MIN_KEYS_PER_SPLIT, int(load * LONG_REQUEST_FACTOR))
+    out = []
+    for q, k in zip(q_lens, keys):
+        if q > tile_tokens:
+            out.append(1)                             # one decode tile at most
+            continue
+        even = min(want, k // MIN_KEYS_PER_SPLIT, cap)
+        long_one = min(-(-k // piece), k // MIN_KEYS_PER_SPLIT, long_cap) if k > piece else 1      # no piece below the minimum
+        out.append(max(1, even, long_one))
+    return out
 
 
 class ModelRunner:
@@ -220,34 +250,9 @@ class ModelRunner:
 
     def _plan_splits(self, gi: int, q_lens: Sequence[int], kv_lens: Sequence[int], cap: int,
                      long_cap: Optional[int] = None) -> List[int]:
-        """kv splits per request.  Only query runs that fit one tile of the decode kernel are split (the
-        prefill kernels take whole key ranges).  Two reasons to split: the launch would otherwise leave
-        most of the SMs idle (few requests: every request is cut alike), or one request is much longer
-        than the launch's mean load per resident block, so that its single block would still run when all
-        others are done (it is cut into pieces of about that load).  `cap` bounds the first kind of cut,
-        `long_cap` (default: the same) the second."""
         n_kv, G, per_sm, qt = self._group_geom[gi]
-        long_cap = cap if long_cap is None else long_cap
-        if cap <= 1 and long_cap <= 1:
-            return [1] * len(q_lens)
-        chunks = 1 if G <= 16 else -(-G // 16)
-        heads = n_kv * chunks
-        slots = SM_COUNT * per_sm
-        blocks = sum(-(-q // qt) for q in q_lens) * heads
-        want = slots // max(blocks, 1)                    # fill the SMs once, not more
-        window = self.mgr.groups[gi].window
-        keys = [min(kv, window + q) if window else kv for q, kv in zip(q_lens, kv_lens)]
-        load = sum(k for q, k in zip(q_lens, keys) if q <= qt) * heads / slots      # keys per resident block, dealt out evenly
-        piece = max(MIN_KEYS_PER_SPLIT, int(load * LONG_REQUEST_FACTOR))
-        out = []
-        for q, k in zip(q_lens, keys):
-            if q > qt:
-                out.append(1)                             # one decode tile at most
-                continue
-            even = min(want, k // MIN_KEYS_PER_SPLIT, cap)
-            long_one = min(-(-k // piece), long_cap) if k > piece else 1
-            out.append(max(1, even, long_one))
-        return out
+        return plan_kv_splits(q_lens, kv_lens, n_kv=n_kv, group=G, blocks_per_sm=per_sm, tile_tokens=qt,
+                              window=self.mgr.groups[gi].window, cap=cap, long_cap=long_cap)
 
     def _fill(self, host: np.ndarray, lay: _Layout, entries: Sequence[StepEntry], starts: Sequence[int],
               want_rows: Sequence[int], nsplits: Sequence[Sequence[int]], pad_to: int = 0) -> None:

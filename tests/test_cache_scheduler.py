@@ -406,3 +406,36 @@ def test_policies_order():
     assert [r.rid for r, _, _ in sch._ordered_waiting()] == ["r1", "r2", "r0"]
     with pytest.raises(ValueError, match="dfs-weight"):
         Scheduler(FakeRunner(mgr), ArgmaxSampler(), policy="dfs-weight")
+
+
+# ---------------------------------------------------------------------------------------
+# the step function's plan of kv splits (pure arithmetic on the host)
+# ---------------------------------------------------------------------------------------
+def test_kv_split_plan():
+    from mini_sglang_b200.engine.step import MIN_KEYS_PER_SPLIT, SM_COUNT, plan_kv_splits
+    geo = dict(n_kv=8, group=4, blocks_per_sm=4, tile_tokens=2, window=None)
+    slots = SM_COUNT * 4
+    # few requests: everybody is cut alike, so that the blocks fill the SMs once
+    ns = plan_kv_splits([1] * 8, [4096] * 8, cap=16, **geo)
+    assert ns == [slots // 64] * 8
+    # a cut never leaves pieces shorter than MIN_KEYS_PER_SPLIT, and a cap holds
+    assert plan_kv_splits([1], [3 * MIN_KEYS_PER_SPLIT + 5], cap=16, **geo) == [3]
+    assert plan_kv_splits([1] * 8, [4096] * 8, cap=4, **geo) == [4] * 8
+    assert plan_kv_splits([1] * 8, [4096] * 8, cap=1, **geo) == [1] * 8
+    # as many requests of like length as the GPU holds blocks: nothing is cut
+    assert plan_kv_splits([1] * 64, [4096] * 64, cap=1, long_cap=8, **geo) == [1] * 64
+    assert plan_kv_splits([1] * 64, [4000 + 3 * i for i in range(64)], cap=1, long_cap=8, **geo) == [1] * 64
+    # one request far longer than the rest is cut into pieces of about the mean load of a block, the others stay whole
+    ns = plan_kv_splits([1] * 65, [1200] + [20] * 64, cap=1, long_cap=8, **geo)
+    assert ns[0] == 1200 // MIN_KEYS_PER_SPLIT and ns[1:] == [1] * 64
+    ns = plan_kv_splits([1] * 48, [8192] + [1024] * 47, cap=1, long_cap=8, **geo)
+    assert 2 <= ns[0] <= 8 and ns[1:] == [1] * 47
+    # runs longer than one decode tile go whole to the prefill kernels, whatever their length; they do not count as load
+    ns = plan_kv_splits([1, 5, 1], [8192, 8192, 300], cap=16, **geo)
+    assert ns[1] == 1 and ns[0] > 1 and ns[2] == 1
+    # a window bounds the keys that count
+    geo_w = dict(geo, window=512)
+    assert plan_kv_splits([1] * 8, [4096] * 8, cap=16, **geo_w) == [513 // MIN_KEYS_PER_SPLIT] * 8
+    # wide groups take several blocks per kv head: fewer splits fill the SMs
+    wide = dict(n_kv=2, group=32, blocks_per_sm=4, tile_tokens=1, window=None)
+    assert plan_kv_splits([1] * 16, [8192] * 16, cap=16, **wide) == [slots // (16 * 2 * 2)] * 16
