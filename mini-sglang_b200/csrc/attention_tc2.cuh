@@ -22,6 +22,26 @@
 // 11 idle after the Q gather.  All waits are bounded as in attention_tc.cuh.
 #pragma once
 
+// two float32 values in one 64-bit register, for the packed float32 instructions of sm_100
+__device__ __forceinline__ unsigned long long f2_pack(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long f2_fma(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long f2_add(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
 constexpr int TC2_ROWS = 256;               // query rows per block (two tiles of 128)
 constexpr int TC2_THREADS = 384;
 constexpr unsigned TC2_SMEM_BYTES = 2u * TC_Q_BYTES + 4u * TC_KV_BYTES;      // 192 KB
@@ -296,20 +316,31 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) attn_tc2_kernel(const AttnPara
             TC2_MARK(2)
             float tile_sum;
             auto exponentials = [&]() {
+                // two neighbouring scores at a time through the packed float32 instructions (fma.rn.f32x2, add.rn.f32x2): the
+                // softmax warps are bound by the number of instructions they issue, and these halve the multiply-adds and adds
                 const float mu = (m_run == -INFINITY) ? 0.f : m_run;
-                float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                const unsigned long long sc2 = f2_pack(sc, sc), nmu2 = f2_pack(-mu, -mu);
+                unsigned long long sum2[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sum2[j] = 0ull;                  // (0.f, 0.f)
                 auto expo = [&](const float (&sv)[32], int cb) {
                     unsigned pk[16];
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
-                        const float e0 = fast_exp2(fmaf(sv[j], sc, -mu)), e1 = fast_exp2(fmaf(sv[j + 1], sc, -mu));
-                        sum8[(j >> 1) & 7] += e0 + e1;
+                        float x0, x1;
+                        f2_unpack(f2_fma(f2_pack(sv[j], sv[j + 1]), sc2, nmu2), x0, x1);
+                        const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+                        sum2[(j >> 1) & 7] = f2_add(sum2[(j >> 1) & 7], f2_pack(e0, e1));
                         pk[j >> 1] = pack_bf16(e0, e1);
                     }
                     tc_st16(ts + cb * 16, pk);         // P columns [16 cb, 16 cb + 16); the row's scores are all in registers
                 };
                 expo(s0, 0); expo(s1, 1); expo(s2, 2); expo(s3, 3);
-                tile_sum = ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
+                const unsigned long long t4 = f2_add(f2_add(f2_add(sum2[0], sum2[1]), f2_add(sum2[2], sum2[3])),
+                                                     f2_add(f2_add(sum2[4], sum2[5]), f2_add(sum2[6], sum2[7])));
+                float lo, hi;
+                f2_unpack(t4, lo, hi);
+                tile_sum = lo + hi;
             };
             exponentials();
             if (__any_sync(0xffffffffu, !(tile_sum < 1.0e30f))) {        // overflow (inf, or nan from inf - inf): again, from the maximum
