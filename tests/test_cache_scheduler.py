@@ -416,8 +416,10 @@ def test_kv_split_plan():
     geo = dict(n_kv=8, group=4, blocks_per_sm=4, tile_tokens=2, window=None)
     slots = SM_COUNT * 4
     # few requests: everybody is cut alike, so that the blocks fill the SMs once
+    # (9 blocks a request would fill the 592 places, but 4,096 keys are 256 units of 16 for 4 warps: 8 blocks are as fast)
     ns = plan_kv_splits([1] * 8, [4096] * 8, cap=16, **geo)
-    assert ns == [slots // 64] * 8
+    assert slots // 64 == 9 and ns == [8] * 8
+    assert plan_kv_splits([1] * 8, [4096 + 16 * 4 * 8] * 8, cap=16, **geo) == [9] * 8
     # a cut never leaves pieces shorter than MIN_KEYS_PER_SPLIT, and a cap holds
     assert plan_kv_splits([1], [3 * MIN_KEYS_PER_SPLIT + 5], cap=16, **geo) == [3]
     assert plan_kv_splits([1] * 8, [4096] * 8, cap=4, **geo) == [4] * 8
