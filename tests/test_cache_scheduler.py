@@ -427,6 +427,12 @@ def test_kv_split_plan():
     # as many requests of like length as the GPU holds blocks: nothing is cut
     assert plan_kv_splits([1] * 64, [4096] * 64, cap=1, long_cap=8, **geo) == [1] * 64
     assert plan_kv_splits([1] * 64, [4000 + 3 * i for i in range(64)], cap=1, long_cap=8, **geo) == [1] * 64
+    # ... unless the contexts are long and the blocks fall unevenly on the SMs (512 blocks: 3.5 an SM): then halves (1,024: 6.9)
+    assert plan_kv_splits([1] * 64, [8192] * 64, cap=1, long_cap=8, **geo) == [2] * 64
+    assert plan_kv_splits([1] * 64, [8192] * 64, cap=1, long_cap=1, **geo) == [1] * 64
+    assert plan_kv_splits([1] * 72, [8192] * 72, cap=1, long_cap=8, **geo) == [1] * 72        # 576 blocks: 3.9 an SM already
+    # fewer blocks than the GPU holds: every request is longer than 1.5 mean loads of a block and is halved (measured better)
+    assert plan_kv_splits([1] * 40, [4096] * 40, cap=1, long_cap=8, **geo) == [2] * 40
     # one request far longer than the rest is cut into pieces of about the mean load of a block, the others stay whole
     ns = plan_kv_splits([1] * 65, [1200] + [20] * 64, cap=1, long_cap=8, **geo)
     assert ns[0] == 1200 // MIN_KEYS_PER_SPLIT and ns[1:] == [1] * 64
