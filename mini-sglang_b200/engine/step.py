@@ -387,10 +387,17 @@ class ModelRunner:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         V = self.vocab_size
         lowest = -int(prev_ids.numel()) if prev_ids is not None else 0        # -1 - r: row r of prev_ids, on the device
-        for e in entries:
-            toks = np.asarray(e.tokens)
+        if all(len(e.tokens) == 1 for e in entries):          # a decode batch: one look at all tokens
+            toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=len(entries))
             if toks.min() < lowest or toks.max() >= V:
-                raise ValueError(f"token id outside [0, {V}) in the entry of slot {e.slot}")
+                bad = next(e for e in entries if not lowest <= e.tokens[0] < V)
+                raise ValueError(f"token id outside [0, {V}) in the entry of slot {bad.slot}")
+        else:
+            for e in entries:
+                toks = np.asarray(e.tokens)
+                if toks.min() < lowest or toks.max() >= V:
+                    raise ValueError(f"token id outside [0, {V}) in the entry of slot {e.slot}")
+        for e in entries:
             for w in e.want:
                 if not 0 <= w < len(e.tokens):
                     raise ValueError(f"wanted place {w} is outside the entry's {len(e.tokens)} tokens")
