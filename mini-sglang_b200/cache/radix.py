@@ -55,6 +55,13 @@ class PrefixTree:
 
     # -- pinning -----------------------------------------------------------------------
     def lock(self, node: Node) -> None:
+        """Pin the path from `node` to the root.  A node that was evicted since it was matched is refused:
+        its page may belong to someone else by now."""
+        up = node
+        while up is not self.root:
+            if up.parent is None:
+                raise RuntimeError("prefix tree: lock of a node that is no longer in the tree (evicted after it was matched)")
+            up = up.parent
         while node is not self.root:
             if node.lock_ref == 0:
                 self.evictable_pages -= 1
@@ -113,6 +120,7 @@ class PrefixTree:
             freed.append(nd.page)
             parent = nd.parent
             del parent.children[nd.key]
+            nd.parent = None                     # detached: lock() refuses it from now on
             self.evictable_pages -= 1
             self.num_nodes -= 1
             if parent is not self.root and not parent.children and parent.lock_ref == 0:
@@ -142,6 +150,11 @@ class PrefixTree:
         if self.protected_pages:
             raise RuntimeError("prefix tree: reset while pages are pinned")
         pages = self.all_pages()
+        stack = list(self.root.children.values())
+        while stack:
+            nd = stack.pop()
+            stack.extend(nd.children.values())
+            nd.parent = None
         self.root.children.clear()
         self.evictable_pages = 0
         self.num_nodes = 0

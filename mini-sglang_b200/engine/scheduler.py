@@ -83,7 +83,6 @@ class Req:
         self.retractions = 0
         self.t_arrive = time.time()
         self.t_first_token: Optional[float] = None
-        self.prompt_inserted = False
 
     @property
     def n_output(self) -> int:
@@ -191,9 +190,34 @@ class Scheduler:
         return not self.waiting and not self.running and self._inflight is None
 
     # -- accounting ------------------------------------------------------------------------
-    def _free_tokens(self) -> int:
-        ev = self.tree.evictable_pages if self.tree else 0
-        return (self.mgr.available_pages(0) + ev) * self.P
+    def _hold(self, gi: int, n_tokens: float, portion: int = 1) -> float:
+        """Tokens' worth of pages of group `gi` that a request of n_tokens holds at most: all of them, or for a
+        group that keeps a window the window plus the largest `portion` it is still fed in one step (pages
+        behind the window are given back) plus a page for the ragged ends."""
+        w = self.mgr.groups[gi].window
+        if w is None:
+            return n_tokens
+        return min(n_tokens, w + portion + self.P)
+
+    def _portion(self, n_unfed: int) -> int:
+        return max(1, min(n_unfed, self.chunk_size, self.max_step_tokens))
+
+    def _free_tokens(self, gi: int = 0) -> int:
+        ev = self.tree.evictable_pages if (self.tree is not None and gi == 0) else 0
+        return (self.mgr.available_pages(gi) + ev) * self.P
+
+    def _claims(self) -> List[float]:
+        """Per group: what the running requests will still take (their unfed tokens plus the estimated share of
+        the tokens they may still generate)."""
+        ratio = self.new_token_ratio
+        out = [0.0] * len(self.mgr.groups)
+        for r in self.running:
+            total = len(r.tokens) + (r.params.max_new_tokens - r.n_output) * ratio
+            have = int(self.mgr.length[r.slot])
+            portion = self._portion(len(r.tokens) - have)
+            for gi in range(len(out)):
+                out[gi] += self._hold(gi, total, portion) - self._hold(gi, have, portion)
+        return out
 
     def _make_room(self, pages_per_group: Sequence[int]) -> bool:
         """Evict prefix-cache pages until the pools can hand out `pages_per_group`."""
@@ -248,7 +272,8 @@ class Scheduler:
     # -- ordering --------------------------------------------------------------------------
     def _ordered_waiting(self) -> List[Tuple[Req, List[int], object]]:
         """Waiting requests in policy order with their prefix match; requests that should wait for
-        another one to fill the prefix cache are left out of this step."""
+        another one to fill the prefix cache are left out of this step.  The match is a first look for
+        the order only: admission matches again, since admitting one request may evict what another matched."""
         matches = {}
         for r in self.waiting:
             if self.tree is not None:
@@ -264,21 +289,40 @@ class Scheduler:
         elif self.policy == "random":
             self._rand.shuffle(order)
         out = []
+        feeding: Dict[tuple, List[Req]] = {}       # requests whose prompt is under way, by their first tokens
         if self.tree is not None:
-            inflight = {tuple(r.tokens[:IN_BATCH_PREFIX]) for r in self.running
-                        if not r.prompt_inserted and r.n_prompt >= IN_BATCH_PREFIX}
-        else:
-            inflight = set()
+            for q in self.running:
+                if len(q.tokens) >= IN_BATCH_PREFIX and int(self.mgr.length[q.slot]) < len(q.tokens) - 1:
+                    feeding.setdefault(tuple(q.tokens[:IN_BATCH_PREFIX]), []).append(q)
         seen = set()
         for r in order:
             pages, node = matches[r.rid]
-            if self.tree is not None and len(pages) * self.P < IN_BATCH_PREFIX and len(r.tokens) - 1 >= IN_BATCH_PREFIX:
+            if self.tree is not None and len(r.tokens) - 1 >= IN_BATCH_PREFIX:
                 key = tuple(r.tokens[:IN_BATCH_PREFIX])
-                if key in inflight or key in seen:
+                if self._prefix_on_its_way(r, len(pages) * self.P, feeding.get(key, ())):
                     continue
-                seen.add(key)
+                if len(pages) * self.P < IN_BATCH_PREFIX:
+                    if key in seen:
+                        continue                 # an earlier waiting request computes the shared tokens first
+                    seen.add(key)
             out.append((r, pages, node))
         return out
+
+    def _prefix_on_its_way(self, r: Req, matched: int, feeding: Sequence[Req]) -> bool:
+        """True while a request that is still feeding its prompt has yet to reach whole pages that `r` shares
+        with it beyond the `matched` tokens the prefix cache holds now: every portion's full pages go to the
+        cache right after its step, so waiting saves `r` from computing them again."""
+        P = self.P
+        mine = r.tokens[:-1]
+        for q in feeding:
+            n = min(len(mine), len(q.tokens))
+            c = IN_BATCH_PREFIX                 # the caller found the first IN_BATCH_PREFIX tokens equal
+            while c < n and mine[c] == q.tokens[c]:
+                c += 1
+            c = c // P * P
+            if c >= IN_BATCH_PREFIX and c > matched and int(self.mgr.length[q.slot]) < c:
+                return True
+        return False
 
     # -- retraction ------------------------------------------------------------------------
     def _decode_pages(self, reqs: Sequence[Req], turns: int) -> List[int]:
@@ -309,7 +353,6 @@ class Scheduler:
             r = keep.pop()
             self._release(r, insert=False)
             r.retractions += 1
-            r.prompt_inserted = False
             self.running.remove(r)
             self.waiting.append(r)
             retracted.append(r)
@@ -368,27 +411,35 @@ class Scheduler:
         # 3. new requests (none in a step that had to retract)
         if not retracted and budget > 0 and self.waiting:
             ratio = self.new_token_ratio
-            used = sum((len(r.tokens) - int(self.mgr.length[r.slot])) + (r.params.max_new_tokens - r.n_output) * ratio
-                       for r in self.running)
-            for r, pages, node in self._ordered_waiting():
+            n_groups = len(self.mgr.groups)
+            used = self._claims()
+            for r, _, _ in self._ordered_waiting():
                 if len(self.running) >= self.max_num_reqs or budget <= 0 or self.mgr.free_slots == 0:
                     break
+                # matched now, not when the order was made: making room for a request admitted earlier in
+                # this step may have evicted pages that this one matched then
+                pages, node = self.tree.match(r.tokens[:-1]) if self.tree is not None else ([], None)
                 prefix = len(pages) * self.P
                 extend = len(r.tokens) - prefix
-                need = extend + (r.params.max_new_tokens - r.n_output) * ratio
+                total = len(r.tokens) + (r.params.max_new_tokens - r.n_output) * ratio
+                portion = self._portion(extend)
+                need = [self._hold(gi, total, portion) - self._hold(gi, prefix, portion) for gi in range(n_groups)]
                 if node is not None:
                     self.tree.lock(node)             # the matched pages are no longer evictable
-                fits = need <= self._free_tokens() - used
-                if not fits and not self.running and not plan and extend + 1 <= self._free_tokens():
+                free = [self._free_tokens(gi) for gi in range(n_groups)]
+                fits = all(need[gi] <= free[gi] - used[gi] for gi in range(n_groups))
+                alone = not self.running and not plan
+                if not fits and alone and all(self._hold(gi, len(r.tokens) + 1, portion) - self._hold(gi, prefix, portion) <= free[gi]
+                                              for gi in range(n_groups)):
                     fits = True          # alone: the estimate of its future length must not keep it out
                 if not fits:
                     if node is not None:
                         self.tree.unlock(node)
-                    total_tokens = self.mgr.groups[0].pool.num_pages * self.P
-                    if not self.running and not plan and len(r.tokens) + 1 > total_tokens:
+                    pool_tokens = [g.pool.num_pages * self.P for g in self.mgr.groups]
+                    if alone and any(self._hold(gi, len(r.tokens) + 1, portion) > pool_tokens[gi] for gi in range(n_groups)):
                         # alone and still too large for the whole pool: it can never run
                         self.waiting.remove(r)
-                        r.to_abort = f"request of {len(r.tokens)} tokens does not fit the cache of {total_tokens} tokens"
+                        r.to_abort = f"request of {len(r.tokens)} tokens does not fit the cache of {min(pool_tokens)} tokens"
                         r.check_finished()
                         outputs.append(StepOutput(r, None, True))
                         self.stats["aborted"] += 1
@@ -409,7 +460,8 @@ class Scheduler:
                 self.running.append(r)
                 plan.append((r, n))
                 budget -= n
-                used += need
+                for gi in range(n_groups):
+                    used[gi] += need[gi]
 
         if not plan and self.running:
             # nobody can move: prompts under way hold the pages and none of them can grow.  The one
@@ -419,7 +471,6 @@ class Scheduler:
             if self.running:
                 self._release(victim, insert=False)
                 victim.retractions += 1
-                victim.prompt_inserted = False
                 self.waiting.append(victim)
                 self.stats["retractions"] += 1
             else:
@@ -446,6 +497,12 @@ class Scheduler:
                 self.stats["prefill_tokens"] += n
         logits = self.runner.step(entries)
         self.stats["steps"] += 1
+        if self.tree is not None:
+            # a prompt's full pages become shareable as soon as the step that computes them is launched
+            # (later steps run after it on the same stream), portion by portion
+            for (r, n), e in zip(plan, entries):
+                if not (n == 1 and int(self.mgr.length[r.slot]) > r.n_prompt):
+                    self._insert(r)
         flight = self._sample(logits, sampled)
         if self.lookahead:
             self._inflight = flight          # read at the next call
@@ -509,9 +566,6 @@ class Scheduler:
                 self.stats["finished"] += 1
                 outputs.append(StepOutput(r, tok, True))
             else:
-                if not r.prompt_inserted and self.tree is not None:
-                    self._insert(r)               # the prompt's pages become shareable
-                r.prompt_inserted = True
                 outputs.append(StepOutput(r, tok, False))
         return outputs
 

@@ -162,7 +162,12 @@ def test_prefix_tree_lru_order():
 # ---------------------------------------------------------------------------------------
 class FakeRunner:
     """Keeps the real cache manager busy; the 'logits' at a wanted place depend only on the
-    request's tokens up to that place, so any schedule must generate the same tokens."""
+    request's tokens up to that place, so any schedule must generate the same tokens.
+
+    It also plays the cache itself: every page remembers which (position, token) was written into each of its
+    places.  Before a request's tokens are 'computed', every earlier position that the request may still read
+    must hold exactly that request's token in the page its block table names, so a page that two requests
+    write, or a prefix page that was evicted and handed to someone else, fails the step that reads it."""
 
     V = 64
 
@@ -171,11 +176,22 @@ class FakeRunner:
         self.history = {}
         self.steps = []
         self.lookahead_steps = 0
+        self.content = [dict() for _ in mgr.groups]          # per group: page -> {place: (position, token)}
 
     supports_device_tokens = True
 
+    def _check_owned_pages_are_private(self):
+        for gi, g in enumerate(self.mgr.groups):
+            seen = {}
+            for slot in range(1, self.mgr.max_reqs + 1):
+                if self.mgr.is_open(slot):
+                    for p in self.mgr.owned_pages(slot, gi):
+                        assert p not in seen, f"page {p} of group {gi} is owned by slots {seen[p]} and {slot}"
+                        seen[p] = slot
+
     def step(self, entries, prev_ids=None):
         rows = []
+        P = self.mgr.page_size
         self.steps.append([(e.slot, len(e.tokens)) for e in entries])
         self.lookahead_steps += prev_ids is not None
         short = [0] * len(self.mgr.groups)
@@ -184,7 +200,8 @@ class FakeRunner:
                 short[gi] += n
         for gi, g in enumerate(self.mgr.groups):
             assert short[gi] <= g.pool.available, "the scheduler planned a step that does not fit"
-        for e in entries:
+        hists = []
+        for e in entries:                                    # first every entry writes, as one batch does
             start = int(self.mgr.length[e.slot])
             # tokens before `start` may sit in pages taken over from the prefix cache: the request knows them
             req = next(r for r in self.sched.running if r.slot == e.slot)
@@ -192,7 +209,23 @@ class FakeRunner:
             fed = [int(prev_ids[-1 - t]) if t < 0 else t for t in e.tokens]      # -1 - r: row r of the tokens in flight
             hist = list(req.tokens[:start]) + fed
             assert min(hist) >= 0
+            hists.append((start, hist))
             self.mgr.reserve(e.slot, len(e.tokens))
+            for gi, g in enumerate(self.mgr.groups):
+                for pos in range(start, start + len(e.tokens)):
+                    page = int(g.table[e.slot, pos // P])
+                    assert page > 0
+                    self.content[gi].setdefault(page, {})[pos % P] = (pos, hist[pos])
+        self._check_owned_pages_are_private()
+        for e, (start, hist) in zip(entries, hists):         # then every entry reads
+            end = start + len(e.tokens)
+            for gi, g in enumerate(self.mgr.groups):
+                lo = 0 if g.window is None else max(0, start - g.window + 1)
+                for pos in range(lo, end):
+                    page = int(g.table[e.slot, pos // P])
+                    got = self.content[gi].get(page, {}).get(pos % P)
+                    assert got == (pos, hist[pos]), \
+                        f"slot {e.slot} reads position {pos} from page {page} of group {gi}: holds {got}, wants {(pos, hist[pos])}"
             for w in e.want:
                 row = torch.zeros(self.V)
                 row[hash(tuple(hist[:start + w + 1])) % (self.V - 1) + 1] = 1.0     # never token 0 (eos)
@@ -447,3 +480,125 @@ def test_kv_split_plan():
     # wide groups take several blocks per kv head: fewer splits fill the SMs
     wide = dict(n_kv=2, group=32, blocks_per_sm=4, tile_tokens=1, window=None)
     assert plan_kv_splits([1] * 16, [8192] * 16, cap=16, **wide) == [slots // (16 * 2 * 2)] * 16
+
+
+# ---------------------------------------------------------------------------------------
+# prefix cache under pressure, portions, and several groups
+# ---------------------------------------------------------------------------------------
+def make_sched(needs, page_size, num_pages, *, max_reqs=8, budget=16384, chunk=8192, policy="fcfs", **kw):
+    mgr = CacheManager(needs, page_size=page_size, num_pages=num_pages, max_reqs=max_reqs, max_context_len=4096,
+                       max_step_tokens=budget)
+    runner = FakeRunner(mgr)
+    sch = Scheduler(runner, ArgmaxSampler(), max_num_reqs=max_reqs, max_step_tokens=budget, chunk_size=chunk,
+                    policy=policy, eos_ids=[0], retract_decode_steps=4, **kw)
+    runner.sched = sch
+    return sch, runner
+
+
+def drain(sch, limit=20000):
+    n = 0
+    while not sch.idle:
+        sch.step()
+        n += 1
+        assert n < limit, "scheduler does not make progress"
+    sch.check_idle_invariants()
+
+
+def test_admission_evicting_a_prefix_that_a_later_request_matched():
+    """Three requests wait; making room for the first evicts cached pages that the other two matched a
+    moment earlier.  Those two must not adopt the evicted pages (the first request owns them now)."""
+    X, Z = list(range(1, 13)), list(range(21, 33))
+    for policy in ("fcfs", "lpm"):
+        sch, runner = make_sched({0: PagedKVNeed(2, 16)}, 4, 42, policy=policy)
+        for i, p in enumerate((X, Z)):
+            sch.add_request(Req(f"warm{i}", p + [40 + i], SamplingParams(max_new_tokens=2, ignore_eos=True)))
+        drain(sch)
+        assert sch.tree.num_nodes == 6 and sch.tree.match(X)[0] and sch.tree.match(Z)[0]
+        a = Req("a", [50 + i % 9 for i in range(150)], SamplingParams(max_new_tokens=2, ignore_eos=True))
+        b = Req("b", X + [45, 46], SamplingParams(max_new_tokens=2, ignore_eos=True))
+        c = Req("c", Z + [47, 48], SamplingParams(max_new_tokens=2, ignore_eos=True))
+        order = (a, b, c) if policy == "fcfs" else (b, c, a)
+        for r in order:
+            sch.add_request(r)
+        drain(sch)                                           # FakeRunner asserts on every read and on page ownership
+        assert sch.stats["evicted_pages"] > 0
+        assert all(r.finish_reason.type == "length" and len(r.output) == 2 for r in (a, b, c))
+
+
+def test_lock_refuses_an_evicted_node():
+    tree = PrefixTree(2)
+    tree.insert([1, 2, 3, 4], [5, 6], 0)
+    _, node = tree.match([1, 2, 3, 4])
+    assert tree.evict(2) == [6, 5]
+    with pytest.raises(RuntimeError, match="no longer in the tree"):
+        tree.lock(node)
+    assert tree.evictable_pages == 0 and tree.protected_pages == 0
+
+
+def test_prompt_portions_reach_the_prefix_cache_one_by_one():
+    """Two requests share 64 tokens; prompts are fed 16 tokens a step.  The first one's full pages go to the
+    prefix cache after every portion, and the second starts as soon as the shared pages are there: it takes
+    all 64 tokens from the cache and never waits for the rest of the first one's prompt."""
+    shared = [1 + i % 50 for i in range(64)]
+    first = Req("first", shared + [51] * 70, SamplingParams(max_new_tokens=3, ignore_eos=True))
+    second = Req("second", shared + [52] * 9, SamplingParams(max_new_tokens=3, ignore_eos=True))
+    sch, runner = make_sched({0: PagedKVNeed(2, 16)}, 4, 200, chunk=16, budget=64, policy="lpm")
+    sch.add_request(first)
+    sch.add_request(second)
+    started_at = None
+    for step in range(200):
+        if sch.idle:
+            break
+        sch.step()
+        if step < 4:
+            assert sch.tree.num_nodes == 4 * (step + 1)              # 16 tokens = 4 pages more after every portion
+        if started_at is None and second.slot is not None:
+            started_at = step
+            assert int(sch.mgr.length[first.slot]) < first.n_prompt   # the first prompt is still under way
+    assert started_at == 4 and second.cached_tokens == 64
+    assert len(first.output) == 3 and len(second.output) == 3
+    sch.check_idle_invariants()
+    # same tokens as without any sharing
+    base = []
+    for r in (first, second):
+        sch2, _ = make_sched({0: PagedKVNeed(2, 16)}, 4, 200, enable_prefix_cache=False)
+        q = Req(r.rid, r.tokens[:r.n_prompt], SamplingParams(max_new_tokens=3, ignore_eos=True))
+        sch2.add_request(q)
+        drain(sch2)
+        base.append(q.output)
+    assert [first.output, second.output] == base
+
+
+def test_scheduler_on_a_model_with_an_all_keys_group_and_a_windowed_group():
+    """Admission, retraction and give-backs count every group's pool: here the windowed group's pool is the
+    scarce one.  Everything finishes with the tokens of an unconstrained run, no page is lost and nothing starves."""
+    needs = {0: PagedKVNeed(2, 16), 1: PagedKVNeed(2, 16, window=12), 2: StateNeed((4,))}
+    prompts = prompts_for(5, 10, 10, 70)
+    max_new = [5 + (3 * i) % 25 for i in range(10)]
+
+    def run(num_pages, shrink_window_pool=None, **kw):
+        sch, runner = make_sched(needs, 4, num_pages, max_reqs=6, budget=40, chunk=16, **kw)
+        assert sch.tree is None and len(sch.mgr.groups) == 2
+        if shrink_window_pool:
+            g = sch.mgr.groups[1]
+            g.pool = PagePool(shrink_window_pool)
+        reqs = [Req(f"r{i}", p, SamplingParams(max_new_tokens=m, ignore_eos=True)) for i, (p, m) in enumerate(zip(prompts, max_new))]
+        for r in reqs:
+            sch.add_request(r)
+        drain(sch)
+        for g in sch.mgr.groups:
+            assert g.pool.in_use == 0
+        return reqs, sch, runner
+
+    base, sch0, _ = run(4000)
+    assert sch0.stats["retractions"] == 0
+    # all-keys pool short
+    reqs, sch, _ = run(60, conservativeness=0.3)
+    assert [r.output for r in reqs] == [r.output for r in base]
+    # windowed pool short (14 pages; a request being fed 16 tokens a step holds up to (12 + 16) / 4 + 1 = 8 of them
+    # there): admission counts that pool too, so nobody is let in only to be thrown out again
+    reqs, sch, runner = run(4000, shrink_window_pool=14)
+    assert [r.output for r in reqs] == [r.output for r in base]
+    assert sch.stats["retractions"] == 0, "admission ignored the windowed group's pool"
+    assert max(len(st) for st in runner.steps) <= 4
+    assert all(r.finish_reason.type == "length" for r in reqs)
