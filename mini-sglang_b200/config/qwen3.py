@@ -99,6 +99,11 @@ class Qwen3Config:
         return d
 
 
+# what a Qwen3 checkpoint calls the parts of a layer (mini_sglang/models/qwen3.py:137-160)
+QWEN3_LAYER_NAMES = {"input": "input_layernorm", "post_mixer": "post_attention_layernorm", "mixer": "self_attn",
+                     "feed_forward": "mlp"}
+
+
 def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
     """embed -> N x (norm, attention, norm, SwiGLU) -> norm -> head
     (mini_sglang/models/qwen3.py:129-232); every layer the same kind, run once in order."""
@@ -114,7 +119,7 @@ def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
             "qk_norm_eps": cfg.rms_norm_eps, "window": None})
         ffn = PartSpec("swiglu_mlp", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size})
         layers.append(LayerSpec(prefix=f"model.layers.{l}", mixer=mixer, feed_forward=ffn,
-                                norms={"input": norm, "post_mixer": norm}, position=rope))
+                                norms={"input": norm, "post_mixer": norm}, position=rope, names=QWEN3_LAYER_NAMES))
     return ModelSpec(
         architecture="Qwen3ForCausalLM",
         hidden_size=cfg.hidden_size,

@@ -30,7 +30,8 @@ class PartSpec:
 class LayerSpec:
     """One block: how the parts are arranged (`block`), and the parts themselves.
 
-    `prefix` is the checkpoint name prefix of the layer's tensors ("model.layers.3")."""
+    `prefix` is the checkpoint name prefix of the layer's tensors ("model.layers.3"); `names` says what
+    each part is called below it ("mixer" -> "self_attn" in a Qwen3 checkpoint)."""
 
     prefix: str
     mixer: PartSpec
@@ -38,6 +39,12 @@ class LayerSpec:
     norms: Dict[str, PartSpec]
     position: Optional[PartSpec] = None
     block: str = "prenorm_residual"
+    # checkpoint sub-names of the layer's parts under `prefix`: the block's role -> the name the checkpoint uses
+    # (roles "mixer", "feed_forward" and the keys of `norms`); a role that is not listed keeps its own name
+    names: Dict[str, str] = dataclasses.field(default_factory=dict)
+
+    def part_prefix(self, role: str) -> str:
+        return f"{self.prefix}.{self.names.get(role, role)}"
 
 
 @dataclasses.dataclass(frozen=True)

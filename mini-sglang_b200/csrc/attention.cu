@@ -1233,17 +1233,18 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
         if (d > 512) return MSGL_ERR_SIZE;
         const size_t smem = simt_smem_bytes(d);
         if (smem > 227 * 1024) return MSGL_ERR_SIZE;
-        static size_t simt_attr[2] = {0, 0};   // largest size already granted per element type
+        static size_t simt_attr[MSGL_MAX_DEVICES][2] = {};   // largest size already granted per device and element type
+        size_t* granted = simt_attr[msgl_device()];
         if (dtype == MSGL_F32) {
-            if (smem > 48 * 1024 && smem > simt_attr[0]) {
+            if (smem > 48 * 1024 && smem > granted[0]) {
                 cudaFuncSetAttribute(attn_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                simt_attr[0] = smem;
+                granted[0] = smem;
             }
             attn_simt_kernel<float><<<grid, SIMT_THREADS, smem, stream>>>(p);
         } else if (dtype == MSGL_BF16) {
-            if (smem > 48 * 1024 && smem > simt_attr[1]) {
+            if (smem > 48 * 1024 && smem > granted[1]) {
                 cudaFuncSetAttribute(attn_simt_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                simt_attr[1] = smem;
+                granted[1] = smem;
             }
             attn_simt_kernel<__nv_bfloat16><<<grid, SIMT_THREADS, smem, stream>>>(p);
         } else {
@@ -1256,10 +1257,10 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
     if (variant == 1) {
         const size_t smem = mma_smem_bytes<MSGL_HEAD_DIM>();
-        static bool attr_set = false;   // set once, outside any stream capture (the first launch is never captured)
-        if (!attr_set) {
+        static MsglOncePerDevice attr_set;   // set once per device, outside any stream capture (the first launch is never captured)
+        if (attr_set.due()) {
             cudaFuncSetAttribute(attn_mma_kernel<MSGL_HEAD_DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            attr_set = true;
+            attr_set.mark();
         }
         attn_mma_kernel<MSGL_HEAD_DIM><<<grid, MMA_THREADS, smem, stream>>>(p);
     } else if (variant == 2) {
@@ -1271,11 +1272,11 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
             const size_t smem = sizeof(__nv_bfloat16) * (size_t)NW * ST * DEC_WT * (DT + 8);
             const int C = G <= 8 ? 8 : 16;
             grid.y = n_kv;      // G <= C: one chunk
-            static bool attr_set = false;
-            if (!attr_set) {
+            static MsglOncePerDevice attr_set;
+            if (attr_set.due()) {
                 cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                attr_set = true;
+                attr_set.mark();
             }
             if (C == 8) msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 1>, grid, dim3(NW * 32), smem, stream, p);
             else msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 2>, grid, dim3(NW * 32), smem, stream, p);
@@ -1283,10 +1284,10 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
             constexpr int ST = (MSGL_HEAD_DIM <= 128) ? MSGL_DEC_STAGES : 2;   // the ring must fit 227 KB
             const size_t smem = sizeof(__nv_bfloat16) * ((size_t)16 * (MSGL_HEAD_DIM + 8) +
                                                          (size_t)NW * ST * 2 * DEC_WT * (MSGL_HEAD_DIM + 8));
-            static bool attr_set = false;
-            if (!attr_set) {
+            static MsglOncePerDevice attr_set;
+            if (attr_set.due()) {
                 cudaFuncSetAttribute(attn_decode_kernel<MSGL_HEAD_DIM, NW, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                attr_set = true;
+                attr_set.mark();
             }
             attn_decode_kernel<MSGL_HEAD_DIM, NW, ST><<<grid, NW * 32, smem, stream>>>(p);
         }
@@ -1321,12 +1322,12 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
     const int G = n_q / n_kv;
     const int n_chunks = G <= TC_ROWS ? 1 : (G + TC_ROWS - 1) / TC_ROWS;
     const size_t smem = (size_t)TC_SMEM_BYTES + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {      // first call, never inside a stream capture
+    static MsglOncePerDevice attr_set;
+    if (attr_set.due()) {      // first call on this device, never inside a stream capture
         if (cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
             cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM_ALLOC) != cudaSuccess)
             return msgl_check_launch();
-        attr_set = true;
+        attr_set.mark();
     }
     // TMA boxes are whole pages (or 128-row pieces of larger ones): page sizes 8, 16, 32, 64, 128, 256, ...; the cache
     // base must be 128-byte aligned.  Anything else gathers rows with cp.async.
@@ -1336,9 +1337,7 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
     if (pow2 && page_size >= 8 && cache_pages > 0 && ((((uintptr_t)k_cache | (uintptr_t)v_cache) & 127) == 0)) {
         const int box = page_size < TC_KT ? page_size : TC_KT;
         const long long rows = (long long)cache_pages * n_kv * page_size;
-        const CUtensorMap* km = tc_matrix_map(k_cache, rows, 128, 256, box);
-        const CUtensorMap* vm = tc_matrix_map(v_cache, rows, 128, 256, box);
-        if (km != nullptr && vm != nullptr) { kmap = *km; vmap = *vm; tma_box = box; }
+        if (tc_matrix_map(k_cache, rows, 128, 256, box, &kmap) && tc_matrix_map(v_cache, rows, 128, 256, box, &vmap)) tma_box = box;
     }
     if (version == 2) {
         if (tma_box == 0) return MSGL_ERR_SIZE;

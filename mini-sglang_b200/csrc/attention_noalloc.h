@@ -17,9 +17,12 @@
 //     function is ever called.
 //   * A call needs max_split * B * n_q * (d + 2) floats.  Larger problems are refused with
 //     MSGL_ERR_SCRATCH (5); nothing is launched then.  Use msgl_attention with your own scratch.
-//   * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
-//     with that device current) and remembers it.  Make that first call during set-up, before any
-//     stream capture; later calls on the device do no set-up work.
+//   * The first call on each device does that device's set-up, with the device current: it looks
+//     up the array's device address (cudaGetSymbolAddress) and raises the kernels' limit of
+//     dynamic shared memory (cudaFuncSetAttribute), and remembers both per device.  Make that
+//     first call during set-up, before any stream capture, with the problem shapes you will use
+//     later (a group of more than 16 query heads per kv head takes another kernel than a small
+//     one); later calls on the device do no set-up work.
 //   * The function calls no cudaMalloc, cudaFree or any other allocating routine.
 //   * All calls share the one array, and it keeps what the last call left in it.  Nothing in it
 //     has to start at zero: every value a call reads was written earlier by that same call (each

@@ -125,6 +125,27 @@ static inline void msgl_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 blo
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// What a device needs once before a kernel's first launch there (function attributes, occupancy questions) is
+// remembered per device: a process may drive several, and an attribute set while one device is current does not
+// reach the others.
+#define MSGL_MAX_DEVICES 64
+static inline int msgl_device() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= MSGL_MAX_DEVICES) return 0;
+    return d;
+}
+struct MsglOncePerDevice {
+    bool done_[MSGL_MAX_DEVICES] = {};
+    bool due() const { return !done_[msgl_device()]; }       // true until mark() was called with this device current
+    void mark() { done_[msgl_device()] = true; }
+};
+static inline int msgl_sm_count() {
+    static int n[MSGL_MAX_DEVICES] = {};
+    const int d = msgl_device();
+    if (n[d] == 0 && cudaDeviceGetAttribute(&n[d], cudaDevAttrMultiProcessorCount, d) != cudaSuccess) n[d] = 0;
+    return n[d] > 0 ? n[d] : 1;
+}
+
 #include <stdio.h>
 static inline int msgl_check_launch() {
     const cudaError_t e = cudaGetLastError();

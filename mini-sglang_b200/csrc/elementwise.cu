@@ -549,7 +549,8 @@ MSGL_API int msgl_swiglu(const void* gu, void* out, int T_, int I, int dtype, cu
         return msgl_check_launch();
     }
     size_t blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    const size_t most = (size_t)msgl_sm_count() * 32;      // grid-stride beyond 32 blocks an SM
+    if (blocks > most) blocks = most;
     if (dtype == MSGL_F32)
         swiglu_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
     else if (dtype == MSGL_BF16)
@@ -572,7 +573,8 @@ __global__ void cast_from_f32_kernel(const float* __restrict__ in, T* __restrict
 MSGL_API int msgl_cast_from_f32(const float* in, void* out, long long n, int dtype, cudaStream_t stream) {
     if (n <= 0) return MSGL_OK;
     size_t blocks = ((size_t)n + 255) / 256;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    const size_t most = (size_t)msgl_sm_count() * 32;      // grid-stride beyond 32 blocks an SM
+    if (blocks > most) blocks = most;
     if (dtype == MSGL_F32)
         cast_from_f32_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>(in, (float*)out, (size_t)n);
     else if (dtype == MSGL_BF16)

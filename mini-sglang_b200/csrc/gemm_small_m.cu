@@ -194,15 +194,15 @@ MSGL_API int msgl_gemm_small_m(const void* W, const void* X, const void* bias, v
     const __nv_bfloat16* b = (const __nv_bfloat16*)bias;
     const int threads = GS_WARPS * 32;
     const size_t smem1 = (size_t)GS_WARPS * GS_PF * 3 * 32 * 16, smem2 = (size_t)GS_WARPS * GS_PF * 4 * 32 * 16;
-    static bool attr_set = false;
-    if (!attr_set) {      // first call, never inside a stream capture
+    static MsglOncePerDevice attr_set;
+    if (attr_set.due()) {      // first call on this device, never inside a stream capture
         cudaFuncSetAttribute(gemm_small_m_kernel<1, true, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
         cudaFuncSetAttribute(gemm_small_m_kernel<2, true, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
         cudaFuncSetAttribute(gemm_small_m_kernel<1, false, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
         cudaFuncSetAttribute(gemm_small_m_kernel<2, false, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
         cudaFuncSetAttribute(gemm_small_m_kernel<1, false, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
         cudaFuncSetAttribute(gemm_small_m_kernel<2, false, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-        attr_set = true;
+        attr_set.mark();
     }
     if (mode == 1) {
         if ((N & 15) || bias != nullptr) return MSGL_ERR_SIZE;

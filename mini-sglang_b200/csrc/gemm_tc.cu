@@ -390,26 +390,23 @@ MSGL_API int msgl_gemm_tc(const void* W, const void* X, const void* bias, void* 
     if (((uintptr_t)W | (uintptr_t)X | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
     const int I = N / 2;
     if (mode == 1 && ((N & 1) || (I & 7) || bias != nullptr)) return MSGL_ERR_SIZE;
-    const CUtensorMap* xm = tc_matrix_map(X, M, K, ldx * 2, 128);
-    const CUtensorMap* wm = tc_matrix_map(W, N, K, (long long)K * 2, 128);
-    if (xm == nullptr || wm == nullptr) return MSGL_ERR_SIZE;
-    static bool attr_set = false;
-    if (!attr_set) {      // first call, never inside a stream capture
+    CUtensorMap xm, wm;
+    if (!tc_matrix_map(X, M, K, ldx * 2, 128, &xm) || !tc_matrix_map(W, N, K, (long long)K * 2, 128, &wm)) return MSGL_ERR_SIZE;
+    static MsglOncePerDevice attr_set;
+    if (attr_set.due()) {      // first call on this device, never inside a stream capture
         if (cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM_ALLOC) != cudaSuccess ||
             cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM_ALLOC) != cudaSuccess)
             return msgl_check_launch();
-        attr_set = true;
+        attr_set.mark();
     }
     const int n_valid = mode == 1 ? I : N, bn_out = mode == 1 ? GT_BN / 2 : GT_BN;
     const long long tiles = (long long)((M + GT_BM - 1) / GT_BM) * ((n_valid + bn_out - 1) / bn_out);
-    int sms = 148, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = msgl_sm_count();
     const int grid = (int)(tiles < sms ? tiles : sms);
     if (mode == 1)
-        gemm_tc_kernel<true><<<grid, GT_THREADS, GT_SMEM_ALLOC, stream>>>(*xm, *wm, nullptr, (__nv_bfloat16*)out, M, N, K, ldo, I, (int*)status);
+        gemm_tc_kernel<true><<<grid, GT_THREADS, GT_SMEM_ALLOC, stream>>>(xm, wm, nullptr, (__nv_bfloat16*)out, M, N, K, ldo, I, (int*)status);
     else
-        gemm_tc_kernel<false><<<grid, GT_THREADS, GT_SMEM_ALLOC, stream>>>(*xm, *wm, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, M, N, K, ldo, 0,
+        gemm_tc_kernel<false><<<grid, GT_THREADS, GT_SMEM_ALLOC, stream>>>(xm, wm, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, M, N, K, ldo, 0,
                                                                            (int*)status);
     return msgl_check_launch();
 }
@@ -422,9 +419,8 @@ MSGL_API int msgl_gemm_tc2(const void* W, const void* X, const void* bias, void*
     if (((uintptr_t)W | (uintptr_t)X | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
     const int I = N / 2;
     if (mode == 1 && ((N & 1) || (I & 7) || bias != nullptr)) return MSGL_ERR_SIZE;
-    const CUtensorMap* xm = tc_matrix_map(X, M, K, ldx * 2, 128);
-    const CUtensorMap* wm = tc_matrix_map(W, N, K, (long long)K * 2, 128);
-    if (xm == nullptr || wm == nullptr) return MSGL_ERR_SIZE;
+    CUtensorMap xm, wm;
+    if (!tc_matrix_map(X, M, K, ldx * 2, 128, &xm) || !tc_matrix_map(W, N, K, (long long)K * 2, 128, &wm)) return MSGL_ERR_SIZE;
     const int n_valid = mode == 1 ? I : N, bn_out = mode == 1 ? 128 : 256;
     const long long tiles = (long long)((M + 255) / 256) * ((n_valid + bn_out - 1) / bn_out);
     cudaLaunchConfig_t cfg = {};
@@ -435,15 +431,15 @@ MSGL_API int msgl_gemm_tc2(const void* W, const void* X, const void* bias, void*
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.blockDim = dim3(GT2_THREADS); cfg.dynamicSmemBytes = GT2_SMEM_ALLOC; cfg.stream = stream; cfg.attrs = attr;
     cfg.numAttrs = msgl_pdl_enabled() ? 2 : 1;
-    static int max_pairs[2] = {0, 0};      // per mode: how many pairs the device holds at once (asked once, outside any capture)
+    static int pairs_of[MSGL_MAX_DEVICES][2] = {};      // per device and mode: how many pairs the device holds at once (asked once, outside any capture)
+    int* max_pairs = pairs_of[msgl_device()];
     if (max_pairs[mode] == 0) {
         cudaError_t e = mode == 1
             ? cudaFuncSetAttribute(gemm_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT2_SMEM_ALLOC)
             : cudaFuncSetAttribute(gemm_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT2_SMEM_ALLOC);
         if (e != cudaSuccess) return msgl_check_launch();
-        int sms = 148, dev = 0, n = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int sms = msgl_sm_count();
+        int n = 0;
         cfg.gridDim = dim3(2 * (sms / 2));
         e = mode == 1 ? cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<true>, &cfg)
                       : cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<false>, &cfg);
@@ -456,8 +452,8 @@ MSGL_API int msgl_gemm_tc2(const void* W, const void* X, const void* bias, void*
     __nv_bfloat16* o = (__nv_bfloat16*)out;
     int* st = (int*)status;
     const int Iarg = mode == 1 ? I : 0;
-    cudaError_t e = mode == 1 ? cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<true>, *xm, *wm, b, o, M, N, K, ldo, Iarg, st)
-                              : cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<false>, *xm, *wm, b, o, M, N, K, ldo, Iarg, st);
+    cudaError_t e = mode == 1 ? cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<true>, xm, wm, b, o, M, N, K, ldo, Iarg, st)
+                              : cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<false>, xm, wm, b, o, M, N, K, ldo, Iarg, st);
     (void)e;
     return msgl_check_launch();
 }

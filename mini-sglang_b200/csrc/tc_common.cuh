@@ -128,11 +128,12 @@ __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sy
 
 // Tensor maps of row-major bfloat16 matrices [rows x cols] (row pitch `pitch_bytes`), boxes of box_rows x 64 columns
 // with 128-byte swizzle, made once per (matrix, size) and kept.  The driver's encoder is looked up at run time;
-// nullptr if this driver has none or refuses the sizes.
+// false if this driver has none or refuses the sizes.  The map is copied out under the lock, so a later call that
+// empties the table cannot invalidate what an earlier call returned.
 typedef CUresult (*tc_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static const CUtensorMap* tc_matrix_map(const void* base, long long rows, long long cols, long long pitch_bytes, int box_rows) {
+static bool tc_matrix_map(const void* base, long long rows, long long cols, long long pitch_bytes, int box_rows, CUtensorMap* out) {
     static std::mutex mu;
     static std::map<std::tuple<const void*, long long, long long, long long, int>, CUtensorMap> maps;
     static tc_encode_fn encode = nullptr;
@@ -146,10 +147,10 @@ static const CUtensorMap* tc_matrix_map(const void* base, long long rows, long l
             qr == cudaDriverEntryPointSuccess)
             encode = (tc_encode_fn)fn;
     }
-    if (encode == nullptr) return nullptr;
+    if (encode == nullptr) return false;
     const auto key = std::make_tuple(base, rows, cols, pitch_bytes, box_rows);
     auto it = maps.find(key);
-    if (it != maps.end()) return &it->second;
+    if (it != maps.end()) { *out = it->second; return true; }
     if (maps.size() > 4096) maps.clear();                     // activations come and go: do not grow without bound
     CUtensorMap m;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -158,6 +159,8 @@ static const CUtensorMap* tc_matrix_map(const void* base, long long rows, long l
     const cuuint32_t estr[2] = {1, 1};
     if (encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return nullptr;
-    return &maps.emplace(key, m).first->second;
+        return false;
+    maps.emplace(key, m);
+    *out = m;
+    return true;
 }

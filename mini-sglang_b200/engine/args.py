@@ -41,6 +41,7 @@ class EngineArgs:
     chunk_size: int = 8192                   # longest portion of one prompt in one step
     max_context_len: Optional[int] = None    # default: the model's max_position_embeddings
     disable_overlap: bool = False            # read every step's tokens before the next step is launched
+    profile_dir: str = "traces"              # where --profile saves its per-step records
     init_new_token_ratio: float = dataclasses.field(default_factory=lambda: _env("SGLANG_INIT_NEW_TOKEN_RATIO", 0.7))
     min_new_token_ratio_factor: float = dataclasses.field(default_factory=lambda: _env("SGLANG_MIN_NEW_TOKEN_RATIO_FACTOR", 0.14))
     new_token_ratio_decay_steps: int = dataclasses.field(default_factory=lambda: int(_env("SGLANG_NEW_TOKEN_RATIO_DECAY_STEPS", 600)))
@@ -69,33 +70,34 @@ class EngineArgs:
     @staticmethod
     def add_cli_args(parser: argparse.ArgumentParser) -> None:
         d = EngineArgs
-        parser.add_argument("--model", type=str, required=True, help="Path to the model directory.")
-        parser.add_argument("--page_size", type=int, default=d.page_size, help="Page size for KV cache.")
-        parser.add_argument("--tp_size", type=int, default=1, help="Tensor parallelism degree (only 1).")
-        parser.add_argument("--device", type=str, default="cuda", help="Device to run the model on (cuda).")
+        parser.add_argument("--model", type=str, required=True, help="Model folder: config.json and *.safetensors (and a tokenizer, for text prompts).")
+        parser.add_argument("--page_size", type=int, default=d.page_size, help="Tokens per page of the key/value cache (a power of two from 8 on suits the TMA kernels; 1 is allowed).")
+        parser.add_argument("--tp_size", type=int, default=1, help="Number of GPUs the model is split over; this engine takes 1 only.")
+        parser.add_argument("--device", type=str, default="cuda", help="Where the model runs; a CUDA device, nothing else.")
         parser.add_argument("--gpu_memory_utilization", type=float, default=d.gpu_memory_utilization,
-                            help="GPU memory utilization percentage.")
-        parser.add_argument("--max_num_reqs", type=int, default=d.max_num_reqs, help="Maximum number of requests to handle.")
+                            help="Share of the GPU's memory that weights and cache together may fill (0..1).")
+        parser.add_argument("--max_num_reqs", type=int, default=d.max_num_reqs, help="Most requests that may hold a cache slot at one time.")
         parser.add_argument("--schedule_policy", type=str, default=d.schedule_policy,
-                            choices=["fcfs", "lof", "random", "lpm", "dfs-weight"], help="Scheduling policy to use.")
+                            choices=["fcfs", "lof", "random", "lpm", "dfs-weight"], help="Order in which waiting requests are admitted: lpm (longest cached prefix first), fcfs, lof (largest max_new_tokens first), random.")
         parser.add_argument("--log_level", type=str, default=d.log_level,
-                            choices=["DEBUG", "INFO", "WARNING", "ERROR", "CRITICAL"], help="Logging level.")
-        parser.add_argument("--random_seed", type=int, default=None, help="Random seed; random if not set.")
-        parser.add_argument("--profile", action="store_true", help="Record per-step timings.")
-        parser.add_argument("--disable_radix_cache", action="store_true", help="Disable the radix cache mechanism.")
-        parser.add_argument("--disable_cuda_graph", action="store_true", help="Disable the use of CUDA graphs.")
+                            choices=["DEBUG", "INFO", "WARNING", "ERROR", "CRITICAL"], help="Threshold of the engine's log output.")
+        parser.add_argument("--random_seed", type=int, default=None, help="Seed of sampling and of --dummy_load weights; drawn at random when absent.")
+        parser.add_argument("--profile", action="store_true", help="Time every step on host and device, mark steps and layers with NVTX ranges, and save one JSON record per step under --profile_dir.")
+        parser.add_argument("--disable_radix_cache", action="store_true", help="Never share prompt prefixes between requests.")
+        parser.add_argument("--disable_cuda_graph", action="store_true", help="Launch decode steps kernel by kernel instead of replaying a captured graph.")
         parser.add_argument("--max_capture_bs", type=int, default=d.max_capture_bs,
-                            help="Maximum batch size for CUDA graph capture.")
+                            help="Largest decode batch that gets a captured graph; larger ones are launched kernel by kernel.")
         parser.add_argument("--schedule-conservativeness", type=float, default=d.schedule_conservativeness,
-                            help="A larger value means more conservative scheduling.")
+                            help="Scales the estimate of how many tokens a request will still generate when it is admitted: above 1 admits fewer at a time, below 1 more (and retracts when wrong).")
         parser.add_argument("--max_prefill_tokens", type=int, default=d.max_prefill_tokens,
-                            help="Maximum number of tokens in one step's batch.")
+                            help="Token budget of one step: decoded tokens plus prompt portions.")
         parser.add_argument("--dummy_load", action="store_true",
                             help="Random weights for the configuration in --model instead of its checkpoint.")
         parser.add_argument("--dtype", type=str, default=d.dtype, choices=["bfloat16", "float32"])
         parser.add_argument("--num_pages", type=int, default=None, help="Cache size in pages (default: from memory).")
         parser.add_argument("--chunk_size", type=int, default=d.chunk_size, help="Longest prompt portion per step.")
         parser.add_argument("--max_context_len", type=int, default=None)
+        parser.add_argument("--profile_dir", type=str, default=d.profile_dir, help="Folder for the records of --profile.")
         parser.add_argument("--disable_overlap", action="store_true",
                             help="Read a step's tokens before launching the next step (no look-ahead decode).")
 

@@ -10,11 +10,14 @@ token ids always work.
 
 from __future__ import annotations
 
+import asyncio
+import atexit
+import json
 import logging
 import os
 import time
 import uuid
-from typing import Dict, Iterator, List, Optional, Sequence, Union
+from typing import AsyncIterator, Dict, Iterator, List, Optional, Sequence, Union
 
 import torch
 
@@ -67,6 +70,12 @@ class Engine:
             lookahead=not args.disable_overlap)
         self.tokenizer = _load_tokenizer(args.model)
         self.step_times: List[float] = []
+        self.step_records: List[Dict] = []          # --profile: one record per step
+        self._profile_written = 0                   # records already saved
+        if args.profile:
+            from ..parts import model as _model
+            _model.NVTX_RANGES = True
+            atexit.register(self.write_profile)
         self._load_seconds = time.time() - t0
         logger.info("engine ready in %.1f s: %d cache pages of %d tokens", self._load_seconds,
                     self.runner.mgr.groups[0].pool.num_pages if self.runner.mgr.groups else 0, args.page_size)
@@ -92,14 +101,54 @@ class Engine:
     def step(self) -> List[StepOutput]:
         """One scheduler step: the public unit of work (a batch through the model, sampling,
         bookkeeping).  Returns what each sampled request got; unless args.disable_overlap, these are the
-        tokens of the step that the call before launched (they travel to the host while the next step runs)."""
-        if self.args.profile:
-            t0 = time.perf_counter()
-            out = self.scheduler.step()
-            torch.cuda.synchronize()
-            self.step_times.append(time.perf_counter() - t0)
-            return out
-        return self.scheduler.step()
+        tokens of the step that the call before launched (they travel to the host while the next step runs).
+
+        With args.profile every step is bracketed by an NVTX range and two CUDA events, waited for, and
+        recorded: what the step held (batch, tokens, prompt tokens, CUDA graph or not), its time on the host
+        and on the device, and the number of this engine's kernels it launched; `write_profile` saves the list."""
+        if not self.args.profile:
+            return self.scheduler.step()
+        from .. import ops
+        steps_before, launches_before = self.scheduler.stats["steps"], ops.LAUNCHES
+        torch.cuda.nvtx.range_push(f"step {steps_before}")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        out = self.scheduler.step()
+        e1.record()
+        host_ms = (time.perf_counter() - t0) * 1e3
+        torch.cuda.synchronize()
+        torch.cuda.nvtx.range_pop()
+        self.step_times.append(time.perf_counter() - t0)
+        if self.scheduler.stats["steps"] > steps_before:          # a batch was launched
+            self.step_records.append({**self.scheduler.last_step, "host_ms": round(host_ms, 4),
+                                      "device_ms": round(e0.elapsed_time(e1), 4),
+                                      "wall_ms": round(self.step_times[-1] * 1e3, 4),
+                                      "kernels": ops.LAUNCHES - launches_before, "sampled": len(out)})
+        return out
+
+    def write_profile(self, path: Optional[str] = None) -> Optional[str]:
+        """Save the per-step records of --profile as JSON (default: traces/steps_<time>_<pid>.json under
+        args.profile_dir, as the reference keeps its traces under traces/, mini_sglang/utils/profiler.py:16-58).
+        Called at shutdown() and at interpreter exit; a second call without new steps writes nothing."""
+        if not self.args.profile or not self.step_records or (path is None and self._profile_written == len(self.step_records)):
+            return None
+        if path is None:
+            os.makedirs(self.args.profile_dir, exist_ok=True)
+            path = os.path.join(self.args.profile_dir, f"steps_{time.strftime('%Y%m%d-%H%M%S')}_{os.getpid()}.json")
+        kinds = {}
+        for r in self.step_records:
+            k = kinds.setdefault(r["kind"], {"steps": 0, "tokens": 0, "device_ms": 0.0, "host_ms": 0.0})
+            k["steps"] += 1
+            k["tokens"] += r["tokens"]
+            k["device_ms"] += r["device_ms"]
+            k["host_ms"] += r["host_ms"]
+        with open(path, "w") as f:
+            json.dump({"model": self.args.model, "dtype": self.args.dtype, "page_size": self.args.page_size,
+                       "summary": kinds, "scheduler": dict(self.scheduler.stats), "steps": self.step_records}, f)
+        self._profile_written = len(self.step_records)
+        logger.info("[profile] %d steps written to %s", len(self.step_records), path)
+        return path
 
     def _result(self, req: Req, t_start: float) -> Dict:
         out = req.output
@@ -163,4 +212,32 @@ class Engine:
                                      **self.scheduler.stats}]}
 
     def shutdown(self) -> None:
-        pass
+        """One process: nothing to stop.  Saves the step records of --profile."""
+        self.write_profile()
+
+    # -- asyncio face (the reference's Engine.async_generate, mini_sglang/entrypoints/engine.py:63-85) -----
+    async def async_generate(self, prompt: Optional[str] = None, sampling_params: Optional[Dict] = None,
+                             input_ids: Optional[List[int]] = None, stream: bool = False):
+        """`await engine.async_generate(...)` -> dict, or with stream=True an async iterator of dicts, one per
+        new token.  Several coroutines may generate at once: their requests run as one batch, whichever coroutine
+        happens to hold the engine makes the next step, and every step is followed by a yield to the event loop."""
+        req = self.add_request(prompt, sampling_params, input_ids)
+        t0 = time.time()
+        if stream:
+            return self._astream(req, t0)
+        while not req.finished:
+            self.step()
+            await asyncio.sleep(0)
+        return self._result(req, t0)
+
+    async def _astream(self, req: Req, t0: float) -> AsyncIterator[Dict]:
+        sent = 0
+        while True:
+            if not req.finished:
+                self.step()
+                await asyncio.sleep(0)
+            if len(req.output) > sent or req.finished:
+                sent = len(req.output)
+                yield self._result(req, t0)
+            if req.finished:
+                return

@@ -39,6 +39,7 @@ from __future__ import annotations
 
 import dataclasses
 import itertools
+import logging
 import random
 import time
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -46,6 +47,9 @@ from typing import Dict, List, Optional, Sequence, Tuple
 from ..cache import OutOfPages, PrefixTree
 from ..sampling import SamplingParams
 from .step import StepEntry
+
+logger = logging.getLogger("mini_sglang_b200.scheduler")
+DECODE_LOG_EVERY = 64     # a line for every step with prompt tokens, and for every 64th step without (mini_sglang/managers/scheduler.py:457-491)
 
 IN_BATCH_PREFIX = 32      # tokens two requests must share for the later one to wait (scheduler_policy.py:18-19)
 
@@ -167,6 +171,10 @@ class Scheduler:
         self._host_flip = 0
         self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "cached_tokens": 0, "retractions": 0,
                       "evicted_pages": 0, "aborted": 0, "finished": 0}
+        self.last_step: Dict[str, object] = {}     # what the last launched step held (for logs and profiles)
+        self._decode_steps = 0                     # steps without prompt tokens since the last one with
+        self._decode_tokens = 0
+        self._decode_t0 = time.time()
 
     # -- requests --------------------------------------------------------------------------
     def add_request(self, req: Req) -> None:
@@ -484,7 +492,8 @@ class Scheduler:
             return outputs
 
         # 4. run the batch
-        entries, sampled = [], []
+        entries, sampled, fed_prompt = [], [], []
+        prompt_tokens = cached = 0
         for r, n in plan:
             start = int(self.mgr.length[r.slot])
             last = start + n == len(r.tokens)
@@ -495,14 +504,17 @@ class Scheduler:
                 self.stats["decode_tokens"] += 1
             else:
                 self.stats["prefill_tokens"] += n
+                prompt_tokens += n
+                cached += start
+                fed_prompt.append(r)
         logits = self.runner.step(entries)
         self.stats["steps"] += 1
+        self._note_step(len(plan), sum(n for _, n in plan), prompt_tokens, cached)
         if self.tree is not None:
             # a prompt's full pages become shareable as soon as the step that computes them is launched
             # (later steps run after it on the same stream), portion by portion
-            for (r, n), e in zip(plan, entries):
-                if not (n == 1 and int(self.mgr.length[r.slot]) > r.n_prompt):
-                    self._insert(r)
+            for r in fed_prompt:
+                self._insert(r)
         flight = self._sample(logits, sampled)
         if self.lookahead:
             self._inflight = flight          # read at the next call
@@ -515,6 +527,42 @@ class Scheduler:
             self.stats["aborted"] += 1
             outputs.append(StepOutput(r, None, True))
         return outputs
+
+    # -- what a step held -------------------------------------------------------------------
+    def token_usage(self) -> Tuple[int, int, int, float]:
+        """(tokens in use, free, evictable, share in use) of the first cache group, in tokens."""
+        if not self.mgr.groups:
+            return 0, 0, 0, 0.0
+        total = self.mgr.groups[0].pool.num_pages * self.P
+        free = self.mgr.available_pages(0) * self.P
+        ev = (self.tree.evictable_pages if self.tree is not None else 0) * self.P
+        used = total - free - ev
+        return used, free, ev, used / max(total, 1)
+
+    def _note_step(self, batch: int, n_tokens: int, prompt_tokens: int, cached: int) -> None:
+        """Counters of the step just launched, and the log lines: one for every step that feeds prompt
+        tokens, one for every DECODE_LOG_EVERY-th step of single tokens."""
+        graph = bool(getattr(self.runner, "last_step_used_graph", False))
+        self.last_step = {"step": self.stats["steps"], "kind": "extend" if prompt_tokens else "decode", "batch": batch,
+                          "tokens": n_tokens, "prompt_tokens": prompt_tokens, "cuda_graph": graph,
+                          "waiting": len(self.waiting), "running": len(self.running),
+                          "new_token_ratio": round(self.new_token_ratio, 4)}
+        if prompt_tokens:
+            self._decode_steps = self._decode_tokens = 0
+            self._decode_t0 = time.time()
+            logger.info("Extend #BS: %d  #Tokens: %d  #PrefixTokens: %d  #ExtendTokens: %d  #DecodeTokens: %d  #waiting-queue: %d",
+                        batch, cached + prompt_tokens, cached, prompt_tokens, n_tokens - prompt_tokens, len(self.waiting))
+            return
+        self._decode_steps += 1
+        self._decode_tokens += batch
+        if self._decode_steps % DECODE_LOG_EVERY == 1 and logger.isEnabledFor(logging.INFO):
+            now = time.time()
+            tps = self._decode_tokens / (now - self._decode_t0) if now > self._decode_t0 and self._decode_steps > 1 else 0.0
+            used, free, ev, share = self.token_usage()
+            self._decode_t0, self._decode_tokens = now, 0
+            logger.info("Decode #BS: %d  #Tokens: %d %d %d (%.2f)  #TPS(token/s): %.2f  #CUDA-Graph: %s  #waiting-queue: %d  "
+                        "#new-token-ratio: %.3f", batch, used, free, ev, share, tps, graph, len(self.waiting),
+                        self.new_token_ratio)
 
     # -- sampling and results ---------------------------------------------------------------
     def _sample(self, logits, sampled: List[Req]) -> Optional[_InFlight]:
@@ -600,6 +648,7 @@ class Scheduler:
         self.stats["decode_tokens"] += len(nxt)
         logits = self.runner.step(entries, prev_ids=flight.ids)
         self.stats["steps"] += 1
+        self._note_step(len(nxt), len(nxt), 0, 0)
         successor = self._sample(logits, sampled)
         outputs = self._collect(flight, successor)
         self._inflight = successor

@@ -31,7 +31,6 @@ from ..parts import BuildEnv, DecoderModel, GroupContext, KVCacheView, StateCach
 from ..weights import CheckpointSource, RandomSource
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
-SM_COUNT = 148
 MAX_KV_SPLIT = 16
 MIN_KEYS_PER_SPLIT = 256
 LONG_REQUEST_FACTOR = 1.5         # a request beyond this many times the mean load per block is cut up (1.0, 1.25, 1.5 measured: 1.5 best)
@@ -135,19 +134,20 @@ def _fewest_splits_as_fast(keys: int, ns: int) -> int:
 
 
 def plan_kv_splits(q_lens: Sequence[int], kv_lens: Sequence[int], *, n_kv: int, group: int, blocks_per_sm: int,
-                   tile_tokens: int, window: Optional[int], cap: int, long_cap: Optional[int] = None) -> List[int]:
+                   tile_tokens: int, window: Optional[int], cap: int, long_cap: Optional[int] = None,
+                   sm_count: int) -> List[int]:
     """kv splits per request of one attention launch.  Only query runs that fit one tile of the decode kernel
     (`tile_tokens`) are split (the prefill kernels take whole key ranges).  Two reasons to split: the launch
     would otherwise leave most of the SMs idle (few requests: every request is cut alike), or one request is
     much longer than the launch's mean load per resident block, so that its single block would still run when
     all others are done (it is cut into pieces of about that load).  `cap` bounds the first kind of cut,
-    `long_cap` (default: the same) the second."""
+    `long_cap` (default: the same) the second.  `sm_count`: the device's number of SMs."""
     long_cap = cap if long_cap is None else long_cap
     if cap <= 1 and long_cap <= 1:
         return [1] * len(q_lens)
     chunks = 1 if group <= 16 else -(-group // 16)
     heads = n_kv * chunks
-    slots = SM_COUNT * blocks_per_sm
+    slots = sm_count * blocks_per_sm
     blocks = sum(-(-q // tile_tokens) for q in q_lens) * heads
     want = slots // max(blocks, 1)                    # fill the SMs once, not more
     keys = [min(kv, window + q) if window else kv for q, kv in zip(q_lens, kv_lens)]
@@ -168,8 +168,8 @@ def plan_kv_splits(q_lens: Sequence[int], kv_lens: Sequence[int], *, n_kv: int, 
     cut = [i for i, q in enumerate(q_lens) if q <= tile_tokens]
     if cut and long_cap >= 2 and all(n == 1 for n in out):
         n_blocks = len(cut) * heads
-        uneven = -(-n_blocks // SM_COUNT) * SM_COUNT / n_blocks - 1.0
-        uneven_halved = -(-2 * n_blocks // SM_COUNT) * SM_COUNT / (2 * n_blocks) - 1.0
+        uneven = -(-n_blocks // sm_count) * sm_count / n_blocks - 1.0
+        uneven_halved = -(-2 * n_blocks // sm_count) * sm_count / (2 * n_blocks) - 1.0
         if uneven >= 0.08 and uneven_halved <= uneven - 0.04 and sum(keys[i] for i in cut) >= BALANCE_MIN_KEYS * len(cut):
             for i in cut:
                 if keys[i] >= 2 * MIN_KEYS_PER_SPLIT:
@@ -183,6 +183,7 @@ class ModelRunner:
                  max_step_tokens: int = 8192, gpu_memory_utilization: float = 0.9, device: str = "cuda:0",
                  use_cuda_graph: bool = True, max_capture_bs: int = 128):
         self.device = self._init_device(device)
+        self.sm_count = self._sm_count()
         self.dtype = DTYPES[dtype]
         if self.dtype == torch.float32:
             ops.set_true_fp32()
@@ -229,6 +230,7 @@ class ModelRunner:
         self._graphs: Dict[Tuple[int, Tuple[int, ...], bool], _Graph] = {}
         self._graph_pool = None
         self.kernel_launches = 0
+        self.last_step_used_graph = False
         self._group_geom = []
         for g in self.mgr.groups:
             cid = g.cache_ids[0]
@@ -245,6 +247,9 @@ class ModelRunner:
         dev = torch.device(device)
         torch.cuda.set_device(dev)
         return dev
+
+    def _sm_count(self) -> int:
+        return int(torch.cuda.get_device_properties(self.device).multi_processor_count)
 
     def _alloc_pinned(self, n: int) -> torch.Tensor:
         return torch.empty(n, dtype=torch.int32, pin_memory=True)
@@ -285,7 +290,7 @@ class ModelRunner:
                      long_cap: Optional[int] = None) -> List[int]:
         n_kv, G, per_sm, qt = self._group_geom[gi]
         return plan_kv_splits(q_lens, kv_lens, n_kv=n_kv, group=G, blocks_per_sm=per_sm, tile_tokens=qt,
-                              window=self.mgr.groups[gi].window, cap=cap, long_cap=long_cap)
+                              window=self.mgr.groups[gi].window, cap=cap, long_cap=long_cap, sm_count=self.sm_count)
 
     def _fill(self, host: np.ndarray, lay: _Layout, entries: Sequence[StepEntry], starts: Sequence[int],
               want_rows: Sequence[int], nsplits: Sequence[Sequence[int]], pad_to: int = 0) -> None:
@@ -421,7 +426,8 @@ class ModelRunner:
         # arrived, and queue a fresh one after this step (every step with prompt portions, else now and then)
         ops.raise_if_failed()
         self._steps_run += 1
-        if self.use_cuda_graph and all_last and B <= self.max_capture_bs:
+        self.last_step_used_graph = bool(self.use_cuda_graph and all_last and B <= self.max_capture_bs)
+        if self.last_step_used_graph:
             logits = self._step_graph(entries, starts, q_lens, kv_lens, prev_ids)
             if self._steps_run % 32 == 0:
                 ops.poll_status()
@@ -467,7 +473,7 @@ class ModelRunner:
         n_kv, G, per_sm, _ = self._group_geom[gi]
         chunks = 1 if G <= 16 else -(-G // 16)
         blocks = b * n_kv * chunks
-        return max(1, min(MAX_KV_SPLIT, (SM_COUNT * per_sm) // blocks))
+        return max(1, min(MAX_KV_SPLIT, (self.sm_count * per_sm) // blocks))
 
     def _step_graph(self, entries, starts, q_lens, kv_lens, prev_ids=None) -> torch.Tensor:
         B = len(entries)

@@ -31,6 +31,15 @@ from ..weights.loader import TensorDecl
 class BuildEnv:
     dtype: torch.dtype
     device: torch.device
+    _shared: Dict[Any, Any] = dataclasses.field(default_factory=dict, repr=False)
+
+    def shared(self, spec: PartSpec, make: Callable[[], Any]):
+        """One part per distinct (kind, parameters) among the parts that hold no checkpoint tensors of a
+        layer's own (position encodings: 36 layers with the same rotation share one table)."""
+        key = (spec.kind, tuple(sorted((k, repr(v)) for k, v in spec.params.items())))
+        if key not in self._shared:
+            self._shared[key] = make()
+        return self._shared[key]
 
 
 class Part:

@@ -13,22 +13,21 @@ class PreNormResidualBlock(Block):
 
     The block returns its feed-forward output un-added together with the stream, so the next
     norm (the next block's, or the model's final norm) fuses the sum, as the reference does
-    (mini_sglang/models/qwen3.py:162-178).  Norm names: "input" and "post_mixer", stored in the
-    checkpoint as input_layernorm / post_attention_layernorm; mixer under self_attn, feed-forward
-    under mlp."""
-
-    NORM_NAMES = {"input": "input_layernorm", "post_mixer": "post_attention_layernorm"}
+    (mini_sglang/models/qwen3.py:162-178).  Roles: norms "input" and "post_mixer", "mixer", "feed_forward";
+    what the checkpoint calls each of them below the layer's prefix comes from the layer description
+    (`LayerSpec.names`).  Position encodings with equal parameters are one object shared by all layers."""
 
     def __init__(self, layer_spec, env: BuildEnv):
         super().__init__(None, layer_spec.prefix, env)
-        p = layer_spec.prefix
+        at = layer_spec.part_prefix
         self.position = None
         if layer_spec.position is not None:
-            self.position = build_part(POSITION_ENCODINGS, "position encoding", layer_spec.position, p, env)
-        self.norm_in = build_part(NORMS, "norm", layer_spec.norms["input"], f"{p}.{self.NORM_NAMES['input']}", env)
-        self.norm_post = build_part(NORMS, "norm", layer_spec.norms["post_mixer"], f"{p}.{self.NORM_NAMES['post_mixer']}", env)
-        self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, f"{p}.self_attn", env, position=self.position)
-        self.ffn = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward, f"{p}.mlp", env)
+            self.position = env.shared(layer_spec.position, lambda: build_part(
+                POSITION_ENCODINGS, "position encoding", layer_spec.position, layer_spec.prefix, env))
+        self.norm_in = build_part(NORMS, "norm", layer_spec.norms["input"], at("input"), env)
+        self.norm_post = build_part(NORMS, "norm", layer_spec.norms["post_mixer"], at("post_mixer"), env)
+        self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, at("mixer"), env, position=self.position)
+        self.ffn = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward, at("feed_forward"), env)
 
     def parts(self):
         return [p for p in (self.position, self.norm_in, self.mixer, self.norm_post, self.ffn) if p is not None]

@@ -18,6 +18,9 @@ from .base import BLOCKS, EMBEDDINGS, HEADS, NORMS, BuildEnv, build_part
 from .context import StepContext
 
 
+NVTX_RANGES = False      # set by the engine's --profile: NVTX ranges around every run of a layer
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec, env: BuildEnv):
         self.spec, self.env = spec, env
@@ -65,6 +68,8 @@ class DecoderModel:
     # -- compute -----------------------------------------------------------------------
     def forward(self, ctx: StepContext, caches: Dict[int, object], want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """-> float32 logits [len(want_rows), vocab] (all T rows if want_rows is None)."""
+        if NVTX_RANGES:
+            return self._forward_marked(ctx, caches, want_rows)
         residual = self.embedding.forward(ctx.input_ids)
         delta = None
         for run in self.schedule:
@@ -72,6 +77,25 @@ class DecoderModel:
             delta, residual = self.layers[run.layer].forward(delta, residual, ctx, cache, run.writes_cache)
         h = self.final_norm.forward(x=delta, residual=residual, rows=want_rows)
         return self.head.forward(h)
+
+    def _forward_marked(self, ctx, caches, want_rows):
+        """The same with an NVTX range around the embedding, every run of a layer and the head, for profilers
+        that show them on the timeline."""
+        nvtx = torch.cuda.nvtx
+        nvtx.range_push("embedding")
+        residual = self.embedding.forward(ctx.input_ids)
+        nvtx.range_pop()
+        delta = None
+        for i, run in enumerate(self.schedule):
+            nvtx.range_push(f"run {i}: layer {run.layer}")
+            cache = caches.get(run.cache) if run.cache is not None else None
+            delta, residual = self.layers[run.layer].forward(delta, residual, ctx, cache, run.writes_cache)
+            nvtx.range_pop()
+        nvtx.range_push("final norm + head")
+        h = self.final_norm.forward(x=delta, residual=residual, rows=want_rows)
+        out = self.head.forward(h)
+        nvtx.range_pop()
+        return out
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, TensorDecl]:

@@ -25,6 +25,9 @@ class RotaryNeox(PositionEncoding):
             raise ValueError("rotary_dim must be even and at most head_dim")
         self._table: Optional[torch.Tensor] = None
 
+    def load(self, src) -> None:
+        self.rotary_table()      # made with the weights, so that the memory left for the cache is measured after it
+
     def rotary_table(self) -> torch.Tensor:
         if self._table is None:
             # built on the host in float32, operation by operation as the reference does, so the

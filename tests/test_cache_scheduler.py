@@ -445,8 +445,9 @@ def test_policies_order():
 # the step function's plan of kv splits (pure arithmetic on the host)
 # ---------------------------------------------------------------------------------------
 def test_kv_split_plan():
-    from mini_sglang_b200.engine.step import MIN_KEYS_PER_SPLIT, SM_COUNT, plan_kv_splits
-    geo = dict(n_kv=8, group=4, blocks_per_sm=4, tile_tokens=2, window=None)
+    from mini_sglang_b200.engine.step import MIN_KEYS_PER_SPLIT, plan_kv_splits
+    SM_COUNT = 148                     # a B200's
+    geo = dict(n_kv=8, group=4, blocks_per_sm=4, tile_tokens=2, window=None, sm_count=SM_COUNT)
     slots = SM_COUNT * 4
     # few requests: everybody is cut alike, so that the blocks fill the SMs once
     # (9 blocks a request would fill the 592 places, but 4,096 keys are 256 units of 16 for 4 warps: 8 blocks are as fast)
@@ -478,7 +479,7 @@ def test_kv_split_plan():
     geo_w = dict(geo, window=512)
     assert plan_kv_splits([1] * 8, [4096] * 8, cap=16, **geo_w) == [513 // MIN_KEYS_PER_SPLIT] * 8
     # wide groups take several blocks per kv head: fewer splits fill the SMs
-    wide = dict(n_kv=2, group=32, blocks_per_sm=4, tile_tokens=1, window=None)
+    wide = dict(n_kv=2, group=32, blocks_per_sm=4, tile_tokens=1, window=None, sm_count=SM_COUNT)
     assert plan_kv_splits([1] * 16, [8192] * 16, cap=16, **wide) == [slots // (16 * 2 * 2)] * 16
 
 

@@ -177,3 +177,86 @@ def test_missing_extension_or_cpu_tensor_fails_loudly():
     from mini_sglang_b200 import ops
     with pytest.raises(ops.KernelError, match="CUDA device only"):
         ops.swiglu(torch.zeros(2, 8))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_portions_are_shared_while_the_first_prompt_is_still_fed(dtype):
+    """Prompts go in 16 tokens a step.  Two requests share 64 tokens; the second is let in as soon as the first
+    one's shared pages are in the prefix cache (well before the first prompt is done), takes all 64 tokens from
+    there, and generates what the plain implementation generates."""
+    name, cfg = "B", CONFIGS["B"]
+    shared = random_tokens(64, cfg["vocab_size"], 1500)
+    first = shared + random_tokens(70, cfg["vocab_size"], 1501)
+    second = shared + random_tokens(9, cfg["vocab_size"], 1502)
+    eng = make_engine(name, dtype, chunk_size=16, max_prefill_tokens=64)
+    sp = {"max_new_tokens": 5, "ignore_eos": True}
+    r1 = eng.add_request(input_ids=first, sampling_params=sp)
+    r2 = eng.add_request(input_ids=second, sampling_params=sp)
+    started = None
+    for step in range(100):
+        if r1.finished and r2.finished:
+            break
+        eng.step()
+        if started is None and r2.slot is not None:
+            started = step
+            assert not r1.output                          # the first request has not produced a token yet
+    assert started == 4 and r2.cached_tokens == 64 and r1.cached_tokens == 0
+    while not eng.scheduler.idle:
+        eng.step()
+    if dtype == "float32":
+        assert r1.output == P.greedy_generate(cfg, weights(name), first, 5, device="cpu")
+        assert r2.output == P.greedy_generate(cfg, weights(name), second, 5, device="cpu")
+    else:
+        for prompt, r in ((first, r1), (second, r2)):
+            ref = plain_logits(name, prompt + r.output)
+            for i, t in enumerate(r.output):
+                row = ref[len(prompt) - 1 + i]
+                assert row[t] >= row.max() - 0.02, (i, t, row[t].item(), row.max().item())
+    eng.scheduler.check_idle_invariants()
+
+
+def test_profile_records_log_lines_and_async_generate(tmp_path, caplog):
+    """--profile: one record per step with what it held and its times, saved as JSON; INFO log lines for steps
+    with prompt tokens and for every 64th step without; `async_generate` from several coroutines at once."""
+    import asyncio
+    import logging
+    name, cfg = "A", CONFIGS["A"]
+    eng = make_engine(name, "float32", profile=True, profile_dir=str(tmp_path), log_level="INFO")
+    prompts = [random_tokens(n, cfg["vocab_size"], 1600 + n) for n in (5, 9, 13)]
+    sp = {"max_new_tokens": 70, "ignore_eos": True}
+    with caplog.at_level(logging.INFO, logger="mini_sglang_b200.scheduler"):
+        outs = eng.generate(input_ids=prompts, sampling_params=sp)
+    assert [len(o["token_ids"]) for o in outs] == [70] * 3
+    lines = [r.getMessage() for r in caplog.records]
+    assert any(l.startswith("Extend #BS: 3  #Tokens: 27  #PrefixTokens: 0  #ExtendTokens: 27") for l in lines), lines
+    decode_lines = [l for l in lines if l.startswith("Decode #BS: 3")]
+    assert len(decode_lines) == 2 and "#CUDA-Graph: True" in decode_lines[0] and "#new-token-ratio" in decode_lines[0]
+    recs = eng.step_records
+    assert recs[0]["kind"] == "extend" and recs[0]["prompt_tokens"] == 27 and recs[0]["batch"] == 3
+    assert all(r["kind"] == "decode" and r["tokens"] == 3 and r["cuda_graph"] for r in recs[1:])
+    assert len(recs) == 70 and all(r["device_ms"] > 0 and r["kernels"] > 0 and r["host_ms"] > 0 for r in recs)
+    path = eng.write_profile()
+    saved = json.load(open(path))
+    assert saved["summary"]["decode"]["steps"] == 69 and saved["summary"]["extend"]["tokens"] == 27
+    assert len(saved["steps"]) == 70 and eng.write_profile() is None          # nothing new to save
+
+    async def many():
+        a = eng.async_generate(input_ids=prompts[0], sampling_params={"max_new_tokens": 6, "ignore_eos": True})
+        b = eng.async_generate(input_ids=prompts[1], sampling_params={"max_new_tokens": 4, "ignore_eos": True})
+
+        async def streamed():
+            got = []
+            async for part in await eng.async_generate(input_ids=prompts[2], stream=True,
+                                                       sampling_params={"max_new_tokens": 5, "ignore_eos": True}):
+                got.append(list(part["token_ids"]))
+            return got
+        return await asyncio.gather(a, b, streamed())
+
+    ra, rb, rc = asyncio.run(many())
+    assert ra["token_ids"] == outs[0]["token_ids"][:6] and rb["token_ids"] == outs[1]["token_ids"][:4]
+    assert rc[-1] == outs[2]["token_ids"][:5] and [len(x) for x in rc] == sorted({len(x) for x in rc})
+    while not eng.scheduler.idle:
+        eng.step()
+    eng.scheduler.check_idle_invariants()
+    from mini_sglang_b200.parts import model as _model
+    _model.NVTX_RANGES = False

@@ -222,7 +222,9 @@ def test_sampling_greedy_and_race():
     assert out[1].item() == 5
     # all-greedy fast path
     out2 = ops().sample(logits.to(DEV), None, None, None, seed).cpu()
-    assert out2.tolist() == logits.argmax(-1).tolist() or out2[1].item() == 5
+    want2 = logits.argmax(-1).tolist()
+    want2[1] = 5                                                 # the tie goes to the lowest index, whatever torch's argmax picks
+    assert out2.tolist() == want2
     # a request's draw does not depend on its row in the batch
     out3 = ops().sample(logits[[3, 2]].to(DEV), temps[[3, 2]].to(DEV), keys[[3, 2]].to(DEV), steps[[3, 2]].to(DEV), seed).cpu()
     assert out3.tolist() == [out[3].item(), out[2].item()]
@@ -398,3 +400,29 @@ def test_attention_split_requests_never_reach_the_whole_range_kernels():
     nobody wrote)."""
     out, ref = run_attention_case(torch.bfloat16, 32, 8, 128, 16, [5, 1, 12, 1], [3000, 2000, 2500, 700], force_split=4, seed=21)
     torch.testing.assert_close(out, ref.to(torch.bfloat16).float(), **ATT_TOL[torch.bfloat16])
+
+
+def test_status_words_reach_the_host_as_errors():
+    """The kernels with bounded waits report a wait that ran out through status words on the device, which the
+    step function polls.  Here the failure is made on the host (a word set by a copy, no kernel gives up): the
+    next poll must raise, for the attention word and for the GEMM word, and a cleared word must not."""
+    o = ops()
+    st = o._status_tensor(DEV)
+    o.check_kernel_status()                       # clean to begin with
+    for word, what in ((0, "attention"), (2, "GEMM")):
+        st[word] = 1
+        o.poll_status()
+        with pytest.raises(o.KernelError, match=what):
+            o.raise_if_failed(wait=True)
+        with pytest.raises(o.KernelError, match=what):
+            o.check_kernel_status()
+        st[word] = 0
+        o.check_kernel_status()
+    # raise_if_failed() without wait never blocks: it looks only at a poll that has already arrived
+    st[0] = 1
+    o.poll_status()
+    torch.cuda.synchronize()
+    with pytest.raises(o.KernelError):
+        o.raise_if_failed()
+    st[0] = 0
+    o.check_kernel_status()

@@ -6,7 +6,9 @@ import pytest
 import torch
 
 import plain_qwen3 as P
-from helpers import TOL
+from helpers import TOL, assert_row_close, assert_rows_close
+
+DT_NAME = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -55,7 +57,7 @@ def test_norm_part(dtype):
     res = torch.randn(9, 120, generator=g)
     y = n.forward(x=x.to(DEV), residual=res.to(DEV))
     ref = P.rms_norm(res + x.float(), w["blk.norm.weight"].float(), 3e-6)
-    torch.testing.assert_close(y.float().cpu(), ref.to(dtype).float(), **TOL["float32" if dtype == torch.float32 else "bfloat16"])
+    assert_rows_close(y.float().cpu(), ref.to(dtype).float(), DT_NAME[dtype])
 
 
 def test_rope_part_table():
@@ -80,7 +82,7 @@ def test_feed_forward_part(dtype):
     x = torch.randn(11, 72, generator=torch.Generator().manual_seed(3)).to(dtype)
     y = f.forward(x.to(DEV), None)
     ref = P.mlp_block(x.float(), {k: v.float() for k, v in w.items()}, "l.mlp.")
-    torch.testing.assert_close(y.float().cpu(), ref, **TOL["float32" if dtype == torch.float32 else "bfloat16"])
+    assert_rows_close(y.float().cpu(), ref, DT_NAME[dtype])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -101,7 +103,7 @@ def test_embedding_and_head_parts(dtype):
         out = h.forward(x.to(DEV))
         assert out.dtype == torch.float32
         W = w["emb.w"] if tied else hw["head.w"]
-        torch.testing.assert_close(out.cpu(), x.float() @ W.float().T, **TOL["float32" if dtype == torch.float32 else "bfloat16"])
+        assert_rows_close(out.cpu(), x.float() @ W.float().T, DT_NAME[dtype])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -151,7 +153,7 @@ def test_attention_mixer_part_alone(dtype, window):
         cos, sin = P.rope_angles(torch.arange(S), d, 1e4, torch.float32)
         o = P.causal_gqa_attention(P.rope_neox(q, cos, sin), P.rope_neox(k, cos, sin), v, d ** -0.5, window=window)
         ref = o.reshape(S, nq * d) @ wf[p + "o_proj.weight"].T
-    torch.testing.assert_close(got, ref, **TOL["float32" if dtype == torch.float32 else "bfloat16"])
+    assert_rows_close(got, ref, DT_NAME[dtype])
 
 
 # ---------------------------------------------------------------------------------------
@@ -209,11 +211,12 @@ def _register_toy():
         norm = PartSpec("rmsnorm", {"size": H, "eps": r["eps"]})
         ffn = PartSpec("swiglu_mlp", {"hidden_size": H, "intermediate_size": r["ffn"]})
         rope = PartSpec("rope_neox", {"head_dim": 16, "theta": 1e4, "max_positions": 256})
+        names = {"input": "input_layernorm", "post_mixer": "post_attention_layernorm", "mixer": "self_attn", "feed_forward": "mlp"}
         toy = LayerSpec("toy.layers.0", PartSpec("running_mean", {"hidden_size": H}), ffn,
-                        {"input": norm, "post_mixer": norm}, position=None)
+                        {"input": norm, "post_mixer": norm}, position=None, names=names)
         att = LayerSpec("toy.layers.1", PartSpec("paged_attention", {
             "hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "qk_norm": False}), ffn,
-            {"input": norm, "post_mixer": norm}, position=rope)
+            {"input": norm, "post_mixer": norm}, position=rope, names=names)
         # layer 0 runs twice (each run with state of its own), and the last run of the attention
         # layer reads the keys and values its first run wrote
         schedule = [Run(0, cache=0), Run(1, cache=1), Run(0, cache=2), Run(1, cache=1, writes_cache=False)]
@@ -309,8 +312,8 @@ def test_toy_architecture_with_state_is_registered_built_and_stepped(dtype):
         out = runner.step([StepEntry(sc, b, list(range(len(b))))]).float().cpu()
         ref_a, ref_b = toy_plain(holder["w"], a, 1e-5), toy_plain(holder["w"], b, 1e-5)
         for (rid, pos), row in got.items():
-            torch.testing.assert_close(row, (ref_a if rid == "a" else ref_b)[pos], **TOL[dtype])
-        torch.testing.assert_close(out, ref_b, **TOL[dtype])
+            assert_row_close(row, (ref_a if rid == "a" else ref_b)[pos], dtype)
+        assert_rows_close(out, ref_b, dtype)
     finally:
         ARCHITECTURES.pop("ToyStateLM", None)
 
@@ -392,7 +395,9 @@ def _register_routed_toy():
         pos = PartSpec("toy_linear_rotary", {"rot": 8, "step": r["step"], "max_positions": 128})
         att = lambda window: PartSpec("paged_attention", {"hidden_size": H, "num_heads": 6, "num_kv_heads": 3, "head_dim": 16,  # noqa: E731
                                                           "qk_norm": True, "qk_norm_eps": r["eps"], "window": window})
-        layers = [LayerSpec("toy.layers.0", att(None), routed, {"input": norm, "post_mixer": norm}, position=pos),
+        # the checkpoint's names of a layer's parts are data: layer 0 has names of its own, layer 1 none (the roles' names)
+        layers = [LayerSpec("toy.layers.0", att(None), routed, {"input": norm, "post_mixer": norm}, position=pos,
+                            names={"input": "ln1", "post_mixer": "ln2", "mixer": "attn", "feed_forward": "moe"}),
                   LayerSpec("toy.layers.1", att(6), dense, {"input": norm, "post_mixer": norm}, position=pos)]
         return ModelSpec("ToyRoutedLM", H, V, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "name": "toy.embed.weight"}),
                          PartSpec("rmsnorm", {"size": H, "eps": r["eps"], "name": "toy.norm.weight"}),
@@ -435,15 +440,15 @@ def routed_toy_plain(w, tokens, eps, step):
             out[rows] = (torch.nn.functional.gelu(y[rows] @ f[p + f"experts.{e}.up.weight"].T) @ f[p + f"experts.{e}.down.weight"].T) * prob[rows, None]
         return out, best
 
-    y = P.rms_norm(res, f["toy.layers.0.input_layernorm.weight"], eps)
-    res = res + attention(y, "toy.layers.0.self_attn.", None)
-    y = P.rms_norm(res, f["toy.layers.0.post_attention_layernorm.weight"], eps)
-    moe, best = experts(y, "toy.layers.0.mlp.")
+    y = P.rms_norm(res, f["toy.layers.0.ln1.weight"], eps)
+    res = res + attention(y, "toy.layers.0.attn.", None)
+    y = P.rms_norm(res, f["toy.layers.0.ln2.weight"], eps)
+    moe, best = experts(y, "toy.layers.0.moe.")
     res = res + moe
-    y = P.rms_norm(res, f["toy.layers.1.input_layernorm.weight"], eps)
-    res = res + attention(y, "toy.layers.1.self_attn.", 6)
-    y = P.rms_norm(res, f["toy.layers.1.post_attention_layernorm.weight"], eps)
-    res = res + P.mlp_block(y, f, "toy.layers.1.mlp.")
+    y = P.rms_norm(res, f["toy.layers.1.input.weight"], eps)
+    res = res + attention(y, "toy.layers.1.mixer.", 6)
+    y = P.rms_norm(res, f["toy.layers.1.post_mixer.weight"], eps)
+    res = res + P.mlp_block(y, f, "toy.layers.1.feed_forward.")
     return P.rms_norm(res, f["toy.norm.weight"], eps) @ f["toy.head.weight"].T, best
 
 

@@ -58,3 +58,37 @@ def test_sampling_plain():
     t = torch.tensor([0.0, 1.0])
     noise = torch.tensor([[1.0, 1.0, 1.0], [10.0, 0.01, 10.0]])
     assert P.sample_with_noise(logits, t, noise).tolist() == [1, 1]
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_bfloat16_bound_rejects_a_wrong_context_token(name):
+    """The bound that the bfloat16 engine tests use must be able to fail: the logits of the same sequence with ONE
+    context token replaced (what reading one wrong, live cache slot looks like), at whichever of 59 places moves
+    the last row least, are rejected; so are two neighbouring pages (of two tokens at least) swapped; the right logits with noise of the
+    size that bfloat16 rounding leaves are accepted."""
+    from helpers import BF16_RMS_FRACTION, PAGE, assert_row_close
+    from tiny_models import random_tokens
+    cfg, w = CONFIGS[name], make_weights(CONFIGS[name], SEEDS[name])
+    toks = random_tokens(60, cfg["vocab_size"], 5)
+    with torch.no_grad():
+        want = P.forward_sequence(cfg, w, toks)[-1]
+        for i in range(59):
+            wrong = list(toks)
+            wrong[i] = (wrong[i] + 17) % cfg["vocab_size"]
+            row = P.forward_sequence(cfg, w, wrong)[-1]
+            with pytest.raises(AssertionError):
+                assert_row_close(row, want, "bfloat16")
+        page = max(PAGE[name], 2)
+        for first in range(0, 59 - 2 * page, page):
+            wrong = toks[:first] + toks[first + page:first + 2 * page] + toks[first:first + page] + toks[first + 2 * page:]
+            if wrong == toks:
+                continue
+            row = P.forward_sequence(cfg, w, wrong)[-1]
+            with pytest.raises(AssertionError):
+                assert_row_close(row, want, "bfloat16")
+    g = torch.Generator().manual_seed(1)
+    noise = torch.randn(want.shape, generator=g) * (0.5 * BF16_RMS_FRACTION * want.pow(2).mean().sqrt())
+    assert_row_close(want + noise, want, "bfloat16")
+    assert_row_close(want, want, "float32")
+    with pytest.raises(AssertionError):
+        assert_row_close(want + 1e-3, want, "float32")

@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import plain_qwen3
-from helpers import TOL, play
+from helpers import assert_row_close, play
 from tiny_models import make_weights, random_tokens, write_model_dir
 
 pytestmark = pytest.mark.gpu
@@ -69,6 +69,6 @@ def test_random_configuration(seed, dtype):
     assert got
     for (rid, p), row in sorted(got.items()):
         try:
-            torch.testing.assert_close(row, ref[rid][p], **TOL[dtype])
+            assert_row_close(row, ref[rid][p], dtype)
         except AssertionError as e:
             raise AssertionError(f"seed {seed} {dtype} config {cfg}: request {rid} position {p}: {e}") from None
