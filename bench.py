@@ -1,6 +1,10 @@
 """Benchmark of the engine's decode step (headline) and prefill on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+    python bench.py --workload qwen3_0.6b_mixed     128 prompts of 64..1,024 tokens, half of them sharing a 256-token
+                                                    prefix, 256 new tokens each, through the scheduler (Qwen3-0.6B sizes)
+    python bench.py --workload qwen3_32b_long       an 8,192-token prompt in portions of 2,048, then decode at batch 16
+                                                    and context 8,192 (Qwen3-32B sizes)
 
 Default run: Qwen3-8B layer sizes with random weights (N(0, 0.02), bfloat16), a batch of 8
 requests at a context of 4,096 tokens, KV page size 16.  A "step" is one decode step of the
@@ -13,7 +17,10 @@ whole batch.  Prints ONE JSON line:
   prefill    one 2,048-token prompt in one step: tokens/s, ms, and flops / time / bf16 peak
   roofline   bytes the decode step has to read (every weight once + the live requests' cache)
              divided by its time, against the measured copy bandwidth
-  points     decode tokens/s at batch 1 and 64
+  points     decode tokens/s at batch 1 and 64 at this context, and at batch 1, 8 and 64 right after
+             2,048-token prompts (context 2,048 + the steps run)
+  sanity     before anything is timed: a one-layer model of the same widths decodes a token through the same
+             CUDA-graph path and its logits are compared with the plain implementation under tests/
 
 Peaks come from MEASURED_PEAKS.json beside this file when present.  Every timed step reads far
 more than the 126 MB L2 (15 GB of weights), so L2 is not flushed between iterations.
@@ -41,6 +48,10 @@ QWEN3_8B = {
     "eos_token_id": 151645,
 }
 FULL_LAYERS = 36
+QWEN3_0_6B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
+                  head_dim=128, intermediate_size=3072, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,
+                 head_dim=128, intermediate_size=25600, tie_word_embeddings=False)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -89,6 +100,67 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+
+
+def model_sizes(cfg):
+    """(parameters of one layer, bytes of all weights a decode step reads, cache bytes per token) in bfloat16."""
+    V, H, L = cfg["vocab_size"], cfg["hidden_size"], cfg["num_hidden_layers"]
+    nq, nkv, d, I = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["intermediate_size"]
+    layer_params = H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I + 2 * H + 2 * d
+    weight_bytes = 2 * (L * layer_params + V * H + H)            # every weight a decode step reads once (head included;
+    return layer_params, weight_bytes, L * 2 * nkv * d * 2       # the embedding rows it gathers are a few KB)
+
+
+def step_flops(cfg, q_lens, kv_lens, wanted):
+    """Multiply-adds x 2 of one step: every projection for every token, causal attention, the head on `wanted` rows."""
+    V, H, L = cfg["vocab_size"], cfg["hidden_size"], cfg["num_hidden_layers"]
+    nq, d = cfg["num_attention_heads"], cfg["head_dim"]
+    layer_params, _, _ = model_sizes(cfg)
+    T = sum(q_lens)
+    lin = 2 * T * L * (layer_params - 2 * H - 2 * d) + 2 * wanted * V * H
+    attn = sum(L * 4 * nq * d * (q * (kv - q) + q * (q + 1) // 2) for q, kv in zip(q_lens, kv_lens))
+    return lin + attn
+
+
+def sanity_check(cfg, page):
+    """One layer of the benchmark's widths, random weights: a 300-token prompt, then three tokens decoded through
+    the CUDA-graph path; the last row's logits against the plain implementation (float32, on the GPU)."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_qwen3
+    from mini_sglang_b200.config import Qwen3Config
+    from mini_sglang_b200.config.qwen3 import build_qwen3_spec
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    from mini_sglang_b200.parts import expected_tensors
+    from mini_sglang_b200.weights import RandomSource
+    one = dict(cfg, num_hidden_layers=1, max_position_embeddings=1024)
+    spec = build_qwen3_spec(Qwen3Config.from_dict(one))
+    src = RandomSource(expected_tensors(spec), 5, torch.bfloat16, "cuda")
+    weights = {n: src.draw(n) for n in expected_tensors(spec) if src.has(n)}
+    toks = torch.randint(0, one["vocab_size"], (303,), generator=torch.Generator().manual_seed(5)).tolist()
+    runner = ModelRunner.from_random(spec, 5, dtype="bfloat16", page_size=page, num_pages=64, max_reqs=2)
+    s = runner.open()
+    runner.step([StepEntry(s, toks[:300], [])])
+    for i in range(300, 303):
+        row = runner.step([StepEntry(s, [toks[i]], [0])])[0].float().cpu()
+    used_graph = runner.last_step_used_graph
+    runner.close(s)
+    allow = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    with torch.no_grad():
+        want = plain_qwen3.forward_sequence(one, weights, toks, device="cuda", rows=[302])[0].cpu()
+    torch.backends.cuda.matmul.allow_tf32 = allow
+    err = row - want
+    scale = want.pow(2).mean().sqrt().item()
+    out = {"layers": 1, "rms_err_frac": round(err.pow(2).mean().sqrt().item() / scale, 5),
+           "max_err_frac": round(err.abs().max().item() / scale, 5),
+           "argmax_equal": bool(int(row.argmax()) == int(want.argmax())), "cuda_graph": bool(used_graph)}
+    del runner, weights, src
+    torch.cuda.empty_cache()
+    if not (out["rms_err_frac"] < 0.015 and out["max_err_frac"] < 0.09 and used_graph):
+        raise SystemExit(f"bench.py: the engine's logits do not match the plain implementation: {out}")
+    return out
 
 
 def _unavailable(why):
@@ -186,6 +258,161 @@ def reference_arm(args):
     os._exit(0)
 
 
+def _write_config(cfg):
+    tmp = tempfile.mkdtemp(prefix="msgl_bench_")
+    with open(os.path.join(tmp, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    return tmp
+
+
+def workload_mixed(args):
+    """Qwen3-0.6B sizes through the scheduler: 128 prompts with lengths uniform in 64..1,024, every other one opening
+    with the same 256 tokens, 256 new tokens each, all handed to the engine at once (prefix cache on, default policy).
+    value = generated tokens / wall time of Engine.generate.  roofline: the bytes the run has to read (the weights once
+    per step that the scheduler made, and for every decoded token the cache of its request) / its time, against the
+    measured copy bandwidth; the prompts' matrix products are left out of that bound, so it flatters no one."""
+    import random
+
+    import torch
+
+    from mini_sglang_b200 import Engine, EngineArgs, ops
+    cfg = dict(QWEN3_0_6B)
+    pk = peaks()
+    N, NEW, SHARED = 128, 256, 256
+    rnd = random.Random(0)
+    V = cfg["vocab_size"]
+    common = [rnd.randrange(V) for _ in range(SHARED)]
+    prompts = []
+    for i in range(N):
+        n = rnd.randint(64, 1024)
+        prompts.append(common + [rnd.randrange(V) for _ in range(max(n - SHARED, 8))] if i % 2 == 0
+                       else [rnd.randrange(V) for _ in range(n)])
+    clocks = ClockSampler()
+    clocks.start()
+    eng = Engine(EngineArgs(model=_write_config(cfg), dummy_load=True, random_seed=0, page_size=16, max_num_reqs=256,
+                            max_context_len=2048, gpu_memory_utilization=0.5, log_level="WARNING"))
+    sp = {"temperature": 0.0, "max_new_tokens": NEW, "ignore_eos": True}
+    warm = [[rnd.randrange(V) for _ in range(rnd.randint(64, 1024))] for _ in range(N)]
+    eng.generate(input_ids=warm, sampling_params=sp)                  # graphs captured, buffers sized
+    eng.flush_cache()
+    stats0 = dict(eng.scheduler.stats)
+    l0, c0 = ops.LAUNCHES, clocks.mark()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = eng.generate(input_ids=prompts, sampling_params=sp)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    c1 = clocks.mark()
+    clocks.stop()
+    st = {k: v - stats0.get(k, 0) for k, v in eng.scheduler.stats.items()}
+    generated = sum(len(o["token_ids"]) for o in outs)
+    assert generated == N * NEW
+    _, weight_bytes, kv_tok = model_sizes(cfg)
+    kv_read = sum(NEW * len(p) + NEW * (NEW - 1) // 2 for p in prompts) * kv_tok
+    need = st["steps"] * weight_bytes + kv_read
+    achieved = need / dt / 1e9
+    eng.scheduler.check_idle_invariants()
+    print(json.dumps({
+        "workload": "qwen3_0.6b_mixed", "metric": "generated tokens/s through the scheduler, Qwen3-0.6B shape (one B200)",
+        "value": round(generated / dt, 1), "unit": "tokens/s", "seconds": round(dt, 3), "dtype": "bf16",
+        "data": "synthetic: random weights, uniform random token ids",
+        "config": {"model": "Qwen3-0.6B shape", "layers": cfg["num_hidden_layers"], "requests": N, "prompt_tokens": sum(map(len, prompts)),
+                   "shared_prefix": SHARED, "new_tokens": NEW, "page_size": 16, "policy": "lpm", "radix_cache": True},
+        "scheduler": {"steps": st["steps"], "prefill_tokens": st["prefill_tokens"], "cached_tokens": st["cached_tokens"],
+                      "decode_tokens": st["decode_tokens"], "retractions": st["retractions"], "evicted_pages": st["evicted_pages"]},
+        "gpu_launches": ops.LAUNCHES - l0, "clocks": clocks.summary(c0, c1),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
+        "impl": "ours"}))
+    return 0
+
+
+def workload_long(args):
+    """Qwen3-32B sizes (about 65 GB of bfloat16 weights): one 8,192-token prompt fed in portions of 2,048 tokens, timed
+    as a whole (flops / time against the measured bf16 peak), then 16 requests decoding at a context of 8,192
+    (bytes / time against the measured copy bandwidth)."""
+    import torch
+
+    from mini_sglang_b200 import Engine, EngineArgs, ops
+    from mini_sglang_b200.engine.step import StepEntry
+    cfg = dict(QWEN3_32B)
+    cfg["num_hidden_layers"] = args.layers if args.layers != FULL_LAYERS else cfg["num_hidden_layers"]
+    pk = peaks()
+    W, K = max(args.warmup, 3), min(args.steps, 64)
+    B, CTX, PAGE, PORTION = 16, 8192, 16, 2048
+    V = cfg["vocab_size"]
+    gen = torch.Generator().manual_seed(0)
+
+    def rand_tokens(n):
+        return torch.randint(0, V, (n,), generator=gen).tolist()
+
+    clocks = ClockSampler()
+    clocks.start()
+    eng = Engine(EngineArgs(model=_write_config(cfg), dummy_load=True, random_seed=0, page_size=PAGE,
+                            num_pages=(B + 1) * (CTX // PAGE + 2) + 64, max_num_reqs=B + 2, max_context_len=CTX + 64,
+                            max_prefill_tokens=8192, chunk_size=PORTION, disable_radix_cache=True, schedule_policy="fcfs",
+                            log_level="WARNING"))
+    runner = eng.runner
+    _, weight_bytes, kv_tok = model_sizes(cfg)
+
+    # ---- the long prompt, portion by portion
+    times = []
+    for rep in range(3):
+        toks = rand_tokens(CTX)
+        s = runner.open()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(0, CTX, PORTION):
+            runner.step([StepEntry(s, toks[i:i + PORTION], [PORTION - 1] if i + PORTION >= CTX else [])])
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+        runner.close(s)
+    pf_ms = min(times[1:])
+    pf_flops = sum(step_flops(cfg, [PORTION], [i + PORTION], 1 if i + PORTION >= CTX else 0) for i in range(0, CTX, PORTION))
+
+    # ---- decode at batch 16, contexts CTX - (W + K) .. CTX
+    prompt_len = CTX - (W + K) - 1
+    slots = [runner.open() for _ in range(B)]
+    for s in slots:
+        toks = rand_tokens(prompt_len)
+        for i in range(0, prompt_len, PORTION):
+            runner.step([StepEntry(s, toks[i:i + PORTION], [])])
+    feed = [[rand_tokens(1) for _ in slots] for _ in range(W + K)]
+    for i in range(W):
+        runner.step([StepEntry(s, t, [0]) for s, t in zip(slots, feed[i])])
+    torch.cuda.synchronize()
+    l0, c0 = ops.LAUNCHES, clocks.mark()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(W, W + K):
+        runner.step([StepEntry(s, t, [0]) for s, t in zip(slots, feed[i])])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / K
+    launches, c1 = ops.LAUNCHES - l0, clocks.mark()
+    clocks.stop()
+    for s in slots:
+        runner.close(s)
+    step_bytes = weight_bytes + B * (CTX - K // 2) * kv_tok
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "workload": "qwen3_32b_long", "metric": "decode tokens/s, Qwen3-32B shape, batch 16, context 8192 (one B200)",
+        "value": round(B / (ms * 1e-3), 1), "unit": "tokens/s", "steps": K, "warmup": W, "ms_per_step": round(ms, 4), "dtype": "bf16",
+        "data": "synthetic: random weights, uniform random token ids",
+        "config": {"model": "Qwen3-32B shape", "layers": cfg["num_hidden_layers"], "layers_full": QWEN3_32B["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "intermediate": cfg["intermediate_size"], "global_batch": B, "seq_len": CTX, "page_size": PAGE,
+                   "prompt_portion": PORTION, "weight_gb": round(weight_bytes / 1e9, 1)},
+        "prefill": {"value": round(CTX / (pf_ms * 1e-3), 1), "tokens": CTX, "portions": CTX // PORTION, "ms": round(pf_ms, 2),
+                    "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
+        "gpu_launches": launches, "clocks": clocks.summary(c0, c1), "impl": "ours"}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -201,12 +428,19 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="cudaProfilerStart/Stop around the timed region (ncu --profile-from-start off)")
     ap.add_argument("--no-graph", action="store_true", help="decode without CUDA graphs")
+    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long"],
+                    help="headline: the line the contract names; the others: further workloads, one JSON line each")
+    ap.add_argument("--skip-sanity", action="store_true", help="no comparison with the plain implementation before timing")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures the single-GPU engine; --gpus {args.gpus} is not supported (this engine has no multi-GPU path)")
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload == "qwen3_0.6b_mixed":
+        return workload_mixed(args)
+    if args.workload == "qwen3_32b_long":
+        return workload_long(args)
 
     import torch
 
@@ -237,16 +471,18 @@ def main():
     def rand_tokens(n):
         return torch.randint(0, V, (n,), generator=gen).tolist()
 
-    layer_params = H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I + 2 * H + 2 * d
-    weight_bytes = 2 * (L * layer_params + V * H + H)            # every weight a decode step reads once (head included)
-    kv_bytes_per_token = L * 2 * nkv * d * 2
+    layer_params, weight_bytes, kv_bytes_per_token = model_sizes(cfg)
+    sanity = None
+    if args.only == "all" and not args.skip_sanity:
+        sanity = sanity_check(cfg, PAGE)
 
     clocks = ClockSampler()
     clocks.start()
 
-    def timed_decode(batch, steps, warm):
-        """Feed given tokens: `batch` requests at context CTX - (warm + steps) .. CTX."""
-        prompt_len = CTX - (warm + steps) - 1
+    def timed_decode(batch, steps, warm, prompt_len=None):
+        """Feed given tokens: `batch` requests at context CTX - (warm + steps) .. CTX, or from prompt_len on."""
+        if prompt_len is None:
+            prompt_len = CTX - (warm + steps) - 1
         slots = [runner.open() for _ in range(batch)]
         for s in slots:                                           # prompts in portions of 2,048
             toks = rand_tokens(prompt_len)
@@ -338,6 +574,9 @@ def main():
         for b in (1, 64):
             ms_b, _, _ = timed_decode(b, max(K // 2, 8), W)
             points[f"decode_b{b}"] = round(b / (ms_b * 1e-3), 1)
+        for b in (1, 8, 64):                      # right after 2,048-token prompts
+            ms_b, _, _ = timed_decode(b, max(K // 2, 8), W, prompt_len=PREFILL)
+            points[f"decode_b{b}_ctx2048"] = round(b / (ms_b * 1e-3), 1)
 
     # ---- prefill of 2,048 tokens in one step
     pf_ms = []
@@ -354,9 +593,7 @@ def main():
             pf_ms.append(e0.elapsed_time(e1))
         runner.close(s)
     pf = sorted(pf_ms)[len(pf_ms) // 2]
-    lin_flops = 2 * PREFILL * L * (layer_params - 2 * H - 2 * d) + 2 * V * H
-    attn_flops = L * 4 * nq * d * PREFILL * (PREFILL + 1) // 2
-    pf_flops = lin_flops + attn_flops
+    pf_flops = step_flops(cfg, [PREFILL], [PREFILL], 1)
     prefill = {"value": round(PREFILL / (pf * 1e-3), 1), "tokens": PREFILL, "ms": round(pf, 3),
                "frac": round(pf_flops / (pf * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
@@ -373,7 +610,7 @@ def main():
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(c0, c1), "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points, "impl": "ours",
+        "points": points, "sanity": sanity, "impl": "ours",
     }
     print(json.dumps(line))
     return 0

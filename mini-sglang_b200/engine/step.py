@@ -231,6 +231,7 @@ class ModelRunner:
         self._graph_pool = None
         self.kernel_launches = 0
         self.last_step_used_graph = False
+        self.last_plan: Dict[str, object] = {}       # the last step's kv splits per group and the decode graph it replayed
         self._group_geom = []
         for g in self.mgr.groups:
             cid = g.cache_ids[0]
@@ -434,6 +435,7 @@ class ModelRunner:
         else:
             nsplits = [self._plan_splits(gi, q_lens, kv_lens, MAX_KV_SPLIT) for gi in range(len(self.mgr.groups))]
             max_splits = [max(ns) for ns in nsplits]
+            self.last_plan = {"graph_key": None, "nsplits": nsplits, "max_split": max_splits}
             max_pages = [max(int(g.n_pages[e.slot]) for e in entries) for g in self.mgr.groups]
             lay = _Layout(T, B, len(want_rows), max_pages)
             host, idx = self._pinned_buffer(lay.size)
@@ -490,6 +492,7 @@ class ModelRunner:
         if gr is None:
             gr = self._capture(b, mp, [max(c, WIDE_KV_SPLIT) for c in narrow] if wide else narrow)
             self._graphs[key] = gr
+        self.last_plan = {"graph_key": key, "nsplits": nsplits, "max_split": list(gr.max_split)}
         lay = gr.layout
         host, idx = self._pinned_buffer(lay.size)
         self._fill(host.numpy(), lay, entries, starts, list(range(b)), nsplits)

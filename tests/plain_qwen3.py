@@ -112,8 +112,9 @@ def mlp_block(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str) -> torch
 
 
 def forward_sequence(cfg: dict, weights: Dict[str, torch.Tensor], token_ids: List[int],
-                     dtype=torch.float32, device="cpu") -> torch.Tensor:
-    """Logits [S, vocab] at every position of one whole sequence.
+                     dtype=torch.float32, device="cpu", rows: Optional[List[int]] = None) -> torch.Tensor:
+    """Logits [S, vocab] at every position of one whole sequence (or, with `rows`, at those positions only:
+    the whole sequence is computed all the same, only the head is spared for the others).
 
     Residual convention of mini_sglang/models/qwen3.py:169-178,203-206: the stream `res`
     collects x + attn + mlp; every norm reads the updated stream."""
@@ -128,6 +129,8 @@ def forward_sequence(cfg: dict, weights: Dict[str, torch.Tensor], token_ids: Lis
         res = res + attention_block(y, w, p + "self_attn.", cfg, positions)
         y = rms_norm(res, w[p + "post_attention_layernorm.weight"], eps)
         res = res + mlp_block(y, w, p + "mlp.")
+    if rows is not None:
+        res = res[torch.tensor(rows, dtype=torch.long, device=device)]
     h = rms_norm(res, w["model.norm.weight"], eps)
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return h @ head.T      # mini_sglang/layers/logits_processor.py:56-59
