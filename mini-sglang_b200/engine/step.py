@@ -250,7 +250,7 @@ class ModelRunner:
         return dev
 
     def _sm_count(self) -> int:
-        return int(torch.cuda.get_device_properties(self.device).multi_processor_count)
+        return ops.sm_count(self.device)
 
     def _alloc_pinned(self, n: int) -> torch.Tensor:
         return torch.empty(n, dtype=torch.int32, pin_memory=True)

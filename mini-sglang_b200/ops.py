@@ -91,7 +91,7 @@ def _lib():
                                      c_void_p]
         lib.msgl_gemm_tc2.argtypes = lib.msgl_gemm_tc.argtypes
         lib.msgl_sample.argtypes = [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_ull, c_void_p,
-                                    c_void_p]
+                                    c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         _common = lib
     return _common
 
@@ -219,6 +219,34 @@ def cast_from_f32(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
+_sample_scratch = {}          # per device: (part, row_max, tickets)
+_sm_counts = {}
+
+
+def sm_count(device) -> int:
+    """Number of SMs of a CUDA device (asked once)."""
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _sm_counts:
+        _sm_counts[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return _sm_counts[idx]
+
+
+
+def _sample_buffers(device, rows: int, slices: int):
+    """Scratch of the sampling kernels, kept per device and grown on demand.  The tickets are zero between calls:
+    the block that takes a row's last ticket puts it back to zero."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    part, row_max, tickets = _sample_scratch.get(key, (None, None, None))
+    if part is None or part.numel() < rows * slices * 2 or tickets.numel() < rows:
+        n_rows = max(rows, 256, tickets.numel() if tickets is not None else 0)
+        part = torch.empty(max(rows * slices * 2, 256 * 64 * 2), dtype=torch.float32, device=device)
+        row_max = torch.empty(n_rows, dtype=torch.float32, device=device)
+        tickets = torch.zeros(n_rows, dtype=torch.int32, device=device)
+        _sample_scratch[key] = (part, row_max, tickets)
+    return part, row_max, tickets
+
+
 def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor], row_keys: Optional[torch.Tensor],
            steps: Optional[torch.Tensor], seed: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """float32 logits [N, V] -> int32 token ids [N]; greedy where temperature is 0."""
@@ -227,11 +255,20 @@ def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor], row_keys:
     N, V = logits.shape
     if out is None:
         out = torch.empty((N,), dtype=torch.int32, device=logits.device)
+    if N == 0:
+        return out
     if temperatures is not None:
         assert temperatures.dtype == torch.float32 and row_keys.dtype == torch.int32 and steps.dtype == torch.int32
+    # blocks per row: fill the SMs about twice over, but no slice below 1,024 entries
+    sms = sm_count(logits.device)
+    slices = max(1, min(2 * sms // N, V // 1024, 64))
+    part, row_max, tickets = _sample_buffers(logits.device, N, slices)
     code = _lib().msgl_sample(_ptr(logits), N, V, logits.stride(0), _ptr(temperatures), _ptr(row_keys), _ptr(steps),
-                              seed & 0xFFFFFFFFFFFFFFFF, _ptr(out), _stream())
+                              seed & 0xFFFFFFFFFFFFFFFF, _ptr(out), _ptr(part), _ptr(row_max), _ptr(tickets), slices, _stream())
     _check(code, "sample")
+    if temperatures is not None:
+        global LAUNCHES
+        LAUNCHES += 1            # the race is a kernel of its own
     return out
 
 
