@@ -63,7 +63,7 @@ def build_dir() -> str:
 # files a source pulls in with #include: an edit of any of them rebuilds the library
 INCLUDED = {"attention.cu": ["tc_common.cuh", "attention_tc.cuh", "attention_tc2.cuh"],
             "attention_noalloc.cu": ["attention.cu", "tc_common.cuh", "attention_tc.cuh", "attention_tc2.cuh", "attention_noalloc.h"],
-            "gemm_tc.cu": ["tc_common.cuh"]}
+            "gemm_tc.cu": ["tc_common.cuh"], "decode_step.cu": []}
 
 
 def _digest(sources: Sequence[str], flags: Sequence[str]) -> str:
@@ -164,10 +164,22 @@ def attention_noalloc_library(head_dim: int) -> ctypes.CDLL:
     return load_library(f"attention_noalloc_d{hd}", ["attention_noalloc.cu"], {"MSGL_HEAD_DIM": hd})
 
 
+def decode_step_library(head_dim: int) -> ctypes.CDLL:
+    """The whole-step decode kernel of csrc/decode_step.cu, instantiated for `head_dim` (a multiple of 32)."""
+    defines = {"MSGL_HEAD_DIM": head_dim}
+    for knob in ("MSGL_DS_PROFILE", "MSGL_DS_PF", "MSGL_DS_X_CA"):          # phase timers / ring depth
+        if os.environ.get(knob):
+            defines[knob] = int(os.environ[knob])
+    return load_library(f"decode_step_d{head_dim}", ["decode_step.cu"], defines)
+
+
 def build_all(head_dims: Sequence[int] = (16, 32, 48, 64, 128)) -> List[str]:
     """Compile every library ahead of time (used by the repository's build check)."""
     paths = [compile_library("common", COMMON_SOURCES)]
     for hd in head_dims:
         paths.append(compile_library(f"attention_d{hd}", ATTENTION_SOURCES, {"MSGL_HEAD_DIM": hd}))
     paths.append(compile_library("attention_noalloc_d128", ["attention_noalloc.cu"], {"MSGL_HEAD_DIM": 128}))
+    for hd in head_dims:
+        if hd % 32 == 0:
+            paths.append(compile_library(f"decode_step_d{hd}", ["decode_step.cu"], {"MSGL_HEAD_DIM": hd}))
     return paths

@@ -117,13 +117,13 @@ class _Graph:
 DECODE_UNIT_KEYS, DECODE_WARPS = 16, 4        # the decode kernel's warps take units of 16 keys in turn
 
 
-def _fewest_splits_as_fast(keys: int, ns: int) -> int:
+def _fewest_splits_as_fast(keys: int, ns: int, warps: int = DECODE_WARPS) -> int:
     """The smallest number of splits whose busiest warp has no more units of keys than with `ns` splits (fewer
     blocks then leave fewer partial results to merge: 4,096 keys cut for 9 blocks are as fast in 8)."""
     units = -(-keys // DECODE_UNIT_KEYS)
 
     def per_warp(n: int) -> int:
-        return -(-(-(-units // n)) // DECODE_WARPS)
+        return -(-(-(-units // n)) // warps)
 
     if ns <= 1:
         return max(ns, 1)
@@ -135,13 +135,14 @@ def _fewest_splits_as_fast(keys: int, ns: int) -> int:
 
 def plan_kv_splits(q_lens: Sequence[int], kv_lens: Sequence[int], *, n_kv: int, group: int, blocks_per_sm: int,
                    tile_tokens: int, window: Optional[int], cap: int, long_cap: Optional[int] = None,
-                   sm_count: int) -> List[int]:
+                   sm_count: int, warps: int = DECODE_WARPS) -> List[int]:
     """kv splits per request of one attention launch.  Only query runs that fit one tile of the decode kernel
     (`tile_tokens`) are split (the prefill kernels take whole key ranges).  Two reasons to split: the launch
     would otherwise leave most of the SMs idle (few requests: every request is cut alike), or one request is
     much longer than the launch's mean load per resident block, so that its single block would still run when
     all others are done (it is cut into pieces of about that load).  `cap` bounds the first kind of cut,
-    `long_cap` (default: the same) the second.  `sm_count`: the device's number of SMs."""
+    `long_cap` (default: the same) the second.  `sm_count`: the device's number of SMs; `warps`: warps
+    of a block of the kernel that will run the launch."""
     long_cap = cap if long_cap is None else long_cap
     if cap <= 1 and long_cap <= 1:
         return [1] * len(q_lens)
@@ -158,7 +159,7 @@ def plan_kv_splits(q_lens: Sequence[int], kv_lens: Sequence[int], *, n_kv: int, 
         if q > tile_tokens:
             out.append(1)                             # one decode tile at most
             continue
-        even = _fewest_splits_as_fast(k, min(want, k // MIN_KEYS_PER_SPLIT, cap))
+        even = _fewest_splits_as_fast(k, min(want, k // MIN_KEYS_PER_SPLIT, cap), warps)
         long_one = min(-(-k // piece), k // MIN_KEYS_PER_SPLIT, long_cap) if k > piece else 1      # no piece below the minimum
         out.append(max(1, even, long_one))
     # Many requests of like, long contexts and nothing cut so far: the kernel's time follows the largest number of
@@ -287,11 +288,25 @@ class ModelRunner:
             self._pinned[i] = buf
         return buf, i
 
+    FUSED_WARPS = 16         # warps of a block of the whole-step decode kernel
+
+    def _fused_blocks(self, tokens: int) -> int:
+        """Blocks of the whole-step decode kernel for a step of `tokens` single tokens with all logits wanted; 0 if the
+        model or the size goes kernel by kernel."""
+        fd = self.model.fused_decode
+        if fd is None or not 0 < tokens <= ops.FUSED_DECODE_MAX_TOKENS or len(self.mgr.groups) != 1:
+            return 0
+        return fd.blocks_for(tokens)
+
     def _plan_splits(self, gi: int, q_lens: Sequence[int], kv_lens: Sequence[int], cap: int,
-                     long_cap: Optional[int] = None) -> List[int]:
+                     long_cap: Optional[int] = None, fused_blocks: int = 0) -> List[int]:
         n_kv, G, per_sm, qt = self._group_geom[gi]
+        warps = DECODE_WARPS
+        if fused_blocks:          # the whole-step kernel: its blocks are the places, a unit is a (request, kv head, split)
+            per_sm, warps, qt = max(fused_blocks // self.sm_count, 1), self.FUSED_WARPS, 1
         return plan_kv_splits(q_lens, kv_lens, n_kv=n_kv, group=G, blocks_per_sm=per_sm, tile_tokens=qt,
-                              window=self.mgr.groups[gi].window, cap=cap, long_cap=long_cap, sm_count=self.sm_count)
+                              window=self.mgr.groups[gi].window, cap=cap, long_cap=long_cap, sm_count=self.sm_count,
+                              warps=warps)
 
     def _fill(self, host: np.ndarray, lay: _Layout, entries: Sequence[StepEntry], starts: Sequence[int],
               want_rows: Sequence[int], nsplits: Sequence[Sequence[int]], pad_to: int = 0) -> None:
@@ -346,7 +361,7 @@ class ModelRunner:
         host[lay.want: lay.want + len(want_rows)] = want_rows
 
     def _context(self, dev: torch.Tensor, lay: _Layout, q_lens, kv_lens, slots, max_splits, uniform: bool,
-                 nsplits=None) -> StepContext:
+                 nsplits=None, all_rows_wanted: bool = False) -> StepContext:
         def v(off, n):
             return dev[off: off + n]
 
@@ -362,7 +377,8 @@ class ModelRunner:
                            positions=v(lay.positions, lay.T), q_start=v(lay.q_start, lay.B + 1),
                            kv_len=v(lay.kv_len, lay.B), token_req=v(lay.token_req, lay.T), slots=v(lay.slots, lay.B),
                            groups=groups, host_q_lens=list(q_lens), host_kv_lens=list(kv_lens),
-                           host_slots=list(slots), uniform_decode=uniform, workspace=self.workspace)
+                           host_slots=list(slots), uniform_decode=uniform, all_rows_wanted=all_rows_wanted,
+                           workspace=self.workspace)
 
     def _caches(self, ctx: StepContext) -> Dict[int, object]:
         views: Dict[int, object] = {}
@@ -433,7 +449,8 @@ class ModelRunner:
             if self._steps_run % 32 == 0:
                 ops.poll_status()
         else:
-            nsplits = [self._plan_splits(gi, q_lens, kv_lens, MAX_KV_SPLIT) for gi in range(len(self.mgr.groups))]
+            fused = self._fused_blocks(B) if all_last else 0
+            nsplits = [self._plan_splits(gi, q_lens, kv_lens, MAX_KV_SPLIT, fused_blocks=fused) for gi in range(len(self.mgr.groups))]
             max_splits = [max(ns) for ns in nsplits]
             self.last_plan = {"graph_key": None, "nsplits": nsplits, "max_split": max_splits}
             max_pages = [max(int(g.n_pages[e.slot]) for e in entries) for g in self.mgr.groups]
@@ -447,7 +464,8 @@ class ModelRunner:
             self._mark(idx)
             if prev_ids is not None:
                 ops.resolve_ids(dev[lay.input_ids: lay.input_ids + T], prev_ids)
-            ctx = self._context(dev, lay, q_lens, kv_lens, [e.slot for e in entries], max_splits, uniform, nsplits)
+            ctx = self._context(dev, lay, q_lens, kv_lens, [e.slot for e in entries], max_splits, uniform, nsplits,
+                                all_rows_wanted=all_last)
             rows = dev[lay.want: lay.want + len(want_rows)]
             logits = self.model.forward(ctx, self._caches(ctx), rows)
             ops.poll_status()
@@ -475,7 +493,8 @@ class ModelRunner:
         n_kv, G, per_sm, _ = self._group_geom[gi]
         chunks = 1 if G <= 16 else -(-G // 16)
         blocks = b * n_kv * chunks
-        return max(1, min(MAX_KV_SPLIT, (self.sm_count * per_sm) // blocks))
+        places = self._fused_blocks(b) or self.sm_count * per_sm
+        return max(1, min(MAX_KV_SPLIT, places // blocks))
 
     def _step_graph(self, entries, starts, q_lens, kv_lens, prev_ids=None) -> torch.Tensor:
         B = len(entries)
@@ -485,7 +504,9 @@ class ModelRunner:
         # the graph fixes the launch's split dimension: the narrow one suits requests of like length; a batch
         # with a request far longer than the rest takes a second graph with room for more pieces
         narrow = [self._graph_max_split(gi, b) for gi in range(len(self.mgr.groups))]
-        nsplits = [self._plan_splits(gi, q_lens, kv_lens, narrow[gi], max(narrow[gi], WIDE_KV_SPLIT)) for gi in range(len(self.mgr.groups))]
+        fused = self._fused_blocks(b)
+        nsplits = [self._plan_splits(gi, q_lens, kv_lens, narrow[gi], max(narrow[gi], WIDE_KV_SPLIT), fused_blocks=fused)
+                   for gi in range(len(self.mgr.groups))]
         wide = any(max(ns) > cap for ns, cap in zip(nsplits, narrow))
         key = (b, mp, wide)
         gr = self._graphs.get(key)
@@ -513,7 +534,7 @@ class ModelRunner:
         host = np.zeros(lay.size, dtype=np.int32)
         self._fill(host, lay, [], [], list(range(b)), [[1] * b for _ in self.mgr.groups])
         gr.dev.copy_(torch.from_numpy(host))
-        ctx = self._context(gr.dev, lay, [1] * b, [1] * b, [0] * b, gr.max_split, True)
+        ctx = self._context(gr.dev, lay, [1] * b, [1] * b, [0] * b, gr.max_split, True, all_rows_wanted=True)
         caches = self._caches(ctx)
         rows = gr.dev[lay.want: lay.want + b]
         # two eager runs size every scratch buffer outside the graph's private pool

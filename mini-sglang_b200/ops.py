@@ -278,7 +278,7 @@ def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor], row_keys:
 VARIANT_SIMT, VARIANT_MMA_ROWS, VARIANT_MMA_DECODE, VARIANT_TC = 0, 1, 2, 3
 TC_ROWS = 128                     # query rows per block of the tcgen05 prefill kernel
 USE_TC_ATTENTION = os.environ.get("MSGL_NO_TC_ATTENTION", "") == ""
-_status = None                    # device int32[64]: word 0 tcgen05 attention, word 2 tcgen05 GEMM; words 4..: debug counters
+_status = None                    # device int32[64]: word 0 tcgen05 attention, word 2 tcgen05 GEMM, word 3 decode-step kernel; words 4..: debug counters
 _status_host = None               # its pinned mirror, refreshed by poll_status()
 _status_event = None
 
@@ -313,6 +313,8 @@ def raise_if_failed(wait: bool = False) -> None:
         raise KernelError("tcgen05 attention: a block timed out waiting for the tensor core; results are invalid")
     if int(_status_host[2]) != 0:
         raise KernelError("tcgen05 GEMM: a block timed out waiting for its pipeline; results are invalid")
+    if int(_status_host[3]) != 0:
+        raise KernelError("decode step: a block timed out at a grid barrier; results are invalid")
 
 
 def tc_supported(head_dim: int, dtype: torch.dtype, group: int) -> bool:
@@ -515,3 +517,68 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
     if y is not None:
         return y
     return swiglu(torch.nn.functional.linear(x, gate_up))
+
+
+# ---------------------------------------------------------------------------------------
+# the whole decode step in one persistent kernel (csrc/decode_step.cu)
+# ---------------------------------------------------------------------------------------
+# Off unless MSGL_FUSED_DECODE=1: measured on B200 at Qwen3-8B's sizes the one-kernel step takes 5.0 / 5.8 ms at batch 1 / 8
+# (context 4,096) against 3.4 / 4.2 ms kernel by kernel (see profiles/decode_step_kernel_b1_b8.md for where the time goes).
+USE_FUSED_DECODE = os.environ.get("MSGL_FUSED_DECODE", "0") == "1"
+FUSED_DECODE_MAX_TOKENS = 8
+STATUS_WORD_DECODE_STEP = 3
+
+
+class DsLayer(ctypes.Structure):
+    """One run of a layer for the decode-step kernel; mirrors `struct DsLayer`."""
+    _fields_ = [("w_qkv", c_void_p), ("b_qkv", c_void_p), ("w_o", c_void_p), ("w_gu", c_void_p), ("w_down", c_void_p),
+                ("norm_in", c_void_p), ("norm_post", c_void_p), ("q_norm", c_void_p), ("k_norm", c_void_p),
+                ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("eps_in", c_float), ("eps_post", c_float), ("eps_qk", c_float),
+                ("norm_f32", c_int), ("qk_norm_f32", c_int), ("pad_", c_int)]
+
+
+class DsStep(ctypes.Structure):
+    """Arguments of one decode step; mirrors `struct DsStep`."""
+    _fields_ = [("layers", c_void_p), ("n_layers", c_int), ("M", c_int),
+                ("H", c_int), ("n_q", c_int), ("n_kv", c_int), ("I", c_int), ("V", c_int),
+                ("page_size", c_int), ("page_shift", c_int), ("bt_stride", c_int), ("max_split", c_int),
+                ("scale", c_float),
+                ("rope", c_void_p), ("rot", c_int), ("max_pos", c_int),
+                ("ids", c_void_p), ("positions", c_void_p), ("kv_len", c_void_p), ("block_table", c_void_p),
+                ("out_loc", c_void_p), ("nsplit", c_void_p),
+                ("embed", c_void_p), ("final_norm", c_void_p), ("final_f32", c_int), ("eps_final", c_float),
+                ("lm_head", c_void_p),
+                ("res", c_void_p), ("qkv", c_void_p), ("attn", c_void_p), ("act", c_void_p),
+                ("part_o", c_void_p), ("part_ml", c_void_p), ("tickets", c_void_p), ("logits", c_void_p),
+                ("bar", c_void_p), ("status", c_void_p)]
+
+
+_decode_libs = {}
+
+
+def _decode_lib(head_dim: int):
+    lib = _decode_libs.get(head_dim)
+    if lib is None:
+        lib = _build.decode_step_library(head_dim)
+        lib.msgl_decode_step_blocks.argtypes = [c_int] * 6
+        lib.msgl_decode_step_blocks.restype = c_int
+        lib.msgl_decode_step.argtypes = [ctypes.POINTER(DsStep), c_void_p]
+        if lib.msgl_decode_step_layer_bytes() != ctypes.sizeof(DsLayer) or lib.msgl_decode_step_struct_bytes() != ctypes.sizeof(DsStep):
+            raise KernelError("decode_step: the argument structures of the library and of ops.py differ")
+        _decode_libs[head_dim] = lib
+    return lib
+
+
+def decode_step_blocks(tokens: int, hidden: int, n_q: int, n_kv: int, head_dim: int, intermediate: int, vocab: int) -> int:
+    """Blocks the decode-step kernel runs with for these sizes on the current device; 0: it does not take them
+    (the caller then runs the step kernel by kernel).  Not inside a stream capture the first time."""
+    if not USE_FUSED_DECODE or head_dim % 32 or head_dim < 32 or head_dim > 128:      # beyond 128 the accumulators spill
+        return 0
+    return int(_decode_lib(head_dim).msgl_decode_step_blocks(tokens, hidden, n_q, n_kv, intermediate, vocab))
+
+
+def decode_step(step: DsStep, head_dim: int) -> None:
+    """Launch the decode-step kernel on the current stream."""
+    code = _decode_lib(head_dim).msgl_decode_step(ctypes.byref(step), _stream())
+    _check(code, f"decode_step (head size {head_dim})")

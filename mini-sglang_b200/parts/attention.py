@@ -76,6 +76,14 @@ class PagedAttention(Mixer):
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(self.n_kv, self.d, self.window, q_heads=self.n_q)
 
+    def fused_decode_fields(self):
+        if self.window is not None or (self.position is not None and self.position.fused_decode_fields() is None):
+            return None
+        rope = self.position.fused_decode_fields() if self.position is not None else None
+        return {"kind": "paged_attention", "qkv": self.qkv, "qkv_bias": self.qkv_b, "o": self.o, "q_norm": self.q_norm,
+                "k_norm": self.k_norm, "qk_norm_eps": self.qk_norm_eps, "H": self.H, "n_q": self.n_q, "n_kv": self.n_kv,
+                "d": self.d, "scale": self.scale, "rope": rope}
+
     # -- compute -----------------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: KVCacheView, writes_cache: bool = True) -> torch.Tensor:
         qkv = ops.linear(x, self.qkv, self.qkv_b)

@@ -55,6 +55,12 @@ class Part:
     def load(self, src) -> None:
         pass
 
+    def fused_decode_fields(self) -> Optional[Dict[str, Any]]:
+        """What the whole-step decode kernel (csrc/decode_step.cu) needs of this part: its loaded tensors, sizes and
+        constants under the names that kernel knows, or None if the part is of a kind the kernel does not compute
+        (the default: a model with such a part is stepped kernel by kernel)."""
+        return None
+
 
 class Mixer(Part):
     # True if forward() only launches work whose shapes and addresses are fixed by (T, B) and reads

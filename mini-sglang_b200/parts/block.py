@@ -48,3 +48,12 @@ class PreNormResidualBlock(Block):
         a = self.mixer.forward(y, ctx, cache, writes_cache)
         y = self.norm_post.forward(x=a, residual=residual, residual_out=residual)
         return self.ffn.forward(y, ctx), residual
+
+    def fused_decode_fields(self):
+        """This arrangement is the one the whole-step decode kernel walks (norm, mixer, residual sum, norm, feed-forward,
+        residual sum); it takes part if all four parts do."""
+        parts = {"norm_in": self.norm_in.fused_decode_fields(), "mixer": self.mixer.fused_decode_fields(),
+                 "norm_post": self.norm_post.fused_decode_fields(), "ffn": self.ffn.fused_decode_fields()}
+        if any(v is None for v in parts.values()):
+            return None
+        return {"kind": "prenorm_residual", **parts}

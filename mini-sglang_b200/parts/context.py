@@ -40,6 +40,7 @@ class StepContext:
     host_kv_lens: List[int]
     host_slots: List[int]
     uniform_decode: bool = False       # every request brings exactly one token (fixed launch shapes)
+    all_rows_wanted: bool = False      # the wanted rows are all T rows in order (what a decode step asks for)
     workspace: Optional["Workspace"] = None
 
 

@@ -29,6 +29,9 @@ class TokenEmbedding(Part):
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         return ops.embedding(ids, self.weight)
 
+    def fused_decode_fields(self):
+        return {"kind": "token_embedding", "weight": self.weight, "V": self.V, "H": self.H}
+
 
 @register_head("lm_head")
 class LMHead(Part):
@@ -58,3 +61,6 @@ class LMHead(Part):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return ops.linear(h, self.weight, out_dtype=torch.float32)
+
+    def fused_decode_fields(self):
+        return {"kind": "lm_head", "weight": self.weight, "V": self.V, "H": self.H}

@@ -33,3 +33,6 @@ class SwiGLUMLP(FeedForward):
 
     def forward(self, x, ctx):
         return ops.linear(ops.linear_swiglu(x, self.gate_up), self.down)
+
+    def fused_decode_fields(self):
+        return {"kind": "swiglu_mlp", "gate_up": self.gate_up, "down": self.down, "H": self.H, "I": self.I}

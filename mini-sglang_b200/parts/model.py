@@ -33,6 +33,7 @@ class DecoderModel:
         self.final_norm = build_part(NORMS, "norm", spec.final_norm, "", env)
         self.head = build_part(HEADS, "output head", spec.head, "", env)
         self.schedule = list(spec.schedule)
+        self.fused_decode = None
 
     # -- weights -----------------------------------------------------------------------
     def tensors(self) -> Dict[str, TensorDecl]:
@@ -50,6 +51,8 @@ class DecoderModel:
             layer.load(src)
         self.final_norm.load(src)
         self.head.load(src, embedding=self.embedding)
+        from .fused_decode import FusedDecodeStep
+        self.fused_decode = FusedDecodeStep.build(self)      # None: this model is stepped kernel by kernel
 
     def cache_needs(self) -> Dict[int, object]:
         """cache id -> need, from the mixer of the run that writes the cache."""
@@ -68,6 +71,8 @@ class DecoderModel:
     # -- compute -----------------------------------------------------------------------
     def forward(self, ctx: StepContext, caches: Dict[int, object], want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """-> float32 logits [len(want_rows), vocab] (all T rows if want_rows is None)."""
+        if self.fused_decode is not None and self.fused_decode.takes(ctx):
+            return self.fused_decode.forward(ctx, caches)       # the whole step in one persistent kernel
         if NVTX_RANGES:
             return self._forward_marked(ctx, caches, want_rows)
         residual = self.embedding.forward(ctx.input_ids)

@@ -30,3 +30,6 @@ class RMSNorm(Norm):
     def forward(self, x=None, residual=None, residual_out=None, rows=None):
         return ops.rmsnorm(self.weight, self.eps, x=x, residual=residual, residual_out=residual_out, rows=rows,
                            out_dtype=self.env.dtype)
+
+    def fused_decode_fields(self):
+        return {"kind": "rmsnorm", "weight": self.weight, "eps": self.eps, "size": self.size}

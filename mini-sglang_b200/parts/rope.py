@@ -38,3 +38,6 @@ class RotaryNeox(PositionEncoding):
             freqs = t[:, None] * inv_freq[None, :]
             self._table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(self.env.device)
         return self._table
+
+    def fused_decode_fields(self):
+        return {"kind": "rotary_table", "table": self.rotary_table(), "rot": self.rotary_dim, "max_pos": self.max_positions}

@@ -167,3 +167,49 @@ def test_full_width_one_long_request_among_many_short_ones():
             except AssertionError as e:
                 raise AssertionError(f"decode step {i}, {name} request: {e}") from None
     assert any(wide for _, _, wide in runner._graphs), "the batch should have taken the graph with room for more pieces"
+
+
+def test_whole_step_decode_kernel_against_plain(monkeypatch):
+    """The one-kernel decode step (csrc/decode_step.cu; off by default, forced on here) at Qwen3-8B's widths: 1, 3 and 8
+    requests of different lengths decode together, with kv splits, against the plain implementation; and the model must
+    really have taken that kernel (one launch per step)."""
+    from mini_sglang_b200 import ops
+    from mini_sglang_b200.config import Qwen3Config
+    from mini_sglang_b200.config.qwen3 import build_qwen3_spec
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    from mini_sglang_b200.parts import expected_tensors
+    from mini_sglang_b200.weights import RandomSource
+    monkeypatch.setattr(ops, "USE_FUSED_DECODE", True)
+    spec = build_qwen3_spec(Qwen3Config.from_dict(CFG))
+    src = RandomSource(expected_tensors(spec), 7, torch.bfloat16, "cuda")
+    weights = {n: src.draw(n) for n in expected_tensors(spec) if src.has(n)}
+    g = torch.Generator().manual_seed(31)
+    lens = [1500, 40, 700, 17, 260, 90, 5, 1023]
+    n_dec = 5
+    seqs = [torch.randint(0, CFG["vocab_size"], (n + n_dec,), generator=g).tolist() for n in lens]
+    runner = ModelRunner.from_random(spec, 7, dtype="bfloat16", page_size=16, num_pages=sum(-(-(n + n_dec) // 16) for n in lens) + 8, max_reqs=8)
+    assert runner.model.fused_decode is not None
+    slots = [runner.open() for _ in lens]
+    for s, toks, n in zip(slots, seqs, lens):
+        runner.step([StepEntry(s, toks[:n], [])])
+    got, fed = {}, [0] * len(lens)
+    for live in ([0], [0, 1, 2], list(range(8)), list(range(8)), list(range(8))):
+        ents = [StepEntry(slots[i], [seqs[i][lens[i] + fed[i]]], [0]) for i in live]
+        out = runner.step(ents).float().cpu()
+        assert runner.last_step_used_graph
+        for i, row in zip(live, out):
+            got[(i, fed[i])] = row
+            fed[i] += 1
+    assert sorted(k[0] for k in runner._graphs) == [1, 4, 8]
+    assert all(gr.n_kernels == 1 for gr in runner._graphs.values()), "the steps did not go through the one-kernel path"
+    ops.check_kernel_status()
+    assert max(max(ns) for ns in runner.last_plan["nsplits"]) > 1
+    for i in range(len(lens)):
+        rows = sorted(k for (j, k) in got if j == i)
+        with torch.no_grad():
+            ref = P.forward_sequence(CFG, weights, seqs[i], device="cuda", rows=[lens[i] + k for k in rows]).cpu()
+        for k, want in zip(rows, ref):
+            try:
+                check_row(got[(i, k)], want, "bfloat16")
+            except AssertionError as e:
+                raise AssertionError(f"request {i} ({lens[i]} tokens), decoded token {k}: {e}") from None
