@@ -92,12 +92,13 @@ __global__ void sample_slices_kernel(const float* __restrict__ logits, int vocab
     ArgBest best{-INFINITY, 0x7fffffff};
     if (PASS == 0) {
         int j = j0 + threadIdx.x;
-        for (; j + 3 * (int)blockDim.x < j1; j += 4 * blockDim.x) {      // four loads in flight
-            const float a = row[j], b = row[j + blockDim.x], c = row[j + 2 * blockDim.x], d = row[j + 3 * blockDim.x];
-            best = better(best, ArgBest{a, j});
-            best = better(best, ArgBest{b, j + (int)blockDim.x});
-            best = better(best, ArgBest{c, j + 2 * (int)blockDim.x});
-            best = better(best, ArgBest{d, j + 3 * (int)blockDim.x});
+        const int bd = (int)blockDim.x;
+        for (; j + 7 * bd < j1; j += 8 * bd) {      // eight loads in flight
+            float v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = __ldg(row + j + q * bd);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) best = better(best, ArgBest{v[q], j + q * bd});
         }
         for (; j < j1; j += blockDim.x) best = better(best, ArgBest{row[j], j});
     } else {

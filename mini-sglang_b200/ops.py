@@ -259,9 +259,9 @@ def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor], row_keys:
         return out
     if temperatures is not None:
         assert temperatures.dtype == torch.float32 and row_keys.dtype == torch.int32 and steps.dtype == torch.int32
-    # blocks per row: fill the SMs about twice over, but no slice below 1,024 entries
+    # blocks per row: about four blocks an SM over all rows, but no slice below 2,048 entries
     sms = sm_count(logits.device)
-    slices = max(1, min(2 * sms // N, V // 1024, 64))
+    slices = max(1, min(-(-4 * sms // N), V // 2048, 64))
     part, row_max, tickets = _sample_buffers(logits.device, N, slices)
     code = _lib().msgl_sample(_ptr(logits), N, V, logits.stride(0), _ptr(temperatures), _ptr(row_keys), _ptr(steps),
                               seed & 0xFFFFFFFFFFFFFFFF, _ptr(out), _ptr(part), _ptr(row_max), _ptr(tickets), slices, _stream())
