@@ -98,6 +98,32 @@ __device__ __forceinline__ void gt_drain(unsigned acc, int row, int col0, int M,
     }
 }
 
+// Split-K: the same accumulator row as float32 partial sums.  part: [M, ldp] of this split; accumulator column c of the
+// tile goes to column colmap(c): plain c -> n * 256 + c; SwiGLU: gate c < 128 -> n * 128 + c, up c >= 128 -> I + n * 128 + (c - 128),
+// i.e. the partials have the layout of the un-fused [M, 2 I] product.
+__device__ __forceinline__ void gt_drain_partial(unsigned acc, int row, int M, float* __restrict__ part, long long ldp, int col_lo, int col_hi_base,
+                                                 int n_valid_lo, int n_valid_hi, int c_lo, int c_hi) {
+    float* prow = part + (size_t)(row < M ? row : 0) * ldp;
+#pragma unroll 1
+    for (int c = c_lo; c < c_hi; ++c) {
+        float v[32];
+        tc_ld32(acc + c * 32, v);
+        tc_wait_ld(v);
+        if (row < M) {
+            // chunks 0-3 are the tile's first 128 columns, 4-7 its second 128
+            const int col = (c < 4) ? col_lo + c * 32 : col_hi_base + (c - 4) * 32;
+            const int lim = (c < 4) ? n_valid_lo : n_valid_hi;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                if (col + j + 4 <= lim) *reinterpret_cast<float4*>(prow + col + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                else
+                    for (int e = 0; e < 4; ++e)
+                        if (col + j + e < lim) prow[col + j + e] = v[j + e];
+            }
+        }
+    }
+}
+
 template <bool SWIGLU>
 __global__ void __launch_bounds__(GT_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                 const __grid_constant__ CUtensorMap wmap,
@@ -274,7 +300,10 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(GT2_THREADS, 1) gemm_tc2_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                  const __grid_constant__ CUtensorMap wmap,
                                                                  const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out,
-                                                                 int M, int N, int K, long long ldo, int I, int* status) {
+                                                                 int M, int N, int K, long long ldo, int I, int* status,
+                                                                 int splits, float* __restrict__ part) {
+    // splits > 1 (few tokens: too few tiles to fill the GPU): K is cut into `splits` ranges of slabs, a work item is
+    // (tile, range), and the accumulators go out as float32 partial sums part[range][M][N] for gemm_splitk_reduce_kernel.
     extern __shared__ __align__(16) unsigned char gt_smem[];
     const unsigned smem_base = tc_smem_u32(gt_smem);
     const unsigned tiles0 = (smem_base + 256u + 1023u) & ~1023u;
@@ -291,7 +320,14 @@ __global__ void __launch_bounds__(GT2_THREADS, 1) gemm_tc2_kernel(const __grid_c
     const int n_valid = SWIGLU ? I : N;
     const int bn_out = SWIGLU ? 128 : 256;
     const int MT = (M + 255) / 256, NT = (n_valid + bn_out - 1) / bn_out;
-    const int n_tiles = MT * NT, n_slabs = (K + GT_BK - 1) / GT_BK;
+    const int n_slabs = (K + GT_BK - 1) / GT_BK;
+    const int n_tiles = MT * NT * splits;                   // work items: the ranges of a tile are neighbours, so they run at the same time
+    auto item = [&](int t, int& m, int& n, int& k_begin, int& k_end) {
+        const int ks = t % splits, tile = t / splits;
+        m = tile % MT; n = tile / MT;
+        k_begin = (int)((long long)ks * n_slabs / splits);
+        k_end = (int)((long long)(ks + 1) * n_slabs / splits);
+    };
 
     if (tid == 0) {
         for (int s = 0; s < GT2_STAGES; ++s) { tc_mbar_init(bar_full(s), 1); tc_mbar_init(bar_empty(s), 1); }
@@ -315,9 +351,10 @@ __global__ void __launch_bounds__(GT2_THREADS, 1) gemm_tc2_kernel(const __grid_c
             int g = 0;
             pdl_wait();                   // x is the output of the kernel before: everything up to here ran beside its end
             for (int t = pair; t < n_tiles && !fail; t += n_pairs) {
-                const int m = t % MT, n = t / MT;
+                int m, n, k_begin, k_end;
+                item(t, m, n, k_begin, k_end);
                 const int w_row = SWIGLU ? (rank == 0 ? n * 128 : I + n * 128) : n * 256 + (int)rank * 128;
-                for (int k = 0; k < n_slabs; ++k, ++g) {
+                for (int k = k_begin; k < k_end; ++k, ++g) {
                     const int st = g % GT2_STAGES;
                     if (!tc_mbar_wait(bar_empty(st), ((g / GT2_STAGES) & 1) ^ 1)) { fail = 1; break; }
                     const unsigned a_s = tiles0 + (unsigned)st * GT2_STAGE_BYTES, b_s = a_s + GT2_HALF_BYTES;
@@ -340,14 +377,16 @@ __global__ void __launch_bounds__(GT2_THREADS, 1) gemm_tc2_kernel(const __grid_c
                 if (!gt2_mbar_wait_cluster(bar_acc_empty(b), ((it >> 1) & 1) ^ 1)) { fail = 1; break; }
                 tc_fence_after();
                 const unsigned d_t = tmem + (unsigned)b * 256u;
-                for (int k = 0; k < n_slabs; ++k, ++g) {
+                int m_, n_, k_begin, k_end;
+                item(t, m_, n_, k_begin, k_end);
+                for (int k = k_begin; k < k_end; ++k, ++g) {
                     const int st = g % GT2_STAGES;
                     if (!gt2_mbar_wait_cluster(bar_full(st), (g / GT2_STAGES) & 1)) { fail = 1; break; }
                     tc_fence_after();
                     const unsigned long long da = da0 + (unsigned long long)st * stage_step, db = db0 + (unsigned long long)st * stage_step;
 #pragma unroll
                     for (int kk = 0; kk < GT_BK / 16; ++kk)
-                        gt2_mma(d_t, da + (unsigned long long)(2 * kk), db + (unsigned long long)(2 * kk), idesc, (k > 0 || kk > 0) ? 1u : 0u);
+                        gt2_mma(d_t, da + (unsigned long long)(2 * kk), db + (unsigned long long)(2 * kk), idesc, (k > k_begin || kk > 0) ? 1u : 0u);
                     gt2_commit_pair(bar_empty(st));
                 }
                 if (fail) break;
@@ -362,11 +401,20 @@ __global__ void __launch_bounds__(GT2_THREADS, 1) gemm_tc2_kernel(const __grid_c
         const unsigned acc_empty0 = gt2_map_to(bar_acc_empty(0), 0);
         int it = 0;
         for (int t = pair; t < n_tiles; t += n_pairs, ++it) {
-            const int m = t % MT, n = t / MT, b = it & 1;
+            int m, n, k_begin, k_end;
+            item(t, m, n, k_begin, k_end);
+            const int b = it & 1;
             if (!tc_mbar_wait(bar_acc_full(b), (it >> 1) & 1)) { fail = 1; break; }
             tc_fence_after();
-            gt_drain<SWIGLU>(tmem + (unsigned)b * 256u + lane_sel, m * 256 + (int)rank * 128 + q * 32 + lane, n * bn_out, M, n_valid, bias, out, ldo,
-                             second * (n_chunks / 2), (second + 1) * (n_chunks / 2));
+            const int row = m * 256 + (int)rank * 128 + q * 32 + lane;
+            if (part != nullptr) {
+                float* mine = part + (size_t)(t % splits) * (size_t)M * (size_t)N;
+                if (SWIGLU) gt_drain_partial(tmem + (unsigned)b * 256u + lane_sel, row, M, mine, N, n * 128, I + n * 128, I, N, second * 4, second * 4 + 4);
+                else gt_drain_partial(tmem + (unsigned)b * 256u + lane_sel, row, M, mine, N, n * 256, n * 256 + 128, N, N, second * 4, second * 4 + 4);
+            } else {
+                gt_drain<SWIGLU>(tmem + (unsigned)b * 256u + lane_sel, row, n * bn_out, M, n_valid, bias, out, ldo,
+                                 second * (n_chunks / 2), (second + 1) * (n_chunks / 2));
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) gt2_mbar_arrive_remote(acc_empty0 + 8u * (unsigned)b);
@@ -411,10 +459,52 @@ MSGL_API int msgl_gemm_tc(const void* W, const void* X, const void* bias, void* 
     return msgl_check_launch();
 }
 
+// out = sum over the ranges of part[range][M][N], added in range order (the result does not depend on timing), then bias or
+// SwiGLU and one rounding; a thread takes 4 neighbouring output columns of one token.
+template <bool SWIGLU>
+__global__ void gemm_splitk_reduce_kernel(const float* __restrict__ part, int splits, int M, int N, int I,
+                                          const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, long long ldo) {
+    pdl_launch_dependents();
+    pdl_wait();
+    pdl_after_wait();
+    const int n_out = SWIGLU ? I : N;
+    const int per_row = (n_out + 3) / 4;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)M * per_row) return;
+    const int m = (int)(idx / per_row), c = (int)(idx - (long long)m * per_row) * 4;
+    const size_t plane = (size_t)M * N;
+    float a[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool whole = c + 4 <= n_out && (!SWIGLU || (I & 3) == 0);
+    for (int sp = 0; sp < splits; ++sp) {
+        const float* row = part + sp * plane + (size_t)m * N;
+        if (whole) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(row + c));
+            a[0] += v.x; a[1] += v.y; a[2] += v.z; a[3] += v.w;
+            if (SWIGLU) {
+                const float4 w = __ldcg(reinterpret_cast<const float4*>(row + I + c));
+                u[0] += w.x; u[1] += w.y; u[2] += w.z; u[3] += w.w;
+            }
+        } else {
+            for (int e = 0; e < 4; ++e)
+                if (c + e < n_out) { a[e] += __ldcg(row + c + e); if (SWIGLU) u[e] += __ldcg(row + I + c + e); }
+        }
+    }
+    __nv_bfloat16* orow = out + (size_t)m * ldo + c;
+    for (int e = 0; e < 4; ++e) {
+        if (c + e >= n_out) break;
+        float y = a[e];
+        if (SWIGLU) y = y / (1.f + expf(-y)) * u[e];
+        else if (bias != nullptr) y += __bfloat162float(bias[c + e]);
+        orow[e] = __float2bfloat16_rn(y);
+    }
+}
+
 // The same on pairs of SMs (gemm_tc2_kernel); same arguments and return values.
-MSGL_API int msgl_gemm_tc2(const void* W, const void* X, const void* bias, void* out, int M, int N, int K, long long ldx,
-                           long long ldo, int mode, void* status, cudaStream_t stream) {
+// splits > 1: split-K with `partials` = splits * M * N float32 of scratch (see gemm_tc2_kernel); needs N % 4 == 0.
+MSGL_API int msgl_gemm_tc2_splitk(const void* W, const void* X, const void* bias, void* out, int M, int N, int K, long long ldx,
+                                  long long ldo, int mode, int splits, void* partials, void* status, cudaStream_t stream) {
     if (M <= 0) return MSGL_OK;
+    if (splits < 1 || (splits > 1 && (partials == nullptr || (N & 3) || splits > (K + GT_BK - 1) / GT_BK))) return MSGL_ERR_SIZE;
     if (N <= 0 || K <= 0 || (K & 7) || (ldx & 7) || (ldo & 7) || status == nullptr) return MSGL_ERR_SIZE;
     if (((uintptr_t)W | (uintptr_t)X | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
     const int I = N / 2;
@@ -422,7 +512,7 @@ MSGL_API int msgl_gemm_tc2(const void* W, const void* X, const void* bias, void*
     CUtensorMap xm, wm;
     if (!tc_matrix_map(X, M, K, ldx * 2, 128, &xm) || !tc_matrix_map(W, N, K, (long long)K * 2, 128, &wm)) return MSGL_ERR_SIZE;
     const int n_valid = mode == 1 ? I : N, bn_out = mode == 1 ? 128 : 256;
-    const long long tiles = (long long)((M + 255) / 256) * ((n_valid + bn_out - 1) / bn_out);
+    const long long tiles = (long long)((M + 255) / 256) * ((n_valid + bn_out - 1) / bn_out) * splits;      // work items
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -452,8 +542,41 @@ MSGL_API int msgl_gemm_tc2(const void* W, const void* X, const void* bias, void*
     __nv_bfloat16* o = (__nv_bfloat16*)out;
     int* st = (int*)status;
     const int Iarg = mode == 1 ? I : 0;
-    cudaError_t e = mode == 1 ? cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<true>, xm, wm, b, o, M, N, K, ldo, Iarg, st)
-                              : cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<false>, xm, wm, b, o, M, N, K, ldo, Iarg, st);
+    float* part = (float*)partials;
+    if (splits <= 1) part = nullptr;
+    cudaError_t e = mode == 1 ? cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<true>, xm, wm, b, o, M, N, K, ldo, Iarg, st, splits, part)
+                              : cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<false>, xm, wm, b, o, M, N, K, ldo, Iarg, st, splits, part);
     (void)e;
+    if (part == nullptr) return msgl_check_launch();
+    // the ranges' partial sums -> output (bias / SwiGLU, one rounding), in range order
+    const int n_out = mode == 1 ? I : N;
+    const long long groups = (long long)M * ((n_out + 3) / 4);
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((groups + threads - 1) / threads);
+    if (mode == 1) msgl_launch_pdl(gemm_splitk_reduce_kernel<true>, dim3(blocks), dim3(threads), 0, stream, (const float*)part, splits, M, N, I, b, o, ldo);
+    else msgl_launch_pdl(gemm_splitk_reduce_kernel<false>, dim3(blocks), dim3(threads), 0, stream, (const float*)part, splits, M, N, I, b, o, ldo);
     return msgl_check_launch();
+}
+
+MSGL_API int msgl_gemm_tc2(const void* W, const void* X, const void* bias, void* out, int M, int N, int K, long long ldx,
+                           long long ldo, int mode, void* status, cudaStream_t stream) {
+    return msgl_gemm_tc2_splitk(W, X, bias, out, M, N, K, ldx, ldo, mode, 1, nullptr, status, stream);
+}
+
+// How many ranges of K the split-K product should use for these sizes on the current device: the count (at most 8, at
+// least 8 slabs of 64 each) for which the work items fill the pairs of SMs in the fewest rounds of the shortest items.
+MSGL_API int msgl_gemm_tc2_splits(int M, int N, int K, int mode) {
+    const int n_out = mode == 1 ? N / 2 : N, bn_out = mode == 1 ? 128 : 256;
+    const long long tiles = (long long)((M + 255) / 256) * ((n_out + bn_out - 1) / bn_out);
+    const int n_slabs = (K + GT_BK - 1) / GT_BK;
+    const int pairs = msgl_sm_count() / 2;
+    int best = 1;
+    double best_cost = 1e30;
+    for (int sp = 1; sp <= 8 && sp * 8 <= n_slabs; ++sp) {
+        const long long items = tiles * sp;
+        const long long rounds = (items + pairs - 1) / pairs;
+        const double cost = (double)rounds * ((n_slabs + sp - 1) / sp + 3) + (sp > 1 ? 0.5 * sp : 0.0);      // + 3: filling the pipeline
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = sp; }
+    }
+    return best;
 }

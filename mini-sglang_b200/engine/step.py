@@ -32,7 +32,8 @@ from ..weights import CheckpointSource, RandomSource
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 MAX_KV_SPLIT = 16
-MIN_KEYS_PER_SPLIT = 256
+MIN_KEYS_PER_SPLIT = 128          # 64 / 128 / 256 / 512 measured at 1 to 8 requests of 1k to 4k keys: 128 best or level (batch 1, 4,096 keys: 3.46 against 3.54 ms with 256)
+MIN_KEYS_PER_PIECE = 256          # shortest piece when a single long request is cut up among many short ones
 LONG_REQUEST_FACTOR = 1.5         # a request beyond this many times the mean load per block is cut up (1.0, 1.25, 1.5 measured: 1.5 best)
 BALANCE_MIN_KEYS = 6144           # mean keys a request from which halving every request to even out the SMs pays
 WIDE_KV_SPLIT = 8                 # cap of the decode graphs that are captured for batches with such requests
@@ -153,14 +154,14 @@ def plan_kv_splits(q_lens: Sequence[int], kv_lens: Sequence[int], *, n_kv: int, 
     want = slots // max(blocks, 1)                    # fill the SMs once, not more
     keys = [min(kv, window + q) if window else kv for q, kv in zip(q_lens, kv_lens)]
     load = sum(k for q, k in zip(q_lens, keys) if q <= tile_tokens) * heads / slots      # keys per resident block, dealt out evenly
-    piece = max(MIN_KEYS_PER_SPLIT, int(load * LONG_REQUEST_FACTOR))
+    piece = max(MIN_KEYS_PER_PIECE, int(load * LONG_REQUEST_FACTOR))
     out = []
     for q, k in zip(q_lens, keys):
         if q > tile_tokens:
             out.append(1)                             # one decode tile at most
             continue
         even = _fewest_splits_as_fast(k, min(want, k // MIN_KEYS_PER_SPLIT, cap), warps)
-        long_one = min(-(-k // piece), k // MIN_KEYS_PER_SPLIT, long_cap) if k > piece else 1      # no piece below the minimum
+        long_one = min(-(-k // piece), k // MIN_KEYS_PER_PIECE, long_cap) if k > piece else 1      # no piece below the minimum
         out.append(max(1, even, long_one))
     # Many requests of like, long contexts and nothing cut so far: the kernel's time follows the largest number of
     # blocks that one SM gets, so a launch of 3.5 blocks per SM runs as long as one of 4.  Twice as many blocks of half
@@ -173,7 +174,7 @@ def plan_kv_splits(q_lens: Sequence[int], kv_lens: Sequence[int], *, n_kv: int, 
         uneven_halved = -(-2 * n_blocks // sm_count) * sm_count / (2 * n_blocks) - 1.0
         if uneven >= 0.08 and uneven_halved <= uneven - 0.04 and sum(keys[i] for i in cut) >= BALANCE_MIN_KEYS * len(cut):
             for i in cut:
-                if keys[i] >= 2 * MIN_KEYS_PER_SPLIT:
+                if keys[i] >= 2 * MIN_KEYS_PER_PIECE:
                     out[i] = 2
     return out
 

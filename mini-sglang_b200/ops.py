@@ -90,6 +90,10 @@ def _lib():
         lib.msgl_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_int, c_void_p,
                                      c_void_p]
         lib.msgl_gemm_tc2.argtypes = lib.msgl_gemm_tc.argtypes
+        lib.msgl_gemm_tc2_splitk.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int,
+                                             c_void_p, c_void_p, c_void_p]
+        lib.msgl_gemm_tc2_splits.argtypes = [c_int, c_int, c_int, c_int]
+        lib.msgl_gemm_tc2_splits.restype = c_int
         lib.msgl_sample.argtypes = [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_ull, c_void_p,
                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         _common = lib
@@ -477,6 +481,54 @@ def _tc_gemm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]
     return out
 
 
+# Between the weight-streaming kernel (up to SMALL_M_MAX rows) and the tiled tcgen05 kernel (from TC_GEMM_MIN_M rows) a product has
+# too few output tiles to fill the GPU: there the pair kernel cuts K into ranges as well (split-K) and a second kernel adds
+# the ranges' float32 partial sums in order.  Off unless MSGL_TC_MID=1: measured on B200 at Qwen3-8B's sizes it is behind the
+# library GEMM at 16 to 128 rows (qkv 18-26 against 12.5 us, o 15-21 against 10, gate/up + SwiGLU 44-66 against 42-45, down 26-33
+# against 21-22 us), so these sizes stay with the library.
+MID_GEMM = os.environ.get("MSGL_TC_MID", "0") == "1"
+MID_GEMM_SPLITS = int(os.environ.get("MSGL_TC_MID_SPLITS", "0"))        # 0: chosen per size
+_mid_partials = {}
+_mid_splits = {}
+
+
+def _tc_gemm_mid(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], mode: int) -> Optional[torch.Tensor]:
+    """x @ weight^T (mode 0) or SwiGLU of it (mode 1) for a middling number of rows by the split-K tcgen05 kernel; None where
+    it does not apply."""
+    global _tc_gemm_usable
+    if not (MID_GEMM and TC_GEMM != "0" and TC_GEMM_CTAS == 2 and _tc_gemm_usable and x.dtype == torch.bfloat16
+            and weight.dtype == torch.bfloat16 and x.dim() == 2 and SMALL_M_MAX < x.shape[0] < TC_GEMM_MIN_M and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and weight.is_contiguous() and weight.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0
+            and weight.shape[1] >= 512 and (bias is None or bias.dtype == torch.bfloat16)):
+        return None
+    M, (N, K) = x.shape[0], weight.shape
+    n_out = N // 2 if mode == 1 else N
+    if n_out % 8 or (mode == 1 and N % 16):
+        return None
+    key = (M, N, K, mode)
+    splits = MID_GEMM_SPLITS or _mid_splits.get(key)
+    if not splits:
+        splits = _mid_splits[key] = int(_lib().msgl_gemm_tc2_splits(M, N, K, mode))
+    splits = max(1, min(splits, K // 64))
+    part = None
+    if splits > 1:
+        dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
+        part = _mid_partials.get(dev)
+        if part is None or part.numel() < splits * M * N:
+            part = _mid_partials[dev] = torch.empty(max(splits * M * N, 1 << 22), dtype=torch.float32, device=x.device)
+    out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    code = _lib().msgl_gemm_tc2_splitk(_ptr(weight), _ptr(x), _ptr(bias), _ptr(out), M, N, K, x.stride(0), n_out, mode, splits,
+                                       _ptr(part), _ptr(_status_tensor(x.device)), _stream())
+    if code == 2:             # no tensor maps on this driver
+        _tc_gemm_usable = False
+        return None
+    _check(code, "gemm_tc (split-K)")
+    if splits > 1:
+        global LAUNCHES
+        LAUNCHES += 1
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y = x @ weight^T (+ bias); weight is [out, in] as stored in the checkpoint.
@@ -492,7 +544,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         _check(code, "gemm_small_m")
         return out
     if out_dtype in (None, torch.bfloat16):
-        y = _tc_gemm(x, weight, bias, 0)
+        y = _tc_gemm(x, weight, bias, 0) if x.shape[0] >= TC_GEMM_MIN_M else _tc_gemm_mid(x, weight, bias, 0)
         if y is not None:
             return y
     if out_dtype is not None and out_dtype != x.dtype:
@@ -513,7 +565,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
         code = _small_m(gate_up, x, None, out, M, N, K, N // 2, 1, 0)
         _check(code, "gemm_small_m (swiglu)")
         return out
-    y = _tc_gemm(x, gate_up, None, 1)
+    y = _tc_gemm(x, gate_up, None, 1) if x.shape[0] >= TC_GEMM_MIN_M else _tc_gemm_mid(x, gate_up, None, 1)
     if y is not None:
         return y
     return swiglu(torch.nn.functional.linear(x, gate_up))

@@ -445,7 +445,7 @@ def test_policies_order():
 # the step function's plan of kv splits (pure arithmetic on the host)
 # ---------------------------------------------------------------------------------------
 def test_kv_split_plan():
-    from mini_sglang_b200.engine.step import MIN_KEYS_PER_SPLIT, plan_kv_splits
+    from mini_sglang_b200.engine.step import MIN_KEYS_PER_PIECE, MIN_KEYS_PER_SPLIT, plan_kv_splits
     SM_COUNT = 148                     # a B200's
     geo = dict(n_kv=8, group=4, blocks_per_sm=4, tile_tokens=2, window=None, sm_count=SM_COUNT)
     slots = SM_COUNT * 4
@@ -469,15 +469,16 @@ def test_kv_split_plan():
     assert plan_kv_splits([1] * 40, [4096] * 40, cap=1, long_cap=8, **geo) == [2] * 40
     # one request far longer than the rest is cut into pieces of about the mean load of a block, the others stay whole
     ns = plan_kv_splits([1] * 65, [1200] + [20] * 64, cap=1, long_cap=8, **geo)
-    assert ns[0] == 1200 // MIN_KEYS_PER_SPLIT and ns[1:] == [1] * 64
+    assert ns[0] == 1200 // MIN_KEYS_PER_PIECE and ns[1:] == [1] * 64
     ns = plan_kv_splits([1] * 48, [8192] + [1024] * 47, cap=1, long_cap=8, **geo)
     assert 2 <= ns[0] <= 8 and ns[1:] == [1] * 47
     # runs longer than one decode tile go whole to the prefill kernels, whatever their length; they do not count as load
-    ns = plan_kv_splits([1, 5, 1], [8192, 8192, 300], cap=16, **geo)
+    ns = plan_kv_splits([1, 5, 1], [8192, 8192, 200], cap=16, **geo)
     assert ns[1] == 1 and ns[0] > 1 and ns[2] == 1
     # a window bounds the keys that count
     geo_w = dict(geo, window=512)
-    assert plan_kv_splits([1] * 8, [4096] * 8, cap=16, **geo_w) == [513 // MIN_KEYS_PER_SPLIT] * 8
+    # 513 keys: at most 513 // MIN_KEYS_PER_SPLIT = 4 pieces; 33 units of 16 keys are 3 a warp in 3 pieces as in 4
+    assert plan_kv_splits([1] * 8, [4096] * 8, cap=16, **geo_w) == [3] * 8
     # wide groups take several blocks per kv head: fewer splits fill the SMs
     wide = dict(n_kv=2, group=32, blocks_per_sm=4, tile_tokens=1, window=None, sm_count=SM_COUNT)
     assert plan_kv_splits([1] * 16, [8192] * 16, cap=16, **wide) == [slots // (16 * 2 * 2)] * 16

@@ -143,6 +143,42 @@ def test_tcgen05_gemm(M, N, K, ctas, monkeypatch):
     o.check_kernel_status()
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(9, 256, 512, 0), (16, 6144, 4096, 0), (64, 528, 1032, 3), (100, 1040, 4104, 8),
+                                          (200, 4096, 12288, 0), (33, 264, 576, 2), (48, 272, 640, 1)])
+def test_tcgen05_gemm_split_k(M, N, K, splits, monkeypatch):
+    """The pair kernel with K cut into ranges (few tokens, so too few output tiles to fill the GPU) and the kernel that adds
+    the ranges' partial sums: the count of ranges chosen by the library or given, tiles that end inside the matrices, a bias,
+    SwiGLU after the sum; against float32 products of the same bfloat16 operands, and the same bits on a second run."""
+    o = ops()
+    monkeypatch.setattr(o, "MID_GEMM", True)
+    monkeypatch.setattr(o, "MID_GEMM_SPLITS", splits)
+    g = torch.Generator(device="cpu").manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV)
+    ref = x.float() @ w.float().T
+    before = o.LAUNCHES
+    y = o._tc_gemm_mid(x, w, None, 0)
+    assert y is not None and y.dtype == torch.bfloat16 and y.shape == (M, N)
+    if splits > 1:
+        assert o.LAUNCHES - before == 2                      # the product and the sum of the ranges
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+    assert torch.equal(y, o._tc_gemm_mid(x, w, None, 0))
+    torch.testing.assert_close(o._tc_gemm_mid(x, w, b, 0).float(), ref + b.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(o.linear(x, w, b).float(), ref + b.float(), rtol=2e-2, atol=2e-2)      # the engine's entry point
+    if (N // 2) % 8 == 0:
+        z = o._tc_gemm_mid(x, w, None, 1)
+        gate, up = ref[:, :N // 2], ref[:, N // 2:]
+        assert z.shape == (M, N // 2)
+        torch.testing.assert_close(z.float(), gate / (1 + torch.exp(-gate)) * up, rtol=2e-2, atol=2e-2)
+        assert torch.equal(o.linear_swiglu(x, w), z)
+        monkeypatch.setattr(o, "MID_GEMM", False)                    # the library product and the activation kernel
+        torch.testing.assert_close(o.linear_swiglu(x, w).float(), z.float(), rtol=3e-2, atol=3e-2)
+    else:
+        assert o._tc_gemm_mid(x, w, None, 1) is None                 # refused, not computed wrongly
+    o.check_kernel_status()
+
+
 # ---------------------------------------------------------------------------------------
 def rope_table(max_pos, rot, theta):
     idx = torch.arange(0, rot, 2, dtype=torch.float32)
