@@ -5,6 +5,8 @@
                                                     prefix, 256 new tokens each, through the scheduler (Qwen3-0.6B sizes)
     python bench.py --workload qwen3_32b_long       an 8,192-token prompt in portions of 2,048, then decode at batch 16
                                                     and context 8,192 (Qwen3-32B sizes)
+    python bench.py --workload sweep                decode at batch 1 / 8 / 64 and contexts of 1k to 32k, prefill of 512 to
+                                                    16,384 tokens, each with its fraction of the measured peak (Qwen3-8B sizes)
 
 Default run: Qwen3-8B layer sizes with random weights (N(0, 0.02), bfloat16), a batch of 8
 requests at a context of 4,096 tokens, KV page size 16.  A "step" is one decode step of the
@@ -413,6 +415,80 @@ def workload_long(args):
     return 0
 
 
+def workload_sweep(args):
+    """Qwen3-8B sizes: the decode step at several batch sizes and context lengths (bytes it has to read / time against the
+    measured copy bandwidth) and the prefill of one prompt of several lengths, fed in portions of at most 8,192 tokens
+    (flops / time against the measured bf16 peak).  One JSON line."""
+    import torch
+
+    from mini_sglang_b200 import Engine, EngineArgs
+    from mini_sglang_b200.engine.step import StepEntry
+    cfg = dict(QWEN3_8B)
+    cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    PAGE, W, K = 16, 5, 24
+    V = cfg["vocab_size"]
+    gen = torch.Generator().manual_seed(0)
+
+    def rand_tokens(n):
+        return torch.randint(0, V, (n,), generator=gen).tolist()
+
+    clocks = ClockSampler()
+    clocks.start()
+    eng = Engine(EngineArgs(model=_write_config(cfg), dummy_load=True, random_seed=0, page_size=PAGE, num_pages=34000,
+                            max_num_reqs=66, max_context_len=32768 + 64, max_prefill_tokens=8192, chunk_size=8192,
+                            disable_radix_cache=True, schedule_policy="fcfs", log_level="WARNING"))
+    runner = eng.runner
+    _, weight_bytes, kv_tok = model_sizes(cfg)
+    decode, prefill = [], []
+    for batch, ctx in ((1, 1024), (1, 4096), (1, 32768), (8, 1024), (8, 4096), (8, 16384), (8, 32768), (64, 1024), (64, 4096), (64, 8192)):
+        prompt_len = ctx - (W + K) - 1
+        slots = [runner.open() for _ in range(batch)]
+        for s in slots:
+            toks = rand_tokens(prompt_len)
+            for i in range(0, prompt_len, 8192):
+                runner.step([StepEntry(s, toks[i:i + 8192], [])])
+        feed = [[rand_tokens(1) for _ in slots] for _ in range(W + K)]
+        for i in range(W):
+            runner.step([StepEntry(s, t, [0]) for s, t in zip(slots, feed[i])])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(W, W + K):
+            runner.step([StepEntry(s, t, [0]) for s, t in zip(slots, feed[i])])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / K
+        for s in slots:
+            runner.close(s)
+        need = weight_bytes + batch * (ctx - K // 2) * kv_tok
+        decode.append({"batch": batch, "context": ctx, "ms_per_step": round(ms, 3), "tokens_per_s": round(batch / ms * 1e3, 1),
+                       "hbm_frac": round(need / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)})
+    for n in (512, 2048, 8192, 16384):
+        times = []
+        for rep in range(4):
+            toks = rand_tokens(n)
+            s = runner.open()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(0, n, 8192):
+                runner.step([StepEntry(s, toks[i:i + 8192], [min(8192, n - i) - 1] if i + 8192 >= n else [])])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            runner.close(s)
+        ms = sorted(times[1:])[1]
+        flops = sum(step_flops(cfg, [min(8192, n - i)], [min(n, i + 8192)], 1 if i + 8192 >= n else 0) for i in range(0, n, 8192))
+        prefill.append({"tokens": n, "ms": round(ms, 3), "tokens_per_s": round(n / ms * 1e3, 1),
+                        "bf16_frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 3)})
+    clocks.stop()
+    print(json.dumps({"workload": "sweep", "model": "Qwen3-8B shape", "layers": cfg["num_hidden_layers"], "dtype": "bf16", "page_size": PAGE,
+                      "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]},
+                      "decode": decode, "prefill": prefill, "clocks": clocks.summary(), "impl": "ours"}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -428,7 +504,7 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="cudaProfilerStart/Stop around the timed region (ncu --profile-from-start off)")
     ap.add_argument("--no-graph", action="store_true", help="decode without CUDA graphs")
-    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep"],
                     help="headline: the line the contract names; the others: further workloads, one JSON line each")
     ap.add_argument("--skip-sanity", action="store_true", help="no comparison with the plain implementation before timing")
     args = ap.parse_args()
@@ -441,6 +517,8 @@ def main():
         return workload_mixed(args)
     if args.workload == "qwen3_32b_long":
         return workload_long(args)
+    if args.workload == "sweep":
+        return workload_sweep(args)
 
     import torch
 
@@ -572,10 +650,10 @@ def main():
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            ms_b, _, _ = timed_decode(b, max(K // 2, 8), W)
+            ms_b, _, _ = timed_decode(b, max(K, 32), W)
             points[f"decode_b{b}"] = round(b / (ms_b * 1e-3), 1)
         for b in (1, 8, 64):                      # right after 2,048-token prompts
-            ms_b, _, _ = timed_decode(b, max(K // 2, 8), W, prompt_len=PREFILL)
+            ms_b, _, _ = timed_decode(b, max(K, 32), W, prompt_len=PREFILL)
             points[f"decode_b{b}_ctx2048"] = round(b / (ms_b * 1e-3), 1)
 
     # ---- prefill of 2,048 tokens in one step

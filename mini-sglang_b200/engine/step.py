@@ -31,7 +31,8 @@ from ..parts import BuildEnv, DecoderModel, GroupContext, KVCacheView, StateCach
 from ..weights import CheckpointSource, RandomSource
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
-MAX_KV_SPLIT = 16
+MAX_KV_SPLIT = 32                 # more than MANY_SPLITS pieces only where they stay long (below)
+MANY_SPLITS, MANY_SPLITS_MIN_KEYS = 16, 512      # one request of 32k keys: 16 pieces 4.54, 32 pieces 4.29 ms a step; of 4k keys: 3.37 / 3.44
 MIN_KEYS_PER_SPLIT = 128          # 64 / 128 / 256 / 512 measured at 1 to 8 requests of 1k to 4k keys: 128 best or level (batch 1, 4,096 keys: 3.46 against 3.54 ms with 256)
 MIN_KEYS_PER_PIECE = 256          # shortest piece when a single long request is cut up among many short ones
 LONG_REQUEST_FACTOR = 1.5         # a request beyond this many times the mean load per block is cut up (1.0, 1.25, 1.5 measured: 1.5 best)
@@ -160,7 +161,8 @@ def plan_kv_splits(q_lens: Sequence[int], kv_lens: Sequence[int], *, n_kv: int, 
         if q > tile_tokens:
             out.append(1)                             # one decode tile at most
             continue
-        even = _fewest_splits_as_fast(k, min(want, k // MIN_KEYS_PER_SPLIT, cap), warps)
+        most = max(min(k // MIN_KEYS_PER_SPLIT, MANY_SPLITS), k // MANY_SPLITS_MIN_KEYS)
+        even = _fewest_splits_as_fast(k, min(want, most, cap), warps)
         long_one = min(-(-k // piece), k // MIN_KEYS_PER_PIECE, long_cap) if k > piece else 1      # no piece below the minimum
         out.append(max(1, even, long_one))
     # Many requests of like, long contexts and nothing cut so far: the kernel's time follows the largest number of
