@@ -240,7 +240,8 @@ MSGL_API int msgl_rmsnorm(const void* x, const float* res_in, float* res_out, co
 //
 //   qkv row layout: [ q: n_q*d | k: n_kv*d | v: n_kv*d ],  row stride `qkv_stride` elements
 //   table: [max_pos, rot] float32 = cos(angles) | sin(angles), rot/2 each; halves of the
-//          first `rot` elements of a head are rotated against each other (NeoX style)
+//          first `rot` elements of a head are rotated against each other: halves (element i with i + rot/2, NeoX style)
+//          or, with `interleaved`, neighbours (2 p with 2 p + 1)
 //   cache layout per layer: [page][kv head][slot in page][d]; token slot s = page*P + offset
 // ---------------------------------------------------------------------------------------
 #define QKR_MAX_PER_LANE 16   // head sizes up to 512
@@ -251,7 +252,7 @@ __global__ void qknorm_rope_kvwrite_kernel(const T* __restrict__ qkv, int qkv_st
                                            const void* __restrict__ qw, const void* __restrict__ kw, int w_is_f32,
                                            float eps, const float* __restrict__ table, int rot, int max_pos,
                                            T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                                           int page_size, int n_q, int n_kv, int d) {
+                                           int page_size, int n_q, int n_kv, int d, int interleaved) {
     const int t = blockIdx.x;
     const int warps = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -309,13 +310,16 @@ __global__ void qknorm_rope_kvwrite_kernel(const T* __restrict__ qkv, int qkv_st
         const int half = rot >> 1;
         for (int i = lane; i < d; i += 32) {
             float o;
-            if (i < half) {
+            if (i >= rot) {
+                o = hv[i];
+            } else if (interleaved) {           // pairs (2 p, 2 p + 1) share angle p
+                const int p = i >> 1;
+                o = (i & 1) ? hv[i - 1] * cs[half + p] + hv[i] * cs[p] : hv[i] * cs[p] - hv[i + 1] * cs[half + p];
+            } else if (i < half) {              // halves: element i pairs with i + rot / 2
                 o = hv[i] * cs[i] - hv[i + half] * cs[half + i];
-            } else if (i < rot) {
+            } else {
                 const int p = i - half;
                 o = hv[p] * cs[half + p] + hv[i] * cs[p];
-            } else {
-                o = hv[i];
             }
             dst[i] = from_f32<T>(o);
         }
@@ -459,7 +463,7 @@ MSGL_API int msgl_qknorm_rope_kvwrite(const void* qkv, int qkv_stride, const int
                                       const void* qw, const void* kw, int w_is_f32, float eps,
                                       const float* table, int rot, int max_pos, void* q_out, void* k_cache,
                                       void* v_cache, int page_size, int n_q, int n_kv, int d, int T_, int dtype,
-                                      cudaStream_t stream) {
+                                      int interleaved, cudaStream_t stream) {
     if (T_ <= 0) return MSGL_OK;
     if (d <= 0 || d > 32 * QKR_MAX_PER_LANE || rot < 0 || rot > d || (rot & 1) || page_size <= 0) return MSGL_ERR_SIZE;
     const int n_heads = n_q + 2 * n_kv;
@@ -468,7 +472,7 @@ MSGL_API int msgl_qknorm_rope_kvwrite(const void* qkv, int qkv_stride, const int
     const size_t smem = table ? (size_t)warps * d * sizeof(float) : 0;
     const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 31) == 0 &&
                          (qkv_stride % (d / 32 > 0 ? d / 32 : 1)) == 0;
-    if (aligned && (d == 32 || d == 64 || d == 128 || d == 256) && (table == nullptr || rot == d) &&
+    if (aligned && (d == 32 || d == 64 || d == 128 || d == 256) && (table == nullptr || (rot == d && !interleaved)) &&
         (dtype == MSGL_F32 || dtype == MSGL_BF16)) {
 #define QKR_VEC(TT, EE)                                                                                              \
     msgl_launch_pdl(qknorm_rope_kvwrite_vec_kernel<TT, EE>, dim3((T_ + QKR_TOK - 1) / QKR_TOK, grid.y), dim3(warps * 32), 0, stream, \
@@ -487,11 +491,11 @@ MSGL_API int msgl_qknorm_rope_kvwrite(const void* qkv, int qkv_stride, const int
     if (dtype == MSGL_F32)
         qknorm_rope_kvwrite_kernel<float><<<grid, warps * 32, smem, stream>>>(
             (const float*)qkv, qkv_stride, positions, out_loc, qw, kw, w_is_f32, eps, table, rot, max_pos,
-            (float*)q_out, (float*)k_cache, (float*)v_cache, page_size, n_q, n_kv, d);
+            (float*)q_out, (float*)k_cache, (float*)v_cache, page_size, n_q, n_kv, d, interleaved);
     else if (dtype == MSGL_BF16)
         qknorm_rope_kvwrite_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(
             (const __nv_bfloat16*)qkv, qkv_stride, positions, out_loc, qw, kw, w_is_f32, eps, table, rot, max_pos,
-            (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_size, n_q, n_kv, d);
+            (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_size, n_q, n_kv, d, interleaved);
     else
         return MSGL_ERR_DTYPE;
     return msgl_check_launch();

@@ -506,15 +506,18 @@ class ModelRunner:
         mp = tuple(max(8, 1 << (n - 1).bit_length()) for n in need_pages)
         # the graph fixes the launch's split dimension: the narrow one suits requests of like length; a batch
         # with a request far longer than the rest takes a second graph with room for more pieces
-        narrow = [self._graph_max_split(gi, b) for gi in range(len(self.mgr.groups))]
+        room = [self._graph_max_split(gi, b) for gi in range(len(self.mgr.groups))]
+        narrow = [min(c, MANY_SPLITS) for c in room]
         fused = self._fused_blocks(b)
-        nsplits = [self._plan_splits(gi, q_lens, kv_lens, narrow[gi], max(narrow[gi], WIDE_KV_SPLIT), fused_blocks=fused)
+        nsplits = [self._plan_splits(gi, q_lens, kv_lens, room[gi], max(narrow[gi], WIDE_KV_SPLIT), fused_blocks=fused)
                    for gi in range(len(self.mgr.groups))]
+        # blocks of pieces that a request does not have leave at once, but they are launched: a graph with the split
+        # dimension of long contexts (up to MAX_KV_SPLIT) is kept apart from the one that every other step replays
         wide = any(max(ns) > cap for ns, cap in zip(nsplits, narrow))
         key = (b, mp, wide)
         gr = self._graphs.get(key)
         if gr is None:
-            gr = self._capture(b, mp, [max(c, WIDE_KV_SPLIT) for c in narrow] if wide else narrow)
+            gr = self._capture(b, mp, [max(c, r, WIDE_KV_SPLIT) for c, r in zip(narrow, room)] if wide else narrow)
             self._graphs[key] = gr
         self.last_plan = {"graph_key": key, "nsplits": nsplits, "max_split": list(gr.max_split)}
         lay = gr.layout

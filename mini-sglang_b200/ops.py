@@ -82,7 +82,7 @@ def _lib():
                                      c_int, c_int, c_int, c_void_p]
         lib.msgl_qknorm_rope_kvwrite.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                  c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+                                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.msgl_swiglu.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.msgl_cast_from_f32.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_void_p]
         lib.msgl_gemm_small_m.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_int,
@@ -175,10 +175,11 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, n_q: int, n_
                         q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                         rope_table: Optional[torch.Tensor], out_loc: Optional[torch.Tensor],
                         k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], page_size: int,
-                        q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        q_out: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
     """Per-head RMSNorm of q and k (if weights are given), rotary encoding from `rope_table`
-    [max_pos, rot] float32 (if given), k and v written to the paged cache at token slots `out_loc`
-    (if a cache is given), q returned as [T, n_q, d]."""
+    [max_pos, rot] float32 = cos | sin (if given; the first `rot` elements of a head are rotated in halves, element i
+    against i + rot/2, or with `interleaved` in neighbouring pairs 2p, 2p+1), k and v written to the paged cache at token
+    slots `out_loc` (if a cache is given), q returned as [T, n_q, d]."""
     _need_cuda(qkv, positions, q_weight, k_weight, rope_table, out_loc, k_cache, v_cache)
     T = qkv.shape[0]
     assert qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (n_q + 2 * n_kv) * d
@@ -199,7 +200,7 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, n_q: int, n_
     code = _lib().msgl_qknorm_rope_kvwrite(_ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(out_loc), _ptr(q_weight),
                                            _ptr(k_weight), w_f32, float(eps), _ptr(rope_table), rot, max_pos,
                                            _ptr(q_out), _ptr(k_cache), _ptr(v_cache), page_size, n_q, n_kv, d, T,
-                                           _dt(qkv), _stream())
+                                           _dt(qkv), int(bool(interleaved)), _stream())
     _check(code, f"qknorm_rope_kvwrite (head size {d})")
     return q_out
 

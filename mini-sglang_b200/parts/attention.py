@@ -77,7 +77,8 @@ class PagedAttention(Mixer):
         return PagedKVNeed(self.n_kv, self.d, self.window, q_heads=self.n_q)
 
     def fused_decode_fields(self):
-        if self.window is not None or (self.position is not None and self.position.fused_decode_fields() is None):
+        if self.window is not None or (self.position is not None and (self.position.fused_decode_fields() is None
+                                                                      or self.position.interleaved)):
             return None
         rope = self.position.fused_decode_fields() if self.position is not None else None
         return {"kind": "paged_attention", "qkv": self.qkv, "qkv_bias": self.qkv_b, "o": self.o, "q_norm": self.q_norm,
@@ -93,7 +94,7 @@ class PagedAttention(Mixer):
             q_weight=self.q_norm, k_weight=self.k_norm, eps=self.qk_norm_eps, rope_table=table,
             out_loc=cache.group.out_loc if writes_cache else None,
             k_cache=cache.k if writes_cache else None, v_cache=cache.v if writes_cache else None,
-            page_size=cache.page_size)
+            page_size=cache.page_size, interleaved=bool(getattr(self.position, "interleaved", False)))
         out = torch.empty_like(q)
         self.attend(q, out, ctx, cache)
         return ops.linear(out.view(ctx.T, self.n_q * self.d), self.o)

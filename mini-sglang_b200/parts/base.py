@@ -91,9 +91,13 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     """A position encoding that the attention mixer applies to q and k: a rotation of the first
-    `rotary_dim` elements of every head (NeoX halves) by angles that depend on the position and the
-    element pair in any way the encoding likes.  (An encoding that is added to the hidden state instead
+    `rotary_dim` elements of every head (in halves or in neighbouring pairs, see `interleaved`) by angles that
+    depend on the position and the element pair in any way the encoding likes.  (An encoding that is added to the hidden state instead
     belongs to an embedding part.)"""
+
+    # which elements are rotated against each other: False: halves (element i with i + rotary_dim / 2, NeoX style);
+    # True: neighbours (2 p with 2 p + 1, GPT-J style).  Pair p takes angle p of the table either way.
+    interleaved = False
 
     def rotary_table(self) -> Optional[torch.Tensor]:
         """float32 [max_positions, rotary_dim] = cos | sin of the angles; rotary_dim may be smaller than

@@ -187,6 +187,7 @@ def rope_table(max_pos, rot, theta):
     return torch.cat((fr.cos(), fr.sin()), -1)
 
 
+@pytest.mark.parametrize("interleaved", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n_q,n_kv,d,rot,P,norm,wdtype", [
     (4, 2, 16, 16, 1, True, torch.bfloat16),
@@ -199,7 +200,9 @@ def rope_table(max_pos, rot, theta):
     (5, 5, 64, 64, 3, True, torch.float32),
     (2, 1, 128, 0, 16, False, torch.bfloat16),
 ])
-def test_qknorm_rope_kvwrite(dtype, n_q, n_kv, d, rot, P, norm, wdtype):
+def test_qknorm_rope_kvwrite(dtype, n_q, n_kv, d, rot, P, norm, wdtype, interleaved):
+    if interleaved and rot == 0:
+        pytest.skip("no rotation: nothing to pair")
     g = torch.Generator(device="cpu").manual_seed(3)
     T, max_pos, eps = 19, 300, 1e-6
     pages = -(-T // P) + 3
@@ -213,7 +216,8 @@ def test_qknorm_rope_kvwrite(dtype, n_q, n_kv, d, rot, P, norm, wdtype):
     vc = torch.zeros_like(kc)
     cu = lambda t: None if t is None else t.to(DEV)
     q = ops().qknorm_rope_kvwrite(cu(qkv), cu(pos), n_q, n_kv, d, q_weight=cu(qw), k_weight=cu(kw), eps=eps,
-                                  rope_table=cu(table), out_loc=cu(loc), k_cache=kc, v_cache=vc, page_size=P)
+                                  rope_table=cu(table), out_loc=cu(loc), k_cache=kc, v_cache=vc, page_size=P,
+                                  interleaved=interleaved)
     # reference
     x = qkv.float()
     qr = x[:, :n_q * d].reshape(T, n_q, d)
@@ -227,6 +231,9 @@ def test_qknorm_rope_kvwrite(dtype, n_q, n_kv, d, rot, P, norm, wdtype):
         c, s = cs[:, None, :rot // 2], cs[:, None, rot // 2:]
 
         def rope(t):
+            if interleaved:                       # neighbours 2 p, 2 p + 1 with angle p
+                a, b, rest = t[..., 0:rot:2], t[..., 1:rot:2], t[..., rot:]
+                return torch.cat((torch.stack((a * c - b * s, a * s + b * c), -1).flatten(-2), rest), -1)
             a, b, rest = t[..., :rot // 2], t[..., rot // 2:rot], t[..., rot:]
             return torch.cat((a * c - b * s, a * s + b * c, rest), -1)
         qr, kr = rope(qr), rope(kr)

@@ -367,10 +367,12 @@ def _register_routed_toy():
     if "toy_linear_rotary" not in POSITION_ENCODINGS:
         @register_position_encoding("toy_linear_rotary")
         class LinearRotary(PositionEncoding):
-            """angle(p, i) = p * step * (i + 1) over the first `rot` elements of a head (NeoX halves)."""
+            """angle(p, i) = p * step * (i + 1) over the first `rot` elements of a head, rotated in halves or, with
+            the parameter `interleaved`, in neighbouring pairs."""
 
             def __init__(self, spec, prefix, env):
                 super().__init__(spec, prefix, env)
+                self.interleaved = bool(spec.get("interleaved", False))
                 p = torch.arange(spec["max_positions"], dtype=torch.float32)[:, None]
                 ang = p * spec["step"] * torch.arange(1, spec["rot"] // 2 + 1, dtype=torch.float32)[None, :]
                 self.table = torch.cat((ang.cos(), ang.sin()), -1).contiguous().to(env.device)
@@ -393,12 +395,13 @@ def _register_routed_toy():
         routed = PartSpec("toy_top1_experts", {"hidden_size": H, "intermediate_size": r["ffn"], "experts": 3})
         dense = PartSpec("swiglu_mlp", {"hidden_size": H, "intermediate_size": r["ffn"]})
         pos = PartSpec("toy_linear_rotary", {"rot": 8, "step": r["step"], "max_positions": 128})
+        pos_pairs = PartSpec("toy_linear_rotary", {"rot": 8, "step": r["step"], "max_positions": 128, "interleaved": True})
         att = lambda window: PartSpec("paged_attention", {"hidden_size": H, "num_heads": 6, "num_kv_heads": 3, "head_dim": 16,  # noqa: E731
                                                           "qk_norm": True, "qk_norm_eps": r["eps"], "window": window})
         # the checkpoint's names of a layer's parts are data: layer 0 has names of its own, layer 1 none (the roles' names)
         layers = [LayerSpec("toy.layers.0", att(None), routed, {"input": norm, "post_mixer": norm}, position=pos,
                             names={"input": "ln1", "post_mixer": "ln2", "mixer": "attn", "feed_forward": "moe"}),
-                  LayerSpec("toy.layers.1", att(6), dense, {"input": norm, "post_mixer": norm}, position=pos)]
+                  LayerSpec("toy.layers.1", att(6), dense, {"input": norm, "post_mixer": norm}, position=pos_pairs)]
         return ModelSpec("ToyRoutedLM", H, V, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "name": "toy.embed.weight"}),
                          PartSpec("rmsnorm", {"size": H, "eps": r["eps"], "name": "toy.norm.weight"}),
                          PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": False, "name": "toy.head.weight"}),
@@ -416,15 +419,19 @@ def routed_toy_plain(w, tokens, eps, step):
     ang = pos * step * torch.arange(1, 5, dtype=torch.float32)[None, :]
     cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
 
-    def rotate(x):                                   # first 8 elements of every head, halves of 4 against each other
-        a, b, rest = x[..., :4], x[..., 4:8], x[..., 8:]
+    def rotate(x, pairs):                            # first 8 elements of every head
+        if pairs:                                    # neighbours 2 p, 2 p + 1 (layer 1)
+            a, b, rest = x[..., 0:8:2], x[..., 1:8:2], x[..., 8:]
+            return torch.cat((torch.stack((a * cos - b * sin, b * cos + a * sin), -1).flatten(-2), rest), -1)
+        a, b, rest = x[..., :4], x[..., 4:8], x[..., 8:]          # halves of 4 against each other (layer 0)
         return torch.cat((a * cos - b * sin, b * cos + a * sin, rest), -1)
 
     def attention(y, p, window):
+        pairs = window is not None
         q = P.rms_norm((y @ f[p + "q_proj.weight"].T).reshape(S, 6, 16), f[p + "q_norm.weight"], eps)
         k = P.rms_norm((y @ f[p + "k_proj.weight"].T).reshape(S, 3, 16), f[p + "k_norm.weight"], eps)
         v = (y @ f[p + "v_proj.weight"].T).reshape(S, 3, 16)
-        q, k = rotate(q), rotate(k)
+        q, k = rotate(q, pairs), rotate(k, pairs)
         k, v = k.repeat_interleave(2, 1), v.repeat_interleave(2, 1)
         s = torch.einsum("qhd,khd->hqk", q, k) * 16 ** -0.5
         i, j = torch.arange(S)[:, None], torch.arange(S)[None, :]
@@ -454,7 +461,8 @@ def routed_toy_plain(w, tokens, eps, step):
 
 def test_toy_architecture_with_routed_experts_and_another_rotary_encoding():
     """Registered, built and stepped without a change to the framework's files: a feed-forward with routing, a
-    rotary encoding of another kind with partial rotation, layers that differ in feed-forward and window."""
+    rotary encoding of another kind with partial rotation (in halves in one layer, in neighbouring pairs in the other),
+    layers that differ in feed-forward, window and position encoding."""
     from mini_sglang_b200.config import ARCHITECTURES
     from mini_sglang_b200.engine.step import ModelRunner, StepEntry
     from mini_sglang_b200.weights import RandomSource

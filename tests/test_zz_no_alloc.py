@@ -6,8 +6,8 @@ because cudaMalloc / cudaFree can stall the whole device.  For them the library 
 memory of the split-KV decode attention inside itself.  This test calls that entry point through
 its exported C symbol, exactly as such a caller would (raw pointers and a stream, nothing from
 torch's allocator inside the call), and checks it against the regular entry point fed with
-scratch from the caller -- twice in a row with different inputs, because the built-in scratch
-keeps whatever the previous call left there.  Collected last on purpose (file name), so a run
+scratch from the caller and against the attention formula written out in float32 -- twice in a row
+with different inputs, because the built-in scratch keeps whatever the previous call left there.  Collected last on purpose (file name), so a run
 that stops at the first failure has been through every other test before.
 """
 
@@ -65,6 +65,24 @@ def _regular(c, n_kv, P, max_split, scale):
     return out
 
 
+def _restated(c, n_kv, P, scale):
+    """The same attention written out in float32 with torch: every request's keys gathered from its pages, the new
+    token attending to all of them.  Shares nothing with either entry point."""
+    q, kc, vc = c["q"].float(), c["kc"].float(), c["vc"].float()
+    B, n_q, d = q.shape
+    group = n_q // n_kv
+    out = torch.empty_like(q)
+    for r in range(B):
+        L = int(c["kv_len"][r])
+        pages = c["bt"][r, : -(-L // P)].long()
+        k = kc[pages].permute(1, 0, 2, 3).reshape(n_kv, -1, d)[:, :L]          # [kv head, key, d]
+        v = vc[pages].permute(1, 0, 2, 3).reshape(n_kv, -1, d)[:, :L]
+        for h in range(n_q):
+            p = torch.softmax((k[h // group] @ q[r, h]) * scale, dim=0)
+            out[r, h] = p @ v[h // group]
+    return out
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_no_alloc_entry_point_matches_the_regular_one_twice_in_a_row(dtype):
     B, n_q, n_kv, d, P, max_split = 6, 32, 8, 128, 16, 4
@@ -86,6 +104,8 @@ def test_no_alloc_entry_point_matches_the_regular_one_twice_in_a_row(dtype):
         assert torch.cuda.memory_allocated() == before
         tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=2e-5)
         torch.testing.assert_close(out.float(), want.float(), **tol)
+        # and against the formula itself, so that a fault the two entry points had in common would show
+        torch.testing.assert_close(out.float(), _restated(c, n_kv, P, scale), **tol)
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():
