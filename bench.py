@@ -635,16 +635,17 @@ def main():
     torch.cuda.synchronize()
     done0 = sum(len(r.output) for r in reqs)
     t0 = time.perf_counter()
+    h2d_sum = 0
     for _ in range(K):
         eng.step()
+        h2d_sum += runner.last_h2d_bytes
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     done = sum(len(r.output) for r in reqs) - done0
     assert done == B * K, "a request finished inside the timed steps"
     while not eng.scheduler.idle:
         eng.step()
-    key = next(iter(runner._graphs)) if runner._graphs else None
-    h2d = 4 * max((g.layout.size for g in runner._graphs.values() if g.layout.B == runner._bucket(B)), default=0)
+    h2d = h2d_sum // max(K, 1)
     e2e = {"value": round(done / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B}
 
     points = {}

@@ -61,6 +61,7 @@ class KVGroup:
         self.n_pages = np.zeros(max_reqs + 1, dtype=np.int64)      # table entries in use (released ones included)
         self.first_live = np.zeros(max_reqs + 1, dtype=np.int64)   # entries below this were given back
         self.cache_ids: List[int] = []
+        self.dirty: set = set()        # slots whose table row changed since a device copy of the table was last brought up to date
 
 
 class CacheManager:
@@ -145,6 +146,7 @@ class CacheManager:
                 k = int(g.n_pages[slot])
                 g.table[slot, k:k + n] = g.pool.alloc(n)
                 g.n_pages[slot] = k + n
+                g.dirty.add(slot)
         self.reserved[slot] = total
 
     def adopt_prefix(self, slot: int, pages: Sequence[int]) -> None:
@@ -157,6 +159,7 @@ class CacheManager:
         n = len(pages)
         g.table[slot, :n] = pages
         g.n_pages[slot] = n
+        g.dirty.add(slot)
         self.borrowed[slot] = n
         self.length[slot] = self.reserved[slot] = n * self.page_size
 
@@ -164,12 +167,21 @@ class CacheManager:
         """After a prefix tree took (or already had) the request's leading pages."""
         g = self.groups[0]
         g.table[slot, :len(table)] = table
+        g.dirty.add(slot)
         self.borrowed[slot] = n_borrowed
 
     def slot_mapping(self, group: int, slot: int, start: int, n: int) -> np.ndarray:
         P = self.page_size
         pos = np.arange(start, start + n, dtype=np.int64)
         return (self.groups[group].table[slot, pos // P].astype(np.int64) * P + pos % P).astype(np.int32)
+
+    def take_dirty_rows(self, group: int) -> List[Tuple[int, np.ndarray]]:
+        """(slot, its table row) of every open request whose row changed since the last call: what a device copy of the
+        group's block tables has to be given to be up to date."""
+        g = self.groups[group]
+        out = [(slot, g.table[slot, :int(g.n_pages[slot])]) for slot in sorted(g.dirty) if g.n_pages[slot] > 0]
+        g.dirty.clear()
+        return out
 
     def block_table_row(self, group: int, slot: int) -> np.ndarray:
         g = self.groups[group]
@@ -191,6 +203,7 @@ class CacheManager:
                 g.pool.free(int(p) for p in g.table[slot, first:dead])
                 g.table[slot, first:dead] = 0
                 g.first_live[slot] = dead
+                g.dirty.add(slot)
 
     def owned_pages(self, slot: int, group: int = 0) -> List[int]:
         g = self.groups[group]
@@ -212,6 +225,7 @@ class CacheManager:
             g.table[slot, :hi] = 0
             g.n_pages[slot] = 0
             g.first_live[slot] = 0
+            g.dirty.discard(slot)
         self.length[slot] = self.reserved[slot] = self.borrowed[slot] = 0
         self._open[slot] = False
         self._free_slots.append(slot)

@@ -48,6 +48,66 @@ MSGL_API int msgl_resolve_ids(void* ids, const void* prev, int T_, int n_prev, c
     return msgl_check_launch();
 }
 
+// ---------------------------------------------------------------------------------------
+// Step metadata of a decode step, made on the device (the reference fills cu_seqlens and the page table on the device
+// inside its CUDA-graph hooks, mini_sglang/layers/attn/fa3_attn_backend.py:50-81,221-233).  The block tables of a cache
+// group are mirrored in device memory; the host sends, per step, what changed in them (whole rows of the requests that
+// got a page) and three numbers per request; the fields that the captured graph reads are written here.
+// ---------------------------------------------------------------------------------------
+// deltas: [n, (slot, count, offset) x n, page ids ...]: row `slot` of the mirror gets `count` page ids from deltas[offset..]
+__global__ void table_delta_kernel(const int* __restrict__ deltas, int* __restrict__ table, int row_stride) {
+    const int rec = blockIdx.x;
+    const int slot = deltas[1 + 3 * rec], count = min(deltas[2 + 3 * rec], row_stride), off = deltas[3 + 3 * rec];
+    for (int i = threadIdx.x; i < count; i += blockDim.x) table[(size_t)slot * row_stride + i] = deltas[off + i];
+}
+
+// One block per row r of a captured batch of b rows, the first B of them live: request slot[r] feeds token id[r] at position
+// pos[r].  Rows past B are padding: a request of one token on the dump page.  common != 0: the fields that all cache groups
+// share are written too.
+__global__ void decode_meta_kernel(const int* __restrict__ id, const int* __restrict__ slot, const int* __restrict__ pos,
+                                   const int* __restrict__ nsplit_in, int B, int b, const int* __restrict__ table, int row_stride,
+                                   int page_size, int mp, int common, int* __restrict__ input_ids, int* __restrict__ positions,
+                                   int* __restrict__ token_req, int* __restrict__ q_start, int* __restrict__ kv_len,
+                                   int* __restrict__ slots, int* __restrict__ out_loc, int* __restrict__ nsplit,
+                                   int* __restrict__ block_table) {
+    const int r = blockIdx.x;
+    const bool live = r < B;
+    const int sl = live ? slot[r] : 0, ps = live ? pos[r] : 0;
+    const int* row = table + (size_t)sl * row_stride;
+    if (threadIdx.x == 0) {
+        if (common) {
+            input_ids[r] = live ? id[r] : 0;
+            positions[r] = ps;
+            token_req[r] = r;
+            q_start[r] = r;
+            if (r == b - 1) q_start[b] = b;
+            kv_len[r] = ps + 1;
+            slots[r] = sl;
+        }
+        const int pi = ps / page_size;
+        out_loc[r] = (live && pi < row_stride) ? row[pi] * page_size + (ps - pi * page_size) : 0;
+        nsplit[r] = live ? nsplit_in[r] : 1;
+    }
+    for (int i = threadIdx.x; i < mp; i += blockDim.x) block_table[(size_t)r * mp + i] = (live && i < row_stride) ? row[i] : 0;
+}
+
+MSGL_API int msgl_table_delta(const int* deltas, int n_records, int* table, int row_stride, cudaStream_t stream) {
+    if (n_records <= 0) return MSGL_OK;
+    table_delta_kernel<<<n_records, 128, 0, stream>>>(deltas, table, row_stride);
+    return msgl_check_launch();
+}
+
+MSGL_API int msgl_decode_meta(const int* id, const int* slot, const int* pos, const int* nsplit_in, int B, int b, const int* table,
+                              int row_stride, int page_size, int mp, int common, int* input_ids, int* positions, int* token_req,
+                              int* q_start, int* kv_len, int* slots, int* out_loc, int* nsplit, int* block_table,
+                              cudaStream_t stream) {
+    if (b <= 0) return MSGL_OK;
+    if (B < 0 || B > b || page_size < 1 || mp < 1 || row_stride < 1) return MSGL_ERR_SIZE;
+    decode_meta_kernel<<<b, 128, 0, stream>>>(id, slot, pos, nsplit_in, B, b, table, row_stride, page_size, mp, common, input_ids,
+                                             positions, token_req, q_start, kv_len, slots, out_loc, nsplit, block_table);
+    return msgl_check_launch();
+}
+
 MSGL_API int msgl_embedding(const int* ids, const void* table, float* out, int T_, int H, int V,
                             int dtype, cudaStream_t stream) {
     if (T_ <= 0) return MSGL_OK;

@@ -19,6 +19,7 @@ every request brings exactly one token replay a CUDA graph captured for that bat
 from __future__ import annotations
 
 import dataclasses
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -91,6 +92,8 @@ class CacheStorage:
                 self.state[cid] = torch.zeros((mgr.max_reqs + 1, *need.shape), dtype=dt, device=device)
         if self.state:
             mgr.on_open.append(self._zero_slot)
+        # device copies of the groups' block tables, brought up to date by deltas before a decode graph is replayed
+        self.tables = [torch.zeros((mgr.max_reqs + 1, g.table.shape[1]), dtype=torch.int32, device=device) for g in mgr.groups]
 
     def _zero_slot(self, slot: int) -> None:
         for t in self.state.values():
@@ -235,6 +238,11 @@ class ModelRunner:
         self._graph_pool = None
         self.kernel_launches = 0
         self.last_step_used_graph = False
+        # decode steps through a graph: the step's fields are made on the device from three numbers a request and the
+        # device copy of the block tables (MSGL_DEVICE_META=0: the host writes them all and copies them)
+        self.device_meta = os.environ.get("MSGL_DEVICE_META", "1") != "0"
+        self._dev_compact = None
+        self.last_h2d_bytes = 0          # bytes of the last step's host-to-device copy of its fields
         self.last_plan: Dict[str, object] = {}       # the last step's kv splits per group and the decode graph it replayed
         self._group_geom = []
         for g in self.mgr.groups:
@@ -465,6 +473,7 @@ class ModelRunner:
             dev = self._dev_staging
             dev[:lay.size].copy_(host[:lay.size], non_blocking=True)
             self._mark(idx)
+            self.last_h2d_bytes = 4 * lay.size
             if prev_ids is not None:
                 ops.resolve_ids(dev[lay.input_ids: lay.input_ids + T], prev_ids)
             ctx = self._context(dev, lay, q_lens, kv_lens, [e.slot for e in entries], max_splits, uniform, nsplits,
@@ -521,15 +530,67 @@ class ModelRunner:
             self._graphs[key] = gr
         self.last_plan = {"graph_key": key, "nsplits": nsplits, "max_split": list(gr.max_split)}
         lay = gr.layout
-        host, idx = self._pinned_buffer(lay.size)
-        self._fill(host.numpy(), lay, entries, starts, list(range(b)), nsplits)
-        gr.dev.copy_(host[:lay.size], non_blocking=True)
-        self._mark(idx)
+        if self.device_meta:
+            self._meta_on_device(gr, entries, starts, nsplits, b)
+        else:
+            host, idx = self._pinned_buffer(lay.size)
+            self._fill(host.numpy(), lay, entries, starts, list(range(b)), nsplits)
+            gr.dev.copy_(host[:lay.size], non_blocking=True)
+            self._mark(idx)
+            self.last_h2d_bytes = 4 * lay.size
         if prev_ids is not None:
             ops.resolve_ids(gr.dev[lay.input_ids: lay.input_ids + B], prev_ids)
         gr.graph.replay()
         ops.LAUNCHES += gr.n_kernels
         return gr.logits[:B]
+
+    def _meta_on_device(self, gr: "_Graph", entries, starts, nsplits, b: int) -> None:
+        """The fields of a decode step that the captured graph reads, made on the device.  The host sends one small
+        buffer: token id, slot and position of every request, its kv splits per cache group, and per group the table
+        rows of the requests whose pages changed since the last such step (whole rows; a request gets a page every
+        page_size tokens)."""
+        lay, B, G = gr.layout, len(entries), len(self.mgr.groups)
+        rows = [self.mgr.take_dirty_rows(gi) for gi in range(G)]
+        n_delta = [1 + 3 * len(r) + sum(len(t) for _, t in r) for r in rows]
+        size = (3 + G) * B + sum(_align4(n) for n in n_delta)
+        host_t, idx = self._pinned_buffer(size)
+        host = host_t.numpy()
+        host[0:B] = [e.tokens[0] for e in entries]
+        host[B:2 * B] = [e.slot for e in entries]
+        host[2 * B:3 * B] = starts
+        off = 3 * B
+        ns_off = []
+        for gi in range(G):
+            host[off:off + B] = nsplits[gi]
+            ns_off.append(off)
+            off += B
+        d_off = []
+        for gi in range(G):
+            d_off.append(off)
+            recs = rows[gi]
+            host[off] = len(recs)
+            at = off + 1 + 3 * len(recs)
+            for k, (slot, table_row) in enumerate(recs):
+                host[off + 1 + 3 * k: off + 4 + 3 * k] = (slot, len(table_row), at - off)
+                host[at:at + len(table_row)] = table_row
+                at += len(table_row)
+            off += _align4(n_delta[gi])
+        if self._dev_compact is None or self._dev_compact.numel() < size:
+            self._dev_compact = torch.empty(max(size, 1 << 14), dtype=torch.int32, device=self.device)
+        dev = self._dev_compact
+        dev[:size].copy_(host_t[:size], non_blocking=True)
+        self._mark(idx)
+        self.last_h2d_bytes = 4 * size
+        g0 = gr.dev
+        for gi in range(G):
+            if rows[gi]:
+                ops.table_delta(dev[d_off[gi]: d_off[gi] + n_delta[gi]], len(rows[gi]), self.storage.tables[gi])
+            mp = lay.max_pages[gi]
+            ops.decode_meta(dev[0:B], dev[B:2 * B], dev[2 * B:3 * B], dev[ns_off[gi]:ns_off[gi] + B], B, b, self.storage.tables[gi],
+                            self.page_size, mp, gi == 0,
+                            input_ids=g0[lay.input_ids:], positions=g0[lay.positions:], token_req=g0[lay.token_req:],
+                            q_start=g0[lay.q_start:], kv_len=g0[lay.kv_len:], slots=g0[lay.slots:],
+                            out_loc=g0[lay.out_loc[gi]:], nsplit=g0[lay.nsplit[gi]:], block_table=g0[lay.table[gi]:])
 
     def _capture(self, b: int, mp: Tuple[int, ...], max_split: Sequence[int]) -> _Graph:
         gr = _Graph()

@@ -78,6 +78,8 @@ def _lib():
         lib = _build.common_library()
         lib.msgl_embedding.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.msgl_resolve_ids.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.msgl_table_delta.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p]
+        lib.msgl_decode_meta.argtypes = [c_void_p] * 4 + [c_int, c_int, c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 9 + [c_void_p]
         lib.msgl_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p,
                                      c_int, c_int, c_int, c_void_p]
         lib.msgl_qknorm_rope_kvwrite.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -138,6 +140,26 @@ def resolve_ids(ids: torch.Tensor, prev: torch.Tensor) -> None:
     _need_cuda(ids, prev)
     assert ids.dtype == torch.int32 and prev.dtype == torch.int32 and ids.is_contiguous() and prev.is_contiguous()
     _check(_lib().msgl_resolve_ids(_ptr(ids), _ptr(prev), ids.numel(), prev.numel(), _stream()), "resolve_ids")
+
+
+def table_delta(deltas: torch.Tensor, n_records: int, table: torch.Tensor) -> None:
+    """Rows of the device copy of a cache group's block tables, brought up to date: deltas = [n, (slot, count, offset) x n,
+    page ids ...] int32 on the device; table int32 [slots, pages per request]."""
+    _need_cuda(deltas, table)
+    assert deltas.dtype == torch.int32 and table.dtype == torch.int32 and table.is_contiguous()
+    _check(_lib().msgl_table_delta(_ptr(deltas), n_records, _ptr(table), table.shape[1], _stream()), "table_delta")
+
+
+def decode_meta(ids: torch.Tensor, slots_in: torch.Tensor, pos: torch.Tensor, nsplit_in: torch.Tensor, B: int, b: int,
+                table: torch.Tensor, page_size: int, mp: int, common: bool, *, input_ids, positions, token_req, q_start, kv_len,
+                slots, out_loc, nsplit, block_table) -> None:
+    """The step fields of a decode batch of B requests (captured size b) written on the device from (token id, slot,
+    position) per request and the device copy of the block tables; see csrc/elementwise.cu."""
+    _need_cuda(ids, slots_in, pos, nsplit_in, table, input_ids, block_table)
+    code = _lib().msgl_decode_meta(_ptr(ids), _ptr(slots_in), _ptr(pos), _ptr(nsplit_in), B, b, _ptr(table), table.shape[1], page_size,
+                                   mp, int(common), _ptr(input_ids), _ptr(positions), _ptr(token_req), _ptr(q_start), _ptr(kv_len),
+                                   _ptr(slots), _ptr(out_loc), _ptr(nsplit), _ptr(block_table), _stream())
+    _check(code, "decode_meta")
 
 
 def rmsnorm(weight: torch.Tensor, eps: float, *, x: Optional[torch.Tensor] = None,

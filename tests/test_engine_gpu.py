@@ -190,3 +190,61 @@ def test_trace_run_program(tmp_path):
         assert_rows_close(s0, ra[[0, 19]], dtype)
         assert_rows_close(s1, rb[[20]], dtype)
         assert_rows_close(s2, ra[[35, 36]], dtype)
+
+
+def test_step_fields_made_on_the_device_equal_the_hosts(monkeypatch):
+    """Decode steps through a CUDA graph get their fields (positions, lengths, cache slots, block-table rows, kv splits) from
+    a kernel that reads a device copy of the block tables, kept up to date by deltas.  Requests come, grow over page edges,
+    end and are replaced, with so few pages that they are used again; before every replay the graph's buffer must hold
+    exactly what the host's own filling of the same step gives."""
+    from mini_sglang_b200.engine.step import StepEntry
+    name = "B"
+    cfg = CONFIGS[name]
+    runner = make_runner(name, "bfloat16", num_pages=40, max_reqs=6, page_size=4)
+    assert runner.device_meta and runner.use_cuda_graph
+    checked = []
+    inner = runner._meta_on_device
+
+    def checking(gr, entries, starts, nsplits, b):
+        inner(gr, entries, starts, nsplits, b)
+        lay = gr.layout
+        want = np.zeros(lay.size, dtype=np.int32)
+        runner._fill(want, lay, entries, starts, list(range(b)), nsplits, pad_to=b)
+        got = gr.dev.cpu().numpy()
+        B = len(entries)
+        for field, off, n in [("input_ids", lay.input_ids, b), ("positions", lay.positions, b), ("token_req", lay.token_req, b),
+                              ("q_start", lay.q_start, b + 1), ("kv_len", lay.kv_len, b), ("slots", lay.slots, b), ("want", lay.want, b)]:
+            assert (got[off:off + n] == want[off:off + n]).all(), (field, got[off:off + n], want[off:off + n])
+        for gi, g in enumerate(runner.mgr.groups):
+            mp = lay.max_pages[gi]
+            assert (got[lay.out_loc[gi]: lay.out_loc[gi] + b] == want[lay.out_loc[gi]: lay.out_loc[gi] + b]).all()
+            assert (got[lay.nsplit[gi]: lay.nsplit[gi] + b] == want[lay.nsplit[gi]: lay.nsplit[gi] + b]).all()
+            tg, tw = got[lay.table[gi]: lay.table[gi] + b * mp].reshape(b, mp), want[lay.table[gi]: lay.table[gi] + b * mp].reshape(b, mp)
+            for r, e in enumerate(entries):                 # the pages a request holds; what lies beyond them is never read
+                n = int(g.n_pages[e.slot])
+                assert (tg[r, :n] == tw[r, :n]).all(), (r, tg[r, :n], tw[r, :n])
+            assert (tg[B:] == 0).all()
+        checked.append(b)
+
+    monkeypatch.setattr(runner, "_meta_on_device", checking)
+    rnd = np.random.RandomState(0)
+    live = {}
+    for it in range(60):
+        if len(live) < 5 and (not live or rnd.rand() < 0.4):
+            s = runner.open()
+            n = int(rnd.randint(1, 14))
+            runner.step([StepEntry(s, random_tokens(n, cfg["vocab_size"], 3000 + it), [])])
+            live[s] = n
+        if live and rnd.rand() < 0.15:
+            s = list(live)[int(rnd.randint(len(live)))]
+            runner.close(s)
+            del live[s]
+        some = [s for s in live if rnd.rand() < 0.8 and live[s] < 30]
+        if some:
+            out = runner.step([StepEntry(s, [int(rnd.randint(cfg["vocab_size"]))], [0]) for s in some])
+            assert out.shape[0] == len(some) and torch.isfinite(out).all()
+            for s in some:
+                live[s] += 1
+    assert len(checked) > 25 and len(set(checked)) >= 3
+    for s in live:
+        runner.close(s)
