@@ -46,6 +46,7 @@ def test_manager_random_orders_no_page_lost_or_held_twice(page_size):
                        max_step_tokens=40)
     assert len(mgr.groups) == 2 and mgr.groups[0].cache_ids == [0, 1] and mgr.groups[1].window == 24
     live = {}
+    mirror = [np.zeros_like(g.table) for g in mgr.groups]
     for it in range(3000):
         op = rnd.random()
         if op < 0.25 and mgr.free_slots:
@@ -78,6 +79,15 @@ def test_manager_random_orders_no_page_lost_or_held_twice(page_size):
                 if n_tok:
                     pages = g.table[slot, lo // page_size: -(-n_tok // page_size)]
                     assert (pages > 0).all()
+        # a copy of the block tables that only ever sees the rows reported as changed stays equal to them
+        if it % 7 == 0:
+            for gi, g in enumerate(mgr.groups):
+                for slot, row in mgr.take_dirty_rows(gi):
+                    mirror[gi][slot, :len(row)] = row
+                assert not g.dirty
+                for slot in live:
+                    n = int(g.n_pages[slot])
+                    assert (mirror[gi][slot, :n] == g.table[slot, :n]).all()
     for slot in list(live):
         mgr.close(slot)
     mgr.check_idle()
