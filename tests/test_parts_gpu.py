@@ -492,3 +492,57 @@ def test_toy_architecture_with_routed_experts_and_another_rotary_encoding():
         torch.testing.assert_close(torch.cat(got), ref, **TOL["float32"])
     finally:
         ARCHITECTURES.pop("ToyRoutedLM", None)
+
+
+def test_scheduler_runs_a_toy_model_with_two_cache_groups_under_a_small_pool():
+    """The scheduler above the real step function of a model it knows nothing about: routed experts, a layer that keeps all
+    keys and a layer that keeps a window of 6 (two cache groups with pools of their own), prompts fed 8 tokens a step, and so
+    few pages that requests have to wait for one another.  Greedy tokens equal those of the toy's plain restatement; nothing is
+    left in either pool."""
+    from mini_sglang_b200.config import ARCHITECTURES
+    from mini_sglang_b200.engine.scheduler import Req, Scheduler
+    from mini_sglang_b200.engine.step import ModelRunner
+    from mini_sglang_b200.sampling import Sampler, SamplingParams
+    from mini_sglang_b200.weights import RandomSource
+
+    build, Cfg = _register_routed_toy()
+    try:
+        spec = build(Cfg({"width": 48, "vocab": 83, "ffn": 40, "eps": 1e-5, "step": 0.07}))
+        holder = {}
+
+        def factory(expected, dt, dev):
+            src = RandomSource(expected, 23, dt, dev, std=0.15)
+            holder["w"] = {n: src.draw(n).cpu() for n in expected if src.has(n)}
+            return src
+
+        runner = ModelRunner(spec, factory, dtype="float32", page_size=4, num_pages=22, max_reqs=4, max_step_tokens=32)
+        assert len(runner.mgr.groups) == 2
+        sch = Scheduler(runner, Sampler(0, runner.device), max_num_reqs=4, max_step_tokens=32, chunk_size=8, policy="lpm",
+                        retract_decode_steps=2)
+        assert sch.tree is None and sch.policy == "fcfs"      # no prefix sharing for a model with a windowed group
+        g = torch.Generator().manual_seed(9)
+        prompts = [torch.randint(0, 83, (n,), generator=g).tolist() for n in (19, 7, 26, 11, 15)]
+        n_new = 9
+        reqs = [Req(f"r{i}", p, SamplingParams(max_new_tokens=n_new, ignore_eos=True)) for i, p in enumerate(prompts)]
+        for r in reqs:
+            sch.add_request(r)
+        most_running = 0
+        for _ in range(2000):
+            if sch.idle:
+                break
+            sch.step()
+            most_running = max(most_running, len(sch.running))
+        assert sch.idle and most_running >= 2
+        sch.check_idle_invariants()
+        assert all(gr.pool.in_use == 0 for gr in runner.mgr.groups)
+        for r, p in zip(reqs, prompts):
+            assert r.finish_reason.type == "length" and len(r.output) == n_new
+            toks = list(p)
+            for t in r.output:                                 # greedy under the plain restatement, given the same history
+                ref, _ = routed_toy_plain(holder["w"], toks, 1e-5, 0.07)
+                top2 = ref[-1].topk(2).values
+                if top2[0] - top2[1] > 1e-4:
+                    assert int(ref[-1].argmax()) == t, (r.rid, len(toks) - len(p))
+                toks.append(t)
+    finally:
+        ARCHITECTURES.pop("ToyRoutedLM", None)
