@@ -11,29 +11,30 @@
 // its next piece of work (they do not depend on anything computed in the step), so the weight stream goes on
 // across the barrier.
 //
-// Phases of a layer (5 barriers):
-//   A  qkv = norm_in(res) . Wqkv^T (+ b)        the norm is folded into the product: the block stages
-//                                               bf16(res * w_norm) in shared memory once, sums res^2 on the way,
-//                                               and scales its outputs by rsqrt(mean + eps) at the end
+// Phases of a layer (5 barriers); in every product a block owns an equal share of the weight rows:
+//   A  qkv = norm_in(res) . Wqkv^T (+ b)        x = bf16(res * w_norm) was written by the phase that produced res,
+//                                               with partial sums of res^2; the outputs are scaled by
+//                                               rsqrt(mean + eps) at the end, which is the normed product
 //   B  attention of every (request, kv head, kv split): q heads normed and rotated on the fly; the piece that
 //      holds a request's last keys norms and rotates the new key, writes key and value into the paged cache and
 //      takes them into its own sums from shared memory; the piece that finishes a (request, kv head) last (a
 //      ticket) merges the splits, in split order
-//   C  res += attn . Wo^T                       the residual sum is the product's epilogue (float32, in place)
-//   D  act = silu(g) * u, [g; u] = norm_post(res) . Wgu^T     norm folded in as in A
-//   E  res += act . Wdown^T
+//   C  res += attn . Wo^T                       the residual sum is the product's epilogue (float32, in place), and
+//                                               with it bf16(res * w_post) and the partial sums of res^2 for D
+//   D  act = silu(g) * u, [g; u] = norm_post(res) . Wgu^T     scaled as in A
+//   E  res += act . Wdown^T                     with bf16(res * w) for the norm that comes next (next layer's, or the final one)
 // then the head: logits = norm_final(res) . Wlm^T in float32.
 //
-// Everything a block reads that another block wrote during the step (res, qkv, attn, act, partial sums) is read
-// past the L1 cache (ld.global.cg / cp.async.cg): L1 is not coherent between SMs and the kernel does not end
-// between a write and its reads.  Weights, tables and the cache contents of earlier steps never change while the
+// What a block reads that another block wrote during the step is read past the L1 cache (ld.global.cg /
+// cp.async.cg) or after a grid barrier, whose acquire makes the SM drop what its L1 held: L1 is not coherent between
+// SMs and the kernel does not end between a write and its reads.  Weights, tables and the cache contents of earlier steps never change while the
 // kernel runs.
 //
 // Every wait has a limit (polls and time); a block that gives up sets a status word, which ends the waits of all
 // others, and every block returns.  Nothing is left to free.
 //
 // Sizes: bfloat16; up to 8 requests; head size MSGL_HEAD_DIM (a multiple of 32); up to 16 query heads per kv head;
-// hidden and intermediate sizes multiples of 32 / 8; all keys kept (no window).  The entry point refuses anything
+// hidden and intermediate sizes multiples of 32; all keys kept (no window).  The entry point refuses anything
 // else (MSGL_ERR_SIZE) and the caller takes the kernel-by-kernel path.
 #include "common.cuh"
 #include <math.h>
@@ -101,6 +102,8 @@ struct DsStep {
     float eps_final;
     const void* lm_head;                     // [V, H]
     float* res;                              // [M, H]       scratch from here on
+    void* xn;                                // [M, H] bf16(res * weight of the next norm)
+    float* ssq;                              // [blocks, 8] partial sums of res^2 per token
     void* qkv;                               // [M, (n_q + 2 n_kv) d]
     void* attn;                              // [M, n_q d]
     void* act;                               // [M, I]
@@ -244,45 +247,55 @@ namespace ds {
 // ---------------------------------------------------------------------------------------
 // matrix products of the step: out[M, N] = x[M, K] . W[N, K]^T for M <= 8, bound by reading W once
 // ---------------------------------------------------------------------------------------
-// Work is cut into units of 16 weight rows (8 gate rows and their 8 up rows with SwiGLU); unit u belongs to block
-// u % blocks.  Inside a block the warps take the 32-element chunks of K round-robin and every lane copies 16 bytes
-// of two weight rows per chunk with cp.async into a slot of its own in a shared-memory ring, PF chunks ahead, straight
-// into the register layout of mma.sync's A operand (the k index inside a chunk is permuted the same way for W and x).
-// The ring runs on across the units of a block, so while one unit's sums are added up the next unit's weights are
-// already on their way; and it is started BEFORE the grid barrier that guards the phase's input.
+// Every block owns an equal share of W's rows (N / blocks of them, give or take one), so the blocks of a phase finish
+// together and the barrier behind it is short.  A block walks its rows in tiles of 16 (8 gate rows and their 8 up rows
+// with SwiGLU; the last tile may be short: rows past the block's share are not fetched).  The warps take the 32-element
+// chunks of K round-robin and every lane copies 16 bytes of two weight rows per chunk with cp.async into a slot of its
+// own in a shared-memory ring, PF chunks ahead, straight into the register layout of mma.sync's A operand (the k index
+// inside a chunk is permuted the same way for W and x).  The ring runs on across the tiles, and it is started BEFORE the
+// grid barrier that guards the phase's input.
 //
-// x comes either as bfloat16 rows from global memory, chunk by chunk through the same ring (XSRC 0), or from the
-// float32 residual stream through a norm (XSRC 1): bf16(res * w_norm) is staged in shared memory once per block, the
-// rows' sums of squares are taken on the way, and the outputs are scaled by rsqrt(mean(res^2) + eps) at the end,
-// which is the same product as with the normed x because the scale is one number per row.
+// x is bfloat16 [M, K] in global memory, either copied whole into shared memory once per block (XSRC 1; K * 16 bytes
+// whatever M) or streamed chunk by chunk through the ring (XSRC 0, for the long K of the down product).
+//
+// A norm in front of a product is folded in like this: the phase that produces the residual stream (EPI 2) also writes
+// xn = bf16(res * w_next), the un-scaled input of the next product, for the columns it owns, and the sum of res^2 over
+// those columns per token (one partial per block, added in block order by the reader).  The product that follows
+// multiplies its sums by rsqrt(mean(res^2) + eps): the scale is one number per row, so this is the normed product.
 struct GemmJob {
     const bf16* W;
-    int n_units, K, I, M;
-    const bf16* X;               // XSRC 0
+    int n_rows;                  // output columns (SwiGLU: gate/up pairs = I)
+    int K, I, M;
+    const bf16* X;               // [M, ldx] bfloat16
     long long ldx;
-    const float* res;            // XSRC 1: [M, K] float32
-    const void* nw;
-    int nw_f32;
+    const float* ssq;            // not null: [producer blocks][8] partial sums of squares of x's float32 source
+    int n_ssq;
     float eps;
     const bf16* bias;
     void* out;
     long long ldo;
+    // EPI 2: what the next product wants of the stream
+    const void* next_w;          // its norm's weight [H]
+    int next_w_f32;
+    bf16* xn;                    // [M, ldo] bf16(res * next_w)
+    float* ssq_out;              // [blocks][8]
 };
 
 constexpr int RING2_BYTES = WARPS * PF * 2 * 512;
 constexpr int RING3_BYTES = WARPS * PF * 3 * 512;
 constexpr int RED_FLOATS = WARPS * 16 * 9;
-constexpr int RED_BYTES = (RED_FLOATS + WARPS * 8 + 8) * 4;
+constexpr int RED_BYTES = (RED_FLOATS + 128 + 8) * 4;
 
-// MODE 0: plain, 1: SwiGLU.  EPI 0: bfloat16 out, 1: float32 out, 2: added into float32 out (the residual stream).
+// MODE 0: plain, 1: SwiGLU.  XSRC 1: x staged whole in shared memory, 0: streamed.  EPI 0: bfloat16 out, 1: float32
+// out, 2: added into the float32 residual stream, with xn and the partial sums of squares for the next product.
 template <int MODE, int XSRC, int EPI>
 __device__ __forceinline__ bool gemm_phase(const GemmJob& j, unsigned char* sm, int arena, GridBar& bar) {
     constexpr int SLOTS = XSRC ? 2 : 3;
     uint4* ring = reinterpret_cast<uint4*>(sm);
     uint4* xs = reinterpret_cast<uint4*>(sm + RING2_BYTES);
     float* red = reinterpret_cast<float*>(sm + arena - RED_BYTES);
-    float* ssq = red + RED_FLOATS;
-    float* rs = ssq + WARPS * 8;
+    float* ssq_red = red + RED_FLOATS;         // [128]
+    float* rs = ssq_red + 128;                 // [8]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     uint4* my = ring + (size_t)warp * PF * SLOTS * 32 + lane;
@@ -290,28 +303,30 @@ __device__ __forceinline__ bool gemm_phase(const GemmJob& j, unsigned char* sm, 
     const int n_chunks = K >> 5;
     const int n_my = (n_chunks > warp) ? (n_chunks - warp + WARPS - 1) / WARPS : 0;
     const int bid = blockIdx.x, nblk = gridDim.x;
-    const int my_units = (j.n_units > bid) ? (j.n_units - bid + nblk - 1) / nblk : 0;
-    const int total = my_units * n_my;
+    const int r0 = (int)((long long)bid * j.n_rows / nblk), r1 = (int)((long long)(bid + 1) * j.n_rows / nblk);
+    constexpr int TR = MODE == 1 ? 8 : 16;     // output columns per tile
+    const int n_tiles = (r1 - r0 + TR - 1) / TR;
+    const int total = n_tiles * n_my;
 
-    // prefetch cursor: flat item ordinal, unit ordinal, chunk ordinal, weight rows of that unit
+    // prefetch cursor: flat item ordinal, tile ordinal, chunk ordinal, weight rows of that tile
     int f_pf = 0, pf_u = 0, pf_i = 0;
     const bf16 *pw_lo = j.W, *pw_hi = j.W;
-    auto set_unit = [&](int uo) {
-        const size_t unit = (size_t)bid + (size_t)uo * nblk;
+    bool v_lo = false, v_hi = false;
+    auto set_tile = [&](int uo) {
+        const int base = r0 + uo * TR;
         size_t row_lo, row_hi;
-        if (MODE == 1) { row_lo = unit * 8 + g; row_hi = (size_t)j.I + row_lo; }
-        else { row_lo = unit * 16 + g; row_hi = row_lo + 8; }
-        pw_lo = j.W + row_lo * K + 8 * t;
-        pw_hi = j.W + row_hi * K + 8 * t;
+        if (MODE == 1) { row_lo = (size_t)base + g; row_hi = (size_t)j.I + row_lo; v_lo = v_hi = base + g < r1; }
+        else { row_lo = (size_t)base + g; row_hi = row_lo + 8; v_lo = base + g < r1; v_hi = base + g + 8 < r1; }
+        pw_lo = j.W + (v_lo ? row_lo : 0) * K + 8 * t;
+        pw_hi = j.W + (v_hi ? row_hi : 0) * K + 8 * t;
     };
-    if (my_units > 0) set_unit(0);
-    const bf16* xr = j.X;
-    if (XSRC == 0) xr = j.X + (size_t)(g < j.M ? g : 0) * j.ldx + 8 * t;
+    if (n_tiles > 0) set_tile(0);
+    const bf16* xr = j.X + (size_t)(g < j.M ? g : 0) * j.ldx + 8 * t;
     auto fetch_w = [&]() {
         uint4* st = my + (size_t)(f_pf % PF) * SLOTS * 32;
         const size_t k0 = (size_t)(warp + pf_i * WARPS) << 5;
-        cp_async16(st, pw_lo + k0);
-        cp_async16(st + 32, pw_hi + k0);
+        cp_async16_if(st, pw_lo + k0, v_lo);
+        cp_async16_if(st + 32, pw_hi + k0, v_hi);
     };
     auto fetch_x = [&](int f, int i) {
         uint4* st = my + (size_t)(f % PF) * SLOTS * 32;
@@ -323,7 +338,7 @@ __device__ __forceinline__ bool gemm_phase(const GemmJob& j, unsigned char* sm, 
         if (++pf_i == n_my) {
             pf_i = 0;
             ++pf_u;
-            if (pf_u < my_units) set_unit(pf_u);
+            if (pf_u < n_tiles) set_tile(pf_u);
         }
     };
     // the first weights: nothing computed in this step reaches them, so they are asked for before the barrier
@@ -334,76 +349,40 @@ __device__ __forceinline__ bool gemm_phase(const GemmJob& j, unsigned char* sm, 
     if (!grid_sync(bar)) return false;
 
     if (XSRC == 1) {
-        // stage bf16(res * w) for the chunks this warp will read, and the rows' sums of squares; the loads of two
-        // chunks are issued before the first is used
-        float ss = 0.f;
-        const float* rrow = j.res + (size_t)(g < j.M ? g : 0) * K;
-        const bool live = g < j.M;
-        for (int i0 = 0; i0 < n_my; i0 += 2) {
-            float4 a[2], b[2];
-            uint4 wraw[2][2];
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const int k = ((warp + (i0 + q) * WARPS) << 5) + 8 * t;
-                if (i0 + q < n_my && live) {
-                    a[q] = ldcg4(rrow + k);
-                    b[q] = ldcg4(rrow + k + 4);
-                    if (j.nw_f32) {
-                        wraw[q][0] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(j.nw) + k));
-                        wraw[q][1] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(j.nw) + k + 4));
-                    } else {
-                        wraw[q][0] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(j.nw) + k));
-                    }
-                }
-            }
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                if (i0 + q >= n_my) break;
-                const int c = warp + (i0 + q) * WARPS;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (live) {
-                    float w[8];
-                    if (j.nw_f32) {
-                        const float* f0 = reinterpret_cast<const float*>(&wraw[q][0]);
-                        const float* f1 = reinterpret_cast<const float*>(&wraw[q][1]);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) { w[e] = f0[e]; w[4 + e] = f1[e]; }
-                    } else {
-                        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wraw[q][0]);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) { const float2 f2 = __bfloat1622float2(wp[e]); w[2 * e] = f2.x; w[2 * e + 1] = f2.y; }
-                    }
-                    const float4 av = a[q], bv = b[q];
-                    ss += av.x * av.x + av.y * av.y + av.z * av.z + av.w * av.w + bv.x * bv.x + bv.y * bv.y + bv.z * bv.z + bv.w * bv.w;
-                    v.x = pack_bf16(av.x * w[0], av.y * w[1]);
-                    v.y = pack_bf16(av.z * w[2], av.w * w[3]);
-                    v.z = pack_bf16(bv.x * w[4], bv.y * w[5]);
-                    v.w = pack_bf16(bv.z * w[6], bv.w * w[7]);
-                }
-                xs[(size_t)c * 32 + lane] = v;
-            }
+        // x whole into shared memory, every warp the chunks it will read itself; all copies in flight at once
+        for (int i = 0; i < n_my; ++i) {
+            const int c = warp + i * WARPS;
+            cp_async16_if(xs + (size_t)c * 32 + lane, xr + ((size_t)c << 5), g < j.M);
         }
-        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-        if (t == 0) ssq[warp * 8 + g] = ss;
-        __syncthreads();
-        if (tid < 8) {
-            float s = 0.f;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) s += ssq[w * 8 + tid];
-            rs[tid] = rsqrtf(s / (float)K + j.eps);
-        }
-        __syncthreads();
     }
-    // x of the chunks whose weights are already on their way; one group per item, as in the loop
+    if (j.ssq != nullptr) {
+        // the rows' scales from the producers' partial sums, added in block order: warp m takes token m
+        if (warp < 8) {
+            float s = 0.f;
+            for (int b0 = 0; b0 < j.n_ssq; b0 += 32) {
+                const int b = b0 + lane;
+                float v = (b < j.n_ssq && warp < j.M) ? __ldcg(j.ssq + (size_t)b * 8 + warp) : 0.f;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {            // inclusive order-preserving sum: lanes add their left neighbours
+                    const float u = __shfl_up_sync(0xffffffffu, v, o);
+                    if (lane >= o) v += u;
+                }
+                s += __shfl_sync(0xffffffffu, v, 31);
+            }
+            if (lane == 0) rs[warp] = rsqrtf(s / (float)K + j.eps);
+        }
+    }
+    // x of the chunks whose weights are already on their way; one group per item, as in the loop (the first group also
+    // holds the early weight copies and the staged x)
 #pragma unroll
     for (int n = 0; n < PF - 1; ++n) {
         if (XSRC == 0 && n < pre) fetch_x(n, n % (n_my > 0 ? n_my : 1));
         cp_commit();
     }
 
+    float ss_acc = 0.f;                        // EPI 2: this thread's share of the sums of squares of the new stream
     int f = 0;
-    for (int uo = 0; uo < my_units; ++uo) {
+    for (int uo = 0; uo < n_tiles; ++uo) {
         float c[4] = {0.f, 0.f, 0.f, 0.f};
         for (int i = 0; i < n_my; ++i, ++f) {
             if (f_pf < total) {
@@ -425,59 +404,87 @@ __device__ __forceinline__ bool gemm_phase(const GemmJob& j, unsigned char* sm, 
         red[(warp * 16 + g + 8) * 9 + 2 * t] = c[2];
         red[(warp * 16 + g + 8) * 9 + 2 * t + 1] = c[3];
         __syncthreads();
-        const size_t unit = (size_t)bid + (size_t)uo * nblk;
+        const int base = r0 + uo * TR;
         if (MODE == 1) {
             if (tid < 64) {
                 const int r = tid >> 3, tok = tid & 7;
-                if (tok < j.M) {
+                if (tok < j.M && base + r < r1) {
                     float gate = 0.f, up = 0.f;
 #pragma unroll
                     for (int w = 0; w < WARPS; ++w) { gate += red[(w * 16 + r) * 9 + tok]; up += red[(w * 16 + r + 8) * 9 + tok]; }
-                    if (XSRC == 1) { gate *= rs[tok]; up *= rs[tok]; }
+                    if (j.ssq != nullptr) { gate *= rs[tok]; up *= rs[tok]; }
                     const float y = gate / (1.f + expf(-gate)) * up;
-                    reinterpret_cast<bf16*>(j.out)[(size_t)tok * j.ldo + unit * 8 + r] = __float2bfloat16_rn(y);
+                    reinterpret_cast<bf16*>(j.out)[(size_t)tok * j.ldo + base + r] = __float2bfloat16_rn(y);
                 }
             }
         } else {
             if (tid < 128) {
                 const int r = tid >> 3, tok = tid & 7;
-                if (tok < j.M) {
+                if (tok < j.M && base + r < r1) {
                     float acc = 0.f;
 #pragma unroll
                     for (int w = 0; w < WARPS; ++w) acc += red[(w * 16 + r) * 9 + tok];
-                    if (XSRC == 1) acc *= rs[tok];
-                    const size_t col = unit * 16 + r;
+                    if (j.ssq != nullptr) acc *= rs[tok];
+                    const size_t col = (size_t)base + r;
                     if (j.bias) acc += __bfloat162float(j.bias[col]);
                     const size_t o = (size_t)tok * j.ldo + col;
                     if (EPI == 0) reinterpret_cast<bf16*>(j.out)[o] = __float2bfloat16_rn(acc);
                     else if (EPI == 1) reinterpret_cast<float*>(j.out)[o] = acc;
-                    else { float* rp = reinterpret_cast<float*>(j.out) + o; *rp = __ldcg(rp) + acc; }
+                    else {
+                        float* rp = reinterpret_cast<float*>(j.out) + o;
+                        const float v = __ldcg(rp) + acc;
+                        *rp = v;
+                        j.xn[o] = __float2bfloat16_rn(v * ld_w(j.next_w, (int)col, j.next_w_f32));
+                        ss_acc += v * v;
+                    }
                 }
             }
         }
         __syncthreads();
     }
     cp_wait<0>();
+    if (EPI == 2) {
+        // per token: the 16 threads that hold its columns (tid = 8 r + tok), added in order of r
+        if (tid < 128) ssq_red[tid] = ss_acc;
+        __syncthreads();
+        if (tid < 8) {
+            float s = 0.f;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) s += ssq_red[8 * r + tid];
+            j.ssq_out[(size_t)bid * 8 + tid] = s;
+        }
+    }
     return true;
 }
 
-// res[m, :] = float(E[ids[m], :]): the float32 residual stream starts here
-__device__ __forceinline__ void embed_phase(const DsStep& p) {
-    const int H8 = p.H >> 3;
-    const int total = p.M * H8;
+// res[m, :] = float(E[ids[m], :]): the float32 residual stream starts here, with what the first product wants of it
+// (xn and the partial sums of squares, as after an EPI 2 product); every block takes an equal share of the columns.
+__device__ __forceinline__ void embed_phase(const DsStep& p, const void* next_w, int next_w_f32, unsigned char* sm) {
+    float* ssq_red = reinterpret_cast<float*>(sm);          // [THREADS]
+    const int bid = blockIdx.x, nblk = gridDim.x, tid = threadIdx.x;
+    const int c0 = (int)((long long)bid * p.H / nblk), c1 = (int)((long long)(bid + 1) * p.H / nblk);
     const bf16* E = reinterpret_cast<const bf16*>(p.embed);
-    for (int idx = blockIdx.x * THREADS + threadIdx.x; idx < total; idx += gridDim.x * THREADS) {
-        const int m = idx / H8, c = idx - m * H8;
-        int id = p.ids[m];
+    bf16* xn = reinterpret_cast<bf16*>(p.xn);
+    const int tok = tid & 7, lanes = THREADS >> 3;          // thread = (column lane, token)
+    float ss = 0.f;
+    if (tok < p.M) {
+        int id = p.ids[tok];
         id = id < 0 ? 0 : (id >= p.V ? p.V - 1 : id);
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(E + (size_t)id * p.H + c * 8));
-        const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&v);
-        const float2 f0 = __bfloat1622float2(vp[0]), f1 = __bfloat1622float2(vp[1]);
-        const float2 f2 = __bfloat1622float2(vp[2]), f3 = __bfloat1622float2(vp[3]);
-        float4* dst = reinterpret_cast<float4*>(p.res + (size_t)m * p.H + c * 8);
-        dst[0] = make_float4(f0.x, f0.y, f1.x, f1.y);
-        dst[1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+        for (int c = c0 + (tid >> 3); c < c1; c += lanes) {
+            const float v = __bfloat162float(E[(size_t)id * p.H + c]);
+            p.res[(size_t)tok * p.H + c] = v;
+            xn[(size_t)tok * p.H + c] = __float2bfloat16_rn(v * ld_w(next_w, c, next_w_f32));
+            ss += v * v;
+        }
     }
+    ssq_red[tid] = ss;
+    __syncthreads();
+    if (tid < 8) {
+        float s = 0.f;
+        for (int l = 0; l < lanes; ++l) s += ssq_red[8 * l + tid];
+        p.ssq[(size_t)bid * 8 + tid] = s;
+    }
+    __syncthreads();
 }
 
 }  // namespace ds
@@ -882,38 +889,48 @@ __global__ void __launch_bounds__(ds::THREADS, 1) decode_step_kernel(const __gri
     using namespace ds;
     extern __shared__ __align__(16) unsigned char ds_smem[];
     GridBar bar{p.bar, p.status, 0u, gridDim.x, 0ull};
-    embed_phase(p);
+    const int nblk = gridDim.x;
     const int qkv_n = (p.n_q + 2 * p.n_kv) * D;
+    {
+        const bool none = p.n_layers == 0;
+        embed_phase(p, none ? p.final_norm : p.layers[0].norm_in, none ? p.final_f32 : p.layers[0].norm_f32, ds_smem);
+    }
     GemmJob j;
     j.M = p.M;
+    j.n_ssq = nblk;
+    j.xn = reinterpret_cast<bf16*>(p.xn);
+    j.ssq_out = p.ssq;
     for (int l = 0; l < p.n_layers; ++l) {
         const DsLayer& L = p.layers[l];
         // A: qkv = norm_in(res) . Wqkv^T (+ b)
-        j.W = reinterpret_cast<const bf16*>(L.w_qkv); j.n_units = qkv_n / 16; j.K = p.H; j.I = 0;
-        j.X = nullptr; j.ldx = 0; j.res = p.res; j.nw = L.norm_in; j.nw_f32 = L.norm_f32; j.eps = L.eps_in;
+        j.W = reinterpret_cast<const bf16*>(L.w_qkv); j.n_rows = qkv_n; j.K = p.H; j.I = 0;
+        j.X = reinterpret_cast<const bf16*>(p.xn); j.ldx = p.H; j.ssq = p.ssq; j.eps = L.eps_in;
         j.bias = reinterpret_cast<const bf16*>(L.b_qkv); j.out = p.qkv; j.ldo = qkv_n;
         { DS_PROF_BEGIN(0); if (!gemm_phase<0, 1, 0>(j, ds_smem, arena, bar)) return; DS_PROF_END(); }
         // B: attention
         { DS_PROF_BEGIN(1); if (!attn_phase(p, L, ds_smem, bar)) return; DS_PROF_END(); }
-        // C: res += attn . Wo^T
-        j.W = reinterpret_cast<const bf16*>(L.w_o); j.n_units = p.H / 16; j.K = p.n_q * D;
-        j.X = reinterpret_cast<const bf16*>(p.attn); j.ldx = (long long)p.n_q * D; j.res = nullptr; j.nw = nullptr;
-        j.bias = nullptr; j.out = p.res; j.ldo = p.H;
-        { DS_PROF_BEGIN(2); if (!gemm_phase<0, 0, 2>(j, ds_smem, arena, bar)) return; DS_PROF_END(); }
+        // C: res += attn . Wo^T; xn = bf16(res * w_post)
+        j.W = reinterpret_cast<const bf16*>(L.w_o); j.n_rows = p.H; j.K = p.n_q * D;
+        j.X = reinterpret_cast<const bf16*>(p.attn); j.ldx = (long long)p.n_q * D; j.ssq = nullptr;
+        j.bias = nullptr; j.out = p.res; j.ldo = p.H; j.next_w = L.norm_post; j.next_w_f32 = L.norm_f32;
+        { DS_PROF_BEGIN(2); if (!gemm_phase<0, 1, 2>(j, ds_smem, arena, bar)) return; DS_PROF_END(); }
         // D: act = silu(g) * u, [g; u] = norm_post(res) . Wgu^T
-        j.W = reinterpret_cast<const bf16*>(L.w_gu); j.n_units = p.I / 8; j.K = p.H; j.I = p.I;
-        j.X = nullptr; j.ldx = 0; j.res = p.res; j.nw = L.norm_post; j.nw_f32 = L.norm_f32; j.eps = L.eps_post;
+        j.W = reinterpret_cast<const bf16*>(L.w_gu); j.n_rows = p.I; j.K = p.H; j.I = p.I;
+        j.X = reinterpret_cast<const bf16*>(p.xn); j.ldx = p.H; j.ssq = p.ssq; j.eps = L.eps_post;
         j.bias = nullptr; j.out = p.act; j.ldo = p.I;
         { DS_PROF_BEGIN(3); if (!gemm_phase<1, 1, 0>(j, ds_smem, arena, bar)) return; DS_PROF_END(); }
-        // E: res += act . Wdown^T
-        j.W = reinterpret_cast<const bf16*>(L.w_down); j.n_units = p.H / 16; j.K = p.I; j.I = 0;
-        j.X = reinterpret_cast<const bf16*>(p.act); j.ldx = p.I; j.res = nullptr; j.nw = nullptr;
+        // E: res += act . Wdown^T; xn = bf16(res * weight of the norm that comes next)
+        const bool last = l + 1 == p.n_layers;
+        j.W = reinterpret_cast<const bf16*>(L.w_down); j.n_rows = p.H; j.K = p.I; j.I = 0;
+        j.X = reinterpret_cast<const bf16*>(p.act); j.ldx = p.I; j.ssq = nullptr;
         j.bias = nullptr; j.out = p.res; j.ldo = p.H;
+        j.next_w = last ? p.final_norm : p.layers[l + 1].norm_in;
+        j.next_w_f32 = last ? p.final_f32 : p.layers[l + 1].norm_f32;
         { DS_PROF_BEGIN(4); if (!gemm_phase<0, 0, 2>(j, ds_smem, arena, bar)) return; DS_PROF_END(); }
     }
     // head: logits = norm_final(res) . Wlm^T, float32
-    j.W = reinterpret_cast<const bf16*>(p.lm_head); j.n_units = p.V / 16; j.K = p.H; j.I = 0;
-    j.X = nullptr; j.ldx = 0; j.res = p.res; j.nw = p.final_norm; j.nw_f32 = p.final_f32; j.eps = p.eps_final;
+    j.W = reinterpret_cast<const bf16*>(p.lm_head); j.n_rows = p.V; j.K = p.H; j.I = 0;
+    j.X = reinterpret_cast<const bf16*>(p.xn); j.ldx = p.H; j.ssq = p.ssq; j.eps = p.eps_final;
     j.bias = nullptr; j.out = p.logits; j.ldo = p.V;
     { DS_PROF_BEGIN(5); gemm_phase<0, 1, 1>(j, ds_smem, arena, bar); DS_PROF_END(); }
 }
@@ -929,8 +946,9 @@ MSGL_API int msgl_decode_step_struct_bytes() { return (int)sizeof(DsStep); }
 static int ds_arena_bytes(int M, int H, int n_q, int n_kv, int I, int V) {
     using namespace ds;
     if (M < 1 || M > MAX_M || n_kv < 1 || n_q < n_kv || n_q % n_kv || n_q / n_kv > 8) return -1;
-    if (H <= 0 || (H & 31) || I <= 0 || (I & 31) || V <= 0 || (V & 15)) return -1;
-    int need = RING2_BYTES + H * 16 + RED_BYTES;                  // products whose input goes through a norm
+    if (H <= 0 || (H & 31) || I <= 0 || (I & 31) || V <= 0) return -1;
+    const int k_staged = H > n_q * MSGL_HEAD_DIM ? H : n_q * MSGL_HEAD_DIM;
+    int need = RING2_BYTES + k_staged * 16 + RED_BYTES;           // products whose x is copied whole into shared memory
     if (RING3_BYTES + RED_BYTES > need) need = RING3_BYTES + RED_BYTES;
     if (ATT_BYTES > need) need = ATT_BYTES;
     need = (need + 127) & ~127;
@@ -968,7 +986,7 @@ MSGL_API int msgl_decode_step(const DsStep* step, cudaStream_t stream) {
     const int arena = ds_arena_bytes(p.M, p.H, p.n_q, p.n_kv, p.I, p.V);
     if (arena < 0 || p.n_layers < 0 || p.page_size < 1 || p.max_split < 1 || p.bt_stride < 1) return MSGL_ERR_SIZE;
     if (p.rope != nullptr && (p.rot < 2 || (p.rot & 1) || p.rot > MSGL_HEAD_DIM || p.max_pos < 1)) return MSGL_ERR_SIZE;
-    if (p.bar == nullptr || p.status == nullptr || p.tickets == nullptr) return MSGL_ERR_SIZE;
+    if (p.bar == nullptr || p.status == nullptr || p.tickets == nullptr || p.xn == nullptr || p.ssq == nullptr) return MSGL_ERR_SIZE;
     const int blocks = msgl_decode_step_blocks(p.M, p.H, p.n_q, p.n_kv, p.I, p.V);
     if (blocks <= 0) return MSGL_ERR_SIZE;
     if (cudaMemsetAsync(p.bar, 0, sizeof(unsigned), stream) != cudaSuccess) return msgl_check_launch();

@@ -597,7 +597,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------
 # the whole decode step in one persistent kernel (csrc/decode_step.cu)
 # ---------------------------------------------------------------------------------------
-# Off unless MSGL_FUSED_DECODE=1: measured on B200 at Qwen3-8B's sizes the one-kernel step takes 5.0 / 5.8 ms at batch 1 / 8
+# Off unless MSGL_FUSED_DECODE=1: measured on B200 at Qwen3-8B's sizes the one-kernel step takes 4.2 / 5.4 ms at batch 1 / 8
 # (context 4,096) against 3.4 / 4.2 ms kernel by kernel (see profiles/decode_step_kernel_b1_b8.md for where the time goes).
 USE_FUSED_DECODE = os.environ.get("MSGL_FUSED_DECODE", "0") == "1"
 FUSED_DECODE_MAX_TOKENS = 8
@@ -624,7 +624,7 @@ class DsStep(ctypes.Structure):
                 ("out_loc", c_void_p), ("nsplit", c_void_p),
                 ("embed", c_void_p), ("final_norm", c_void_p), ("final_f32", c_int), ("eps_final", c_float),
                 ("lm_head", c_void_p),
-                ("res", c_void_p), ("qkv", c_void_p), ("attn", c_void_p), ("act", c_void_p),
+                ("res", c_void_p), ("xn", c_void_p), ("ssq", c_void_p), ("qkv", c_void_p), ("attn", c_void_p), ("act", c_void_p),
                 ("part_o", c_void_p), ("part_ml", c_void_p), ("tickets", c_void_p), ("logits", c_void_p),
                 ("bar", c_void_p), ("status", c_void_p)]
 

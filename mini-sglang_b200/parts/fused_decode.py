@@ -141,6 +141,8 @@ class FusedDecodeStep:
         M8 = ops.FUSED_DECODE_MAX_TOKENS
         qkv_n = (self.n_q + 2 * self.n_kv) * self.d
         res = ws.get("ds_res", M8 * self.H, torch.float32)
+        xn = ws.get("ds_xn", M8 * self.H, torch.bfloat16)
+        ssq = ws.get("ds_ssq", 8 * max(self.blocks_for(B), 1), torch.float32)
         qkv = ws.get("ds_qkv", M8 * qkv_n, torch.bfloat16)
         attn = ws.get("ds_attn", M8 * self.n_q * self.d, torch.bfloat16)
         act = ws.get("ds_act", M8 * self.I, torch.bfloat16)
@@ -162,6 +164,7 @@ class FusedDecodeStep:
         st.final_f32, st.eps_final = int(self.fin["weight"].dtype == torch.float32), self.fin["eps"]
         st.lm_head = self.head["weight"].data_ptr()
         st.res, st.qkv, st.attn, st.act = res.data_ptr(), qkv.data_ptr(), attn.data_ptr(), act.data_ptr()
+        st.xn, st.ssq = xn.data_ptr(), ssq.data_ptr()
         st.part_o, st.part_ml, st.tickets, st.logits = part_o.data_ptr(), part_ml.data_ptr(), self._tickets.data_ptr(), logits.data_ptr()
         st.bar = self._bar.data_ptr()
         st.status = ops._status_tensor(self.device).data_ptr() + 4 * ops.STATUS_WORD_DECODE_STEP
