@@ -17,7 +17,9 @@ mini_sglang/managers/scheduler_policy.py:47-232, mini_sglang/managers/batch_info
               the requests with the fewest generated tokens (ties: longest prompt) give back
               everything they hold and return to the waiting queue with their tokens, until the
               rest can decode `retract_decode_steps` more steps; they are prefilled again later.
-              If a single request is left and still does not fit, it is finished with reason abort.
+              If a single decoding request is left and still does not fit, requests whose prompts
+              are still being fed give way first (least in the cache first); if it is alone and still
+              does not fit, it is finished with reason abort.
   ratio       new_token_ratio starts at 0.7 * conservativeness, decays to 0.14 of that over 600
               decode steps, and is re-estimated after a retraction.
 
@@ -347,9 +349,21 @@ class Scheduler:
         retracted = []
         while keep and not self._make_room(self._decode_pages(keep, self.retract_decode_steps)):
             if len(keep) == 1:
-                # nothing left to take pages from: one more step still has to fit
+                # no other decoding request to take pages from: one more step still has to fit
                 if self._make_room(self._decode_pages(keep, 1)):
                     break
+                # requests whose prompts are still being fed hold pages too: the one with the least in the cache
+                # gives everything back and waits (it has generated nothing yet), before anybody is given up
+                feeding = [q for q in self.running if q not in keep and q not in retracted]
+                if feeding:
+                    q = min(feeding, key=lambda q: int(self.mgr.length[q.slot]))
+                    self._release(q, insert=False)
+                    q.retractions += 1
+                    self.running.remove(q)
+                    self.waiting.append(q)
+                    retracted.append(q)
+                    self.stats["retractions"] += 1
+                    continue
                 r = keep.pop()
                 r.to_abort = "out of cache pages"
                 r.check_finished()

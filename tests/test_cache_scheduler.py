@@ -614,3 +614,75 @@ def test_scheduler_on_a_model_with_an_all_keys_group_and_a_windowed_group():
     assert sch.stats["retractions"] == 0, "admission ignored the windowed group's pool"
     assert max(len(st) for st in runner.steps) <= 4
     assert all(r.finish_reason.type == "length" for r in reqs)
+
+
+def test_random_prefix_sharing_under_pressure_gives_the_tokens_of_an_unshared_run():
+    """Many random runs: families of prompts that share prefixes of different lengths, prompts fed in small portions, pools so
+    small that cached pages are evicted and requests retracted, requests arriving over time, both policies that use the
+    prefix cache.  Every run must give each request the tokens it gets alone without any sharing; the stand-in runner checks
+    on every step that every page a request reads holds that request's own tokens."""
+    rnd = random.Random(5)
+    for trial in range(40):
+        P = rnd.choice([1, 4, 16])
+        n = rnd.randrange(4, 12)
+        families = [[rnd.randrange(1, 60) for _ in range(rnd.randrange(8, 70))] for _ in range(rnd.randrange(1, 4))]
+        prompts = []
+        for i in range(n):
+            fam = rnd.choice(families)
+            keep = rnd.randrange(0, len(fam) + 1)
+            prompts.append(fam[:keep] + [rnd.randrange(1, 60) for _ in range(rnd.randrange(1, 30))])
+        max_new = [rnd.randrange(1, 20) for _ in range(n)]
+        arrive = sorted(rnd.randrange(0, 25) for _ in range(n))
+        longest = max(len(p) + m for p, m in zip(prompts, max_new))
+        pages = -(-longest // P) + rnd.randrange(2, 40 // P + 6)
+        chunk = rnd.choice([5, 16, 64])
+        kw = dict(max_reqs=rnd.choice([2, 4, 8]), budget=rnd.choice([24, 64]), chunk=chunk, policy=rnd.choice(["lpm", "fcfs"]),
+                  conservativeness=rnd.choice([0.3, 1.0]), lookahead=rnd.random() < 0.5)
+        # every request alone, nothing shared
+        want = []
+        for p, m in zip(prompts, max_new):
+            sch0, _ = make_sched({0: PagedKVNeed(2, 16)}, P, 400, enable_prefix_cache=False)
+            q = Req("solo", p, SamplingParams(max_new_tokens=m, ignore_eos=True))
+            sch0.add_request(q)
+            drain(sch0)
+            want.append(q.output)
+        sch, runner = make_sched({0: PagedKVNeed(2, 16)}, P, pages, **kw)
+        reqs = [Req(f"r{i}", p, SamplingParams(max_new_tokens=m, ignore_eos=True)) for i, (p, m) in enumerate(zip(prompts, max_new))]
+        step, nxt = 0, 0
+        while nxt < n or not sch.idle:
+            while nxt < n and arrive[nxt] <= step:
+                sch.add_request(reqs[nxt])
+                nxt += 1
+            sch.step()
+            step += 1
+            assert step < 20000, (trial, kw)
+        sch.check_idle_invariants()
+        assert [r.output for r in reqs] == want, (trial, P, pages, kw)
+        assert all(r.finish_reason.type == "length" for r in reqs)
+
+
+def test_a_lone_decoding_request_is_not_given_up_while_a_prompt_under_way_holds_pages():
+    """One request decodes, another is still being fed its prompt in small portions, and the pool runs dry.  The request
+    whose prompt is under way (it has produced nothing yet) gives its pages back and waits; nobody is aborted, and everybody
+    gets the tokens of an unconstrained run."""
+    first = [3 + i % 40 for i in range(10)]
+    second = [7 + i % 31 for i in range(30)]
+    want = []
+    for p, m in ((first, 20), (second, 3)):
+        sch0, _ = make_sched({0: PagedKVNeed(2, 16)}, 4, 400, enable_prefix_cache=False)
+        q = Req("solo", p, SamplingParams(max_new_tokens=m, ignore_eos=True))
+        sch0.add_request(q)
+        drain(sch0)
+        want.append(q.output)
+    # 12 pages = 48 tokens: the first request needs 8 of them at its end, the second 8: admission lets the second in on the
+    # estimate that the first will generate a fifth of what it may, and the pool is dry before the second prompt is in
+    sch, runner = make_sched({0: PagedKVNeed(2, 16)}, 4, 12, chunk=3, budget=64, conservativeness=0.3, enable_prefix_cache=False)
+    a = Req("a", first, SamplingParams(max_new_tokens=20, ignore_eos=True))
+    b = Req("b", second, SamplingParams(max_new_tokens=3, ignore_eos=True))
+    sch.add_request(a)
+    for _ in range(2):
+        sch.step()
+    sch.add_request(b)
+    drain(sch)
+    assert sch.stats["aborted"] == 0 and sch.stats["retractions"] >= 1
+    assert [a.output, b.output] == want and b.retractions >= 1 and a.retractions == 0
