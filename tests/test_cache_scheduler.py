@@ -686,3 +686,51 @@ def test_a_lone_decoding_request_is_not_given_up_while_a_prompt_under_way_holds_
     drain(sch)
     assert sch.stats["aborted"] == 0 and sch.stats["retractions"] >= 1
     assert [a.output, b.output] == want and b.retractions >= 1 and a.retractions == 0
+
+
+def test_random_runs_on_two_cache_groups_give_the_tokens_of_an_unconstrained_run():
+    """Random requests, arrivals, aborts and pool sizes on a model with an all-keys group, a windowed group and per-request
+    state: every request that is not aborted gets the tokens of an unconstrained run, and both pools end empty."""
+    rnd = random.Random(9)
+    needs = {0: PagedKVNeed(2, 16), 1: PagedKVNeed(1, 16, window=10), 2: StateNeed((3,))}
+    for trial in range(25):
+        P = rnd.choice([1, 4, 8])
+        n = rnd.randrange(3, 10)
+        prompts = [[rnd.randrange(1, 60) for _ in range(rnd.randrange(1, 60))] for _ in range(n)]
+        max_new = [rnd.randrange(1, 25) for _ in range(n)]
+        arrive = sorted(rnd.randrange(0, 20) for _ in range(n))
+        abort_at = {rnd.randrange(n): rnd.randrange(1, 40)} if trial % 4 == 0 else {}
+        longest = max(len(p) + m for p, m in zip(prompts, max_new))
+        chunk = rnd.choice([4, 16, 64])
+        kw = dict(max_reqs=rnd.choice([2, 4, 6]), budget=rnd.choice([24, 64]), chunk=chunk, conservativeness=rnd.choice([0.3, 1.0]),
+                  lookahead=rnd.random() < 0.5)
+        want = []
+        for p, m in zip(prompts, max_new):
+            sch0, _ = make_sched(needs, P, 600, budget=64)
+            q = Req("solo", p, SamplingParams(max_new_tokens=m, ignore_eos=True))
+            sch0.add_request(q)
+            drain(sch0)
+            want.append(q.output)
+        sch, runner = make_sched(needs, P, -(-longest // P) + rnd.randrange(2, 30), **kw)
+        if rnd.random() < 0.5:                       # a scarce windowed pool: room for one request's window and portion, and some
+            per_req = -(-(10 + min(chunk, kw["budget"]) + P) // P) + 1
+            sch.mgr.groups[1].pool = PagePool(per_req + rnd.randrange(0, 2 * per_req))
+        reqs = [Req(f"r{i}", p, SamplingParams(max_new_tokens=m, ignore_eos=True)) for i, (p, m) in enumerate(zip(prompts, max_new))]
+        step, nxt = 0, 0
+        while nxt < n or not sch.idle:
+            while nxt < n and arrive[nxt] <= step:
+                sch.add_request(reqs[nxt])
+                nxt += 1
+            for i, at in abort_at.items():
+                if at == step:
+                    sch.abort(f"r{i}")
+            sch.step()
+            step += 1
+            assert step < 20000, (trial, kw)
+        sch.check_idle_invariants()
+        assert all(g.pool.in_use == 0 for g in sch.mgr.groups)
+        for i, r in enumerate(reqs):
+            if i in abort_at and r.finish_reason.type == "abort":
+                assert r.output == want[i][:len(r.output)]
+            else:
+                assert r.finish_reason.type == "length" and r.output == want[i], (trial, i, P, kw, r.finish_reason)
