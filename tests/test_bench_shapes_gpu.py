@@ -164,3 +164,35 @@ def test_sixtyfour_requests_decode_at_4090_keys_and_beyond_6144(model):
             close(got[(j, r)], ref[r], dtype, f"request {j}, position {r}")
     for s in slots:
         runner.close(s)
+
+
+def test_one_request_of_32000_tokens(model):
+    """A long context: 32,000 tokens fed in portions of 8,192 (the tcgen05 prefill kernel over prefixes of up to 24,576 keys),
+    then decoded token by token with the keys cut into 32 pieces (the decode graph with the wide split dimension).  bfloat16,
+    the last row of every portion and every decoded row against the plain implementation."""
+    from mini_sglang_b200 import ops
+    from mini_sglang_b200.config import Qwen3Config
+    from mini_sglang_b200.config.qwen3 import build_qwen3_spec
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    _, weights = model
+    cfg = dict(CFG, max_position_embeddings=32768)
+    spec = build_qwen3_spec(Qwen3Config.from_dict(cfg))
+    n_ctx, n_dec = 32000, 3
+    toks = tokens(n_ctx + n_dec, 77)
+    runner = ModelRunner.from_random(spec, 11, dtype="bfloat16", page_size=PAGE, num_pages=(n_ctx + n_dec) // PAGE + 8, max_reqs=2)
+    s = runner.open()
+    got = {}
+    for lo in range(0, n_ctx, 8192):
+        hi = min(lo + 8192, n_ctx)
+        got[hi - 1] = runner.step([StepEntry(s, toks[lo:hi], [hi - lo - 1])]).float().cpu()[0]
+    for t in range(n_dec):
+        got[n_ctx + t] = runner.step([StepEntry(s, [toks[n_ctx + t]], [0])]).float().cpu()[0]
+        assert runner.last_step_used_graph
+        assert runner.last_plan["graph_key"] == (1, (2048,), True) and runner.last_plan["nsplits"] == [[32]], runner.last_plan
+    ops.check_kernel_status()
+    rows = sorted(got)
+    with torch.no_grad():
+        ref = P.forward_sequence(cfg, weights, toks, device="cuda", rows=rows).cpu()
+    for r, want in zip(rows, ref):
+        close(got[r], want, "bfloat16", f"position {r}")
+    runner.close(s)
