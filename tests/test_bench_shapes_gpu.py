@@ -1,7 +1,7 @@
 """The shapes that bench.py times, against the plain implementation: Qwen3-8B's layer widths (two layers), a
 2,048-token prompt in one step and a second 2,048-token portion behind it, 8 and 64 requests decoding at about
-4,090 keys through the CUDA graphs with the kv splits that the planner chooses by itself, and 64 requests beyond
-6,144 keys, where the planner halves every request.  Each test also asserts which graph and which splits were
+4,090 keys through the CUDA graphs with the kv splits that the planner chooses by itself, 64 requests beyond
+6,144 keys, where the planner halves every request, and one request of 32,000 tokens (portions of 8,192, 32 kv splits).  Each test also asserts which graph and which splits were
 taken, so that a change of the planner cannot quietly move the benchmark onto a path that is compared nowhere."""
 
 import pytest
