@@ -213,3 +213,45 @@ def test_whole_step_decode_kernel_against_plain(monkeypatch):
                 check_row(got[(i, k)], want, "bfloat16")
             except AssertionError as e:
                 raise AssertionError(f"request {i} ({lens[i]} tokens), decoded token {k}: {e}") from None
+
+
+@pytest.mark.parametrize("shape", [
+    ("0.6B", 1024, 16, 8, 3072, True), ("1.7B", 2048, 16, 8, 6144, True), ("4B", 2560, 32, 8, 9728, True),
+    ("14B", 5120, 40, 8, 17408, False), ("32B", 5120, 64, 8, 25600, False)], ids=lambda s: s[0])
+def test_layer_widths_of_the_other_qwen3_sizes(shape):
+    """Two layers at the widths of every other Qwen3 dense size (groups of 2, 4, 5 and 8 query heads per kv head, widths and
+    feed-forward widths that are no power of two, tied and untied heads): a 300-token prompt in one step, a 40-token portion,
+    two requests decoding through the graph; bfloat16 against the plain implementation."""
+    from mini_sglang_b200.config import Qwen3Config
+    from mini_sglang_b200.config.qwen3 import build_qwen3_spec
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    from mini_sglang_b200.parts import expected_tensors
+    from mini_sglang_b200.weights import RandomSource
+    _, H, n_q, n_kv, I, tied = shape
+    cfg = dict(CFG, hidden_size=H, num_attention_heads=n_q, num_key_value_heads=n_kv, intermediate_size=I, tie_word_embeddings=tied)
+    spec = build_qwen3_spec(Qwen3Config.from_dict(cfg))
+    src = RandomSource(expected_tensors(spec), 7, torch.bfloat16, "cuda")
+    weights = {n: src.draw(n) for n in expected_tensors(spec) if src.has(n)}
+    g = torch.Generator().manual_seed(H + I)
+    a = torch.randint(0, cfg["vocab_size"], (346,), generator=g).tolist()
+    b = torch.randint(0, cfg["vocab_size"], (25,), generator=g).tolist()
+    runner = ModelRunner.from_random(spec, 7, dtype="bfloat16", page_size=16, num_pages=40, max_reqs=2)
+    sa, sb = runner.open(), runner.open()
+    got = {}
+    out = runner.step([StepEntry(sa, a[:300], [0, 299])]).float().cpu()
+    got[("a", 0)], got[("a", 299)] = out[0], out[1]
+    out = runner.step([StepEntry(sa, a[300:340], [39]), StepEntry(sb, b[:19], [18])]).float().cpu()
+    got[("a", 339)], got[("b", 18)] = out[0], out[1]
+    for t in range(6):
+        out = runner.step([StepEntry(sa, [a[340 + t]], [0]), StepEntry(sb, [b[19 + t]], [0])]).float().cpu()
+        assert runner.last_step_used_graph
+        got[("a", 340 + t)], got[("b", 19 + t)] = out[0], out[1]
+    with torch.no_grad():
+        ref = {"a": P.forward_sequence(cfg, weights, a, device="cuda").cpu(), "b": P.forward_sequence(cfg, weights, b, device="cuda").cpu()}
+    for (rid, pos), row in sorted(got.items()):
+        try:
+            check_row(row, ref[rid][pos], "bfloat16")
+        except AssertionError as e:
+            raise AssertionError(f"{shape[0]}: request {rid} position {pos}: {e}") from None
+    runner.close(sa)
+    runner.close(sb)
