@@ -55,6 +55,7 @@ struct AttnParams {
     const int* kv_len;        // [B]
     const int* block_table;   // [B, bt_stride]
     const int* nsplit;        // [B] or null (1 everywhere)
+    const int* order;         // [B] or null: with uniform_decode, the request that the i-th block along x takes
     float* part_o;            // [(split * T + token) * n_q + head][d]
     float* part_ml;           // [(split * T + token) * n_q + head][2]  (max in log2 units, sum)
     int B, T, n_q, n_kv, d, page_size, bt_stride, window, max_split;
@@ -83,8 +84,11 @@ __device__ __forceinline__ bool find_tile(const AttnParams& p, int tile_tokens, 
                                           int tile_idx = -1, int n_tile_idx = 0) {
     if (tile_idx < 0) { tile_idx = (int)blockIdx.x; n_tile_idx = (int)gridDim.x; }
     if (p.uniform_decode) {
-        const int r = tile_idx;
-        if (r >= p.B) return false;
+        // blocks are handed to the SMs in index order: the host (or the kernel that made the step's fields) lists
+        // the requests by falling number of keys, so that the longest start first and the shortest fill the end
+        if (tile_idx >= p.B) return false;
+        const int r = p.order ? p.order[tile_idx] : tile_idx;
+        if (r < 0 || r >= p.B) return false;
         ti.req = r; ti.t0 = 0; ti.n_tok = 1; ti.q_len = 1; ti.kv_len = p.kv_len[r]; ti.q_base = p.q_start[r];
         return true;
     }
@@ -128,6 +132,20 @@ __device__ __forceinline__ bool find_tile(const AttnParams& p, int tile_tokens, 
     ti.kv_len = p.kv_len[ti.req];
     ti.n_tok = min(tile_tokens, ti.q_len - ti.t0);
     return true;
+}
+
+// This block's place in the launch: (index among the query tiles, index along y = kv head and chunk of q heads).  With an
+// order given (uniform decode) consecutive blocks take the kv heads of one request, so that across the whole launch the
+// requests are walked in that order: the longest first.
+__device__ __forceinline__ void block_place(const AttnParams& p, int& tile_idx, int& y) {
+    if (p.uniform_decode && p.order) {
+        const int lin = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+        tile_idx = lin / (int)gridDim.y;
+        y = lin - tile_idx * (int)gridDim.y;
+    } else {
+        tile_idx = (int)blockIdx.x;
+        y = (int)blockIdx.y;
+    }
 }
 
 // Which key tiles a block walks: the tiles that hold keys [k_lo, p_max], cut into ns splits.
@@ -220,11 +238,13 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
     const int Gc = G <= R ? G : R;
     const int n_chunks = G <= R ? 1 : (G + R - 1) / R;
     const int QT = G <= R ? R / G : 1;
-    const int kvh = blockIdx.y / n_chunks;
-    const int chunk = blockIdx.y - kvh * n_chunks;
+    int tile_idx, by;
+    block_place(p, tile_idx, by);
+    const int kvh = by / n_chunks;
+    const int chunk = by - kvh * n_chunks;
 
     TileInfo ti;
-    if (!find_tile(p, QT, ti, sh_tile)) return;
+    if (!find_tile(p, QT, ti, sh_tile, tile_idx, (int)gridDim.x)) return;
     const int ns = p.nsplit ? min(max(p.nsplit[ti.req], 1), p.max_split) : 1;
     const int split = blockIdx.z;
     if (split >= ns) return;
@@ -452,11 +472,13 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnParams p
     const int Gc = G <= R ? G : R;
     const int n_chunks = G <= R ? 1 : (G + R - 1) / R;
     const int QT = G <= R ? R / G : 1;
-    const int kvh = blockIdx.y / n_chunks;
-    const int chunk = blockIdx.y - kvh * n_chunks;
+    int tile_idx, by;
+    block_place(p, tile_idx, by);
+    const int kvh = by / n_chunks;
+    const int chunk = by - kvh * n_chunks;
 
     TileInfo ti;
-    if (!find_tile(p, QT, ti, sh_tile)) return;
+    if (!find_tile(p, QT, ti, sh_tile, tile_idx, (int)gridDim.x)) return;
     const int ns = p.nsplit ? min(max(p.nsplit[ti.req], 1), p.max_split) : 1;
     const int split = blockIdx.z;
     if (split >= ns) return;
@@ -715,11 +737,13 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
     const int Gc = G <= C ? G : C;
     const int n_chunks = G <= C ? 1 : (G + C - 1) / C;
     const int QT = G <= C ? C / G : 1;
-    const int kvh = blockIdx.y / n_chunks;
-    const int chunk = blockIdx.y - kvh * n_chunks;
+    int tile_idx, by;
+    block_place(p, tile_idx, by);
+    const int kvh = by / n_chunks;
+    const int chunk = by - kvh * n_chunks;
 
     TileInfo ti;
-    if (!find_tile(p, QT, ti, sh_tile)) return;
+    if (!find_tile(p, QT, ti, sh_tile, tile_idx, (int)gridDim.x)) return;
     const int ns = p.nsplit ? min(max(p.nsplit[ti.req], 1), p.max_split) : 1;
     const int split = blockIdx.z;
     if (split >= ns) return;
@@ -1023,11 +1047,13 @@ __global__ void __launch_bounds__(SIMT_THREADS) attn_simt_kernel(const AttnParam
     const int Gc = G <= R ? G : R;
     const int n_chunks = G <= R ? 1 : (G + R - 1) / R;
     const int QT = G <= R ? R / G : 1;
-    const int kvh = blockIdx.y / n_chunks;
-    const int chunk = blockIdx.y - kvh * n_chunks;
+    int tile_idx, by;
+    block_place(p, tile_idx, by);
+    const int kvh = by / n_chunks;
+    const int chunk = by - kvh * n_chunks;
 
     TileInfo ti;
-    if (!find_tile(p, QT, ti, sh_tile)) return;
+    if (!find_tile(p, QT, ti, sh_tile, tile_idx, (int)gridDim.x)) return;
     const int ns = p.nsplit ? min(max(p.nsplit[ti.req], 1), p.max_split) : 1;
     const int split = blockIdx.z;
     if (split >= ns) return;
@@ -1213,13 +1239,13 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
                             const int* kv_len, const int* block_table, const int* nsplit, float* part_o,
                             float* part_ml, int B, int T_, int n_q, int n_kv, int d, int page_size, int bt_stride,
                             int window, int max_split, float scale, int qlen_min, int qlen_max, int uniform_decode,
-                            int variant, int grid_x, int dtype, cudaStream_t stream) {
+                            int variant, int grid_x, int dtype, const int* order, cudaStream_t stream) {
     if (grid_x <= 0 || B <= 0) return MSGL_OK;
     if (n_kv <= 0 || n_q % n_kv != 0 || d <= 0 || page_size <= 0 || max_split < 1) return MSGL_ERR_SIZE;
     if (max_split > 1 && (part_o == nullptr || part_ml == nullptr || nsplit == nullptr)) return MSGL_ERR_SIZE;
     AttnParams p;
     p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len;
-    p.block_table = block_table; p.nsplit = nsplit; p.part_o = part_o; p.part_ml = part_ml;
+    p.block_table = block_table; p.nsplit = nsplit; p.order = order; p.part_o = part_o; p.part_ml = part_ml;
     p.B = B; p.T = T_; p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.page_size = page_size; p.bt_stride = bt_stride;
     p.window = window; p.max_split = max_split;
     p.page_shift = -1;
@@ -1313,7 +1339,7 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
     AttnParams p;
     p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len;
-    p.block_table = block_table; p.nsplit = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
+    p.block_table = block_table; p.nsplit = nullptr; p.order = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
     p.B = B; p.T = T_; p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.page_size = page_size; p.bt_stride = bt_stride;
     p.window = window; p.max_split = 1;
     p.page_shift = -1;

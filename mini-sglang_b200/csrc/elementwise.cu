@@ -69,11 +69,33 @@ __global__ void decode_meta_kernel(const int* __restrict__ id, const int* __rest
                                    int page_size, int mp, int common, int* __restrict__ input_ids, int* __restrict__ positions,
                                    int* __restrict__ token_req, int* __restrict__ q_start, int* __restrict__ kv_len,
                                    int* __restrict__ slots, int* __restrict__ out_loc, int* __restrict__ nsplit,
-                                   int* __restrict__ block_table) {
+                                   int* __restrict__ block_table, int window, int* __restrict__ order) {
     const int r = blockIdx.x;
     const bool live = r < B;
     const int sl = live ? slot[r] : 0, ps = live ? pos[r] : 0;
     const int* row = table + (size_t)sl * row_stride;
+    // order[i] = the row with the i-th most keys per kv split (ties: the lower row first; padding rows last): this
+    // row's place is the number of rows that come before it
+    __shared__ int before;
+    if (threadIdx.x == 0) before = 0;
+    __syncthreads();
+    {
+        auto load_of = [&](int j) -> int {
+            if (j >= B) return 0;
+            int keys = pos[j] + 1;
+            if (window > 0) keys = min(keys, window + 1);
+            return (keys + max(nsplit_in[j], 1) - 1) / max(nsplit_in[j], 1);
+        };
+        const int mine = load_of(r);
+        int n = 0;
+        for (int j = threadIdx.x; j < b; j += blockDim.x) {
+            const int other = load_of(j);
+            n += (other > mine || (other == mine && j < r)) ? 1 : 0;
+        }
+        if (n) atomicAdd(&before, n);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) order[before] = r;
     if (threadIdx.x == 0) {
         if (common) {
             input_ids[r] = live ? id[r] : 0;
@@ -100,11 +122,12 @@ MSGL_API int msgl_table_delta(const int* deltas, int n_records, int* table, int 
 MSGL_API int msgl_decode_meta(const int* id, const int* slot, const int* pos, const int* nsplit_in, int B, int b, const int* table,
                               int row_stride, int page_size, int mp, int common, int* input_ids, int* positions, int* token_req,
                               int* q_start, int* kv_len, int* slots, int* out_loc, int* nsplit, int* block_table,
-                              cudaStream_t stream) {
+                              int window, int* order, cudaStream_t stream) {
     if (b <= 0) return MSGL_OK;
-    if (B < 0 || B > b || page_size < 1 || mp < 1 || row_stride < 1) return MSGL_ERR_SIZE;
+    if (B < 0 || B > b || page_size < 1 || mp < 1 || row_stride < 1 || order == nullptr) return MSGL_ERR_SIZE;
     decode_meta_kernel<<<b, 128, 0, stream>>>(id, slot, pos, nsplit_in, B, b, table, row_stride, page_size, mp, common, input_ids,
-                                             positions, token_req, q_start, kv_len, slots, out_loc, nsplit, block_table);
+                                             positions, token_req, q_start, kv_len, slots, out_loc, nsplit, block_table,
+                                             window, order);
     return msgl_check_launch();
 }
 

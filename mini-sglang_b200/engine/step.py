@@ -67,10 +67,11 @@ class _Layout:
 
         self.input_ids, self.positions, self.token_req = take(T), take(T), take(T)
         self.q_start, self.kv_len, self.slots, self.want = take(B + 1), take(B), take(B), take(W)
-        self.out_loc, self.nsplit, self.table = [], [], []
+        self.out_loc, self.nsplit, self.order, self.table = [], [], [], []
         for mp in max_pages:
             self.out_loc.append(take(T))
             self.nsplit.append(take(B))
+            self.order.append(take(B))
             self.table.append(take(B * mp))
         self.size = off
 
@@ -182,6 +183,19 @@ def plan_kv_splits(q_lens: Sequence[int], kv_lens: Sequence[int], *, n_kv: int, 
                 if keys[i] >= 2 * MIN_KEYS_PER_PIECE:
                     out[i] = 2
     return out
+
+
+def decode_order(kv_lens, nsplits, window: Optional[int], b: int) -> np.ndarray:
+    """The rows of a decode batch in the order in which the attention launch takes them: by falling number of keys
+    per kv split (blocks go to the SMs in index order, so the longest start first and the shortest fill the end);
+    ties keep the rows' order, and the padding rows up to `b` come last."""
+    keys = np.asarray(kv_lens, dtype=np.int64)
+    if window:
+        keys = np.minimum(keys, window + 1)
+    ns = np.maximum(np.asarray(nsplits, dtype=np.int64), 1)
+    load = np.zeros(b, dtype=np.int64)
+    load[:len(keys)] = -(-keys // ns)
+    return np.argsort(-load, kind="stable").astype(np.int32)
 
 
 class ModelRunner:
@@ -326,6 +340,8 @@ class ModelRunner:
         T, B = lay.T, lay.B
         host[:lay.size] = 0
         n_ent = len(entries)
+        for gi in range(len(self.mgr.groups)):
+            host[lay.order[gi]: lay.order[gi] + B] = np.arange(B, dtype=np.int32)
         if n_ent and all(len(e.tokens) == 1 for e in entries):
             # one token per request (decode): every field with a handful of vector operations
             slots = np.fromiter((e.slot for e in entries), dtype=np.int64, count=n_ent)
@@ -341,6 +357,7 @@ class ModelRunner:
                 mp = lay.max_pages[gi]
                 host[lay.out_loc[gi]: lay.out_loc[gi] + n_ent] = g.table[slots, pos // P].astype(np.int64) * P + pos % P
                 host[lay.nsplit[gi]: lay.nsplit[gi] + n_ent] = nsplits[gi]
+                host[lay.order[gi]: lay.order[gi] + B] = decode_order(pos + 1, nsplits[gi], g.window, B)
                 width = min(mp, g.table.shape[1])
                 host[lay.table[gi]: lay.table[gi] + n_ent * mp].reshape(n_ent, mp)[:, :width] = g.table[slots, :width]
             t = n_ent
@@ -383,7 +400,8 @@ class ModelRunner:
                                        out_loc=v(lay.out_loc[gi], lay.T),
                                        nsplit=v(lay.nsplit[gi], lay.B) if max_splits[gi] > 1 else None,
                                        max_split=max_splits[gi], window=g.window,
-                                       host_nsplit=nsplits[gi] if nsplits is not None else None))
+                                       host_nsplit=nsplits[gi] if nsplits is not None else None,
+                                       order=v(lay.order[gi], lay.B) if uniform else None))
         return StepContext(T=lay.T, B=lay.B, page_size=self.page_size, input_ids=v(lay.input_ids, lay.T),
                            positions=v(lay.positions, lay.T), q_start=v(lay.q_start, lay.B + 1),
                            kv_len=v(lay.kv_len, lay.B), token_req=v(lay.token_req, lay.T), slots=v(lay.slots, lay.B),
@@ -590,7 +608,8 @@ class ModelRunner:
                             self.page_size, mp, gi == 0,
                             input_ids=g0[lay.input_ids:], positions=g0[lay.positions:], token_req=g0[lay.token_req:],
                             q_start=g0[lay.q_start:], kv_len=g0[lay.kv_len:], slots=g0[lay.slots:],
-                            out_loc=g0[lay.out_loc[gi]:], nsplit=g0[lay.nsplit[gi]:], block_table=g0[lay.table[gi]:])
+                            out_loc=g0[lay.out_loc[gi]:], nsplit=g0[lay.nsplit[gi]:], block_table=g0[lay.table[gi]:],
+                            order=g0[lay.order[gi]:], window=int(self.mgr.groups[gi].window or 0))
 
     def _capture(self, b: int, mp: Tuple[int, ...], max_split: Sequence[int]) -> _Graph:
         gr = _Graph()

@@ -112,7 +112,7 @@ class PagedAttention(Mixer):
         common = dict(q_start=ctx.q_start, kv_len=ctx.kv_len, block_table=g.block_table,
                       nsplit=g.nsplit if max_split > 1 else None, part_o=part_o, part_ml=part_ml, n_kv=self.n_kv,
                       page_size=cache.page_size, window=window, max_split=max_split, scale=self.scale,
-                      uniform_decode=ctx.uniform_decode)
+                      uniform_decode=ctx.uniform_decode, order=g.order if ctx.uniform_decode else None)
         big = 1 << 30
         if not self.use_mma:
             qt = ops.attention_tile_tokens(ops.VARIANT_SIMT, G)

@@ -22,6 +22,7 @@ class GroupContext:
     max_split: int
     window: Optional[int]
     host_nsplit: Optional[Sequence[int]] = None     # the host's copy of nsplit (None: not known here)
+    order: Optional[torch.Tensor] = None            # [B] int32, uniform decode only: the requests by falling number of keys
 
 
 @dataclasses.dataclass

@@ -494,6 +494,24 @@ def test_kv_split_plan():
     assert plan_kv_splits([1] * 16, [8192] * 16, cap=16, **wide) == [slots // (16 * 2 * 2)] * 16
 
 
+def test_order_of_a_decode_batch():
+    """The attention launch of a decode step takes the requests by falling number of keys per kv split; rows of equal
+    load keep their order, padding rows of a captured batch size come last."""
+    from mini_sglang_b200.engine.step import decode_order
+    assert decode_order([100, 700, 100, 30], [1, 1, 1, 1], None, 4).tolist() == [1, 0, 2, 3]
+    assert decode_order([100, 700, 100, 30], [1, 8, 1, 1], None, 4).tolist() == [0, 2, 1, 3]        # 700 keys in 8 pieces: 88 a block
+    assert decode_order([100, 700, 100, 30], [1, 1, 1, 1], 63, 6).tolist() == [0, 1, 2, 3, 4, 5]    # a window of 63: 64, 64, 64, 30 keys
+    assert decode_order([5, 9], [1, 1], None, 4).tolist() == [1, 0, 2, 3]
+    rnd = np.random.RandomState(3)
+    for _ in range(20):
+        n, b = int(rnd.randint(1, 40)), 48
+        lens, ns = rnd.randint(1, 3000, n), rnd.randint(1, 5, n)
+        order = decode_order(lens, ns, None, b).tolist()
+        assert sorted(order) == list(range(b)) and order[n:] == list(range(n, b))
+        load = [-(-int(lens[i]) // int(ns[i])) for i in order[:n]]
+        assert load == sorted(load, reverse=True)
+
+
 # ---------------------------------------------------------------------------------------
 # prefix cache under pressure, portions, and several groups
 # ---------------------------------------------------------------------------------------

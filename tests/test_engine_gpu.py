@@ -219,6 +219,9 @@ def test_step_fields_made_on_the_device_equal_the_hosts(monkeypatch):
             mp = lay.max_pages[gi]
             assert (got[lay.out_loc[gi]: lay.out_loc[gi] + b] == want[lay.out_loc[gi]: lay.out_loc[gi] + b]).all()
             assert (got[lay.nsplit[gi]: lay.nsplit[gi] + b] == want[lay.nsplit[gi]: lay.nsplit[gi] + b]).all()
+            order = got[lay.order[gi]: lay.order[gi] + b]
+            assert (order == want[lay.order[gi]: lay.order[gi] + b]).all(), (order, want[lay.order[gi]: lay.order[gi] + b])
+            assert sorted(order.tolist()) == list(range(b))
             tg, tw = got[lay.table[gi]: lay.table[gi] + b * mp].reshape(b, mp), want[lay.table[gi]: lay.table[gi] + b * mp].reshape(b, mp)
             for r, e in enumerate(entries):                 # the pages a request holds; what lies beyond them is never read
                 n = int(g.n_pages[e.slot])

@@ -314,7 +314,7 @@ def attention_reference(q, K, V, q_lens, kv_lens, scale, window):
 
 
 def run_attention_case(dtype, n_q, n_kv, d, P, q_lens, kv_lens, window=None, force_split=None, seed=0,
-                       spike=False):
+                       spike=False, order=None):
     from mini_sglang_b200.config import PartSpec
     from mini_sglang_b200.parts import BuildEnv, GroupContext, KVCacheView, StepContext, Workspace
     from mini_sglang_b200.parts.attention import PagedAttention
@@ -364,7 +364,8 @@ def run_attention_case(dtype, n_q, n_kv, d, P, q_lens, kv_lens, window=None, for
     nsplit, max_split = None, 1
     if force_split:
         nsplit, max_split = i32([force_split] * B), force_split
-    grp = GroupContext(block_table=bt.to(DEV), out_loc=i32([0] * T), nsplit=nsplit, max_split=max_split, window=window)
+    grp = GroupContext(block_table=bt.to(DEV), out_loc=i32([0] * T), nsplit=nsplit, max_split=max_split, window=window,
+                       order=i32(list(order)) if order is not None else None)
     uniform = all(n == 1 for n in q_lens)
     ctx = StepContext(T=T, B=B, page_size=P, input_ids=i32([0] * T), positions=i32([0] * T), q_start=i32(q_start),
                       kv_len=i32(kv_lens), token_req=i32(token_req), slots=i32([0] * B), groups=[grp],
@@ -393,10 +394,19 @@ def test_attention_mixed_batch(dtype, n_q, n_kv, d, P):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("force_split", [None, 2, 5])
-def test_attention_decode_batch_with_splits(dtype, force_split):
+@pytest.mark.parametrize("order", [None, "longest first", "any"])
+def test_attention_decode_batch_with_splits(dtype, force_split, order):
+    """Single decoded tokens of requests of very different lengths; the blocks take the requests in index order, by
+    falling length (what a decode step asks for) or in any other order: which block computes a request changes nothing."""
+    from mini_sglang_b200.engine.step import decode_order
     kv_lens = [1, 63, 64, 65, 700, 1500, 300, 129]
+    if order == "longest first":
+        order = decode_order(kv_lens, [force_split or 1] * len(kv_lens), None, len(kv_lens)).tolist()
+        assert order[:4] == [5, 4, 6, 7] and sorted(order) == list(range(8))
+    elif order == "any":
+        order = [3, 0, 7, 5, 1, 6, 2, 4]
     out, ref = run_attention_case(dtype, 32, 8, 128, 16, [1] * len(kv_lens), kv_lens, force_split=force_split,
-                                  seed=7, spike=True)
+                                  seed=7, spike=True, order=order)
     torch.testing.assert_close(out, ref.to(dtype).float(), **ATT_TOL[dtype])
 
 
