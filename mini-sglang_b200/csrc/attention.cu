@@ -56,6 +56,10 @@ struct AttnParams {
     const int* block_table;   // [B, bt_stride]
     const int* nsplit;        // [B] or null (1 everywhere)
     const int* order;         // [B] or null: with uniform_decode, the request that the i-th block along x takes
+    const int* even;          // null, or the even cut of a uniform decode launch (attn_decode_even_kernel): [0] blocks in use,
+                              // then start unit of every block [even_nb + 1], first request of every block [even_nb], first
+                              // unit of every request [B + 1], first block of every request [B]
+    int even_nb;              // blocks per (kv head, chunk of q heads) that the launch has
     float* part_o;            // [(split * T + token) * n_q + head][d]
     float* part_ml;           // [(split * T + token) * n_q + head][2]  (max in log2 units, sum)
     int B, T, n_q, n_kv, d, page_size, bt_stride, window, max_split;
@@ -715,43 +719,23 @@ __device__ __forceinline__ uint4 ldg16_stream(const void* ptr) {
     return v;
 }
 
+// One run of keys of one request through the transposed decode arithmetic: units [u_begin, u_end) of DEC_WT keys, the block's
+// warps taking them in turn; the result goes to the output (ns == 1) or to piece `split` of the request's partial results.
+// wait_here: this is the block's first run, the wait for the kernel before this one falls behind its first prefetches;
+// release_here: it is the last one, the next kernel may start beside its reduction.
 template <int D, int NW, int ST, int NBH>
-__global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_decode_t_kernel(const AttnParams p) {
+__device__ __forceinline__ void decode_t_run(const AttnParams& p, const TileInfo& ti, int ns, int split, int u_begin, int u_end,
+                                             int p_min, int p_max, int kvh, int chunk, bool wait_here, bool release_here,
+                                             __nv_bfloat16* ring) {
     constexpr int LDS = D + 8;
     constexpr int C = 8 * NBH;                      // (token, head) columns per block
     constexpr int KP = D / 32;                      // 32-element groups of the head size
     constexpr int MT = D / 16;                      // 16-row tiles of O^T
     constexpr int CH = D / 8;
     constexpr int THREADS = NW * 32;
-    static_assert(D % 32 == 0, "the transposed decode kernel needs head sizes in steps of 32");
-
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [NW][ST][16][LDS]  (V only)
-    __shared__ int sh_tile[4];
-
-    // What the kernel before this one writes are q and the new tokens' cache rows.  Lengths, splits and block
-    // tables come from the step's staging copy, so the block finds its work and asks for its first keys to be
-    // brought into L2 while that kernel still runs, and waits for it only then.
-    pdl_launch_dependents();
     const int G = p.n_q / p.n_kv;
     const int Gc = G <= C ? G : C;
-    const int n_chunks = G <= C ? 1 : (G + C - 1) / C;
     const int QT = G <= C ? C / G : 1;
-    int tile_idx, by;
-    block_place(p, tile_idx, by);
-    const int kvh = by / n_chunks;
-    const int chunk = by - kvh * n_chunks;
-
-    TileInfo ti;
-    if (!find_tile(p, QT, ti, sh_tile, tile_idx, (int)gridDim.x)) return;
-    const int ns = p.nsplit ? min(max(p.nsplit[ti.req], 1), p.max_split) : 1;
-    const int split = blockIdx.z;
-    if (split >= ns) return;
-
-    int p_min, p_max, kt_begin, kt_end;
-    key_tile_range(p, ti, MMA_KT, split, ns, p_min, p_max, kt_begin, kt_end);
-    const int u_begin = kt_begin * (MMA_KT / DEC_WT);
-    const int u_end = min(kt_end * (MMA_KT / DEC_WT), p_max / DEC_WT + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -823,8 +807,10 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
         const int pg = unit_page(i);
         prefetch_k(i, __shfl_sync(0xffffffffu, pg, v_key));
     }
-    pdl_wait();
-    pdl_after_wait();
+    if (wait_here) {
+        pdl_wait();
+        pdl_after_wait();
+    }
 
     // Q as B operand: lane (g, t) holds Q[column nb*8 + g][32 j + 8 t .. + 7]
     uint4 qf[NBH][KP];
@@ -953,7 +939,7 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
         }
         __syncwarp();
     }
-    pdl_late();
+    if (release_here) pdl_late();
     cp_async_wait<0>();
 
     // column sums over the 8 lanes that share a column pair
@@ -1018,6 +1004,91 @@ __global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_
             p.part_o[prow * D + col] = acc;
             if (col == 0) { p.part_ml[prow * 2] = M; p.part_ml[prow * 2 + 1] = L; }
         }
+    }
+}
+
+template <int D, int NW, int ST, int NBH>
+__global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_decode_t_kernel(const AttnParams p) {
+    constexpr int C = 8 * NBH;
+    static_assert(D % 32 == 0, "the transposed decode kernel needs head sizes in steps of 32");
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [NW][ST][16][LDS]  (V only)
+    __shared__ int sh_tile[4];
+
+    // What the kernel before this one writes are q and the new tokens' cache rows.  Lengths, splits and block
+    // tables come from the step's staging copy, so the block finds its work and asks for its first keys to be
+    // brought into L2 while that kernel still runs, and waits for it only then.
+    pdl_launch_dependents();
+    const int G = p.n_q / p.n_kv;
+    const int n_chunks = G <= C ? 1 : (G + C - 1) / C;
+    const int QT = G <= C ? C / G : 1;
+    int tile_idx, by;
+    block_place(p, tile_idx, by);
+    const int kvh = by / n_chunks;
+    const int chunk = by - kvh * n_chunks;
+
+    TileInfo ti;
+    if (!find_tile(p, QT, ti, sh_tile, tile_idx, (int)gridDim.x)) return;
+    const int ns = p.nsplit ? min(max(p.nsplit[ti.req], 1), p.max_split) : 1;
+    const int split = blockIdx.z;
+    if (split >= ns) return;
+
+    int p_min, p_max, kt_begin, kt_end;
+    key_tile_range(p, ti, MMA_KT, split, ns, p_min, p_max, kt_begin, kt_end);
+    const int u_begin = kt_begin * (MMA_KT / DEC_WT);
+    const int u_end = min(kt_end * (MMA_KT / DEC_WT), p_max / DEC_WT + 1);
+    decode_t_run<D, NW, ST, NBH>(p, ti, ns, split, u_begin, u_end, p_min, p_max, kvh, chunk, true, true, ring);
+}
+
+// The same arithmetic for a decode step (one token a request) with the keys of all requests dealt out evenly: the launch
+// has a fixed number of blocks per kv head, block j takes units [start[j], start[j + 1]) of the requests' units laid end
+// to end, whatever requests they belong to.  A request that several blocks share is merged by attn_combine_kernel from
+// its pieces (piece = block index - first block of the request); one that lies within a block is written out at once.
+// The host deals the units out (engine/step.py: plan_even_cut); this kernel only reads the result.
+template <int D, int NW, int ST, int NBH>
+__global__ void __launch_bounds__(NW * 32, (NBH == 1 && D <= 128) ? 4 : 2) attn_decode_even_kernel(const AttnParams p) {
+    constexpr int C = 8 * NBH;
+    static_assert(D % 32 == 0, "the transposed decode kernel needs head sizes in steps of 32");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+
+    pdl_launch_dependents();
+    const int G = p.n_q / p.n_kv;
+    const int n_chunks = G <= C ? 1 : (G + C - 1) / C;
+    const int kvh = blockIdx.y / n_chunks;
+    const int chunk = blockIdx.y - kvh * n_chunks;
+    const int j = blockIdx.x;
+    const int NB = p.even_nb;
+    if (j >= NB || j >= p.even[0]) return;
+    const int* blk_start = p.even + 1;
+    const int* blk_req = blk_start + NB + 1;
+    const int* req_start = blk_req + NB;
+    const int* req_first_blk = req_start + p.B + 1;
+    int lo = blk_start[j];
+    const int hi = blk_start[j + 1];
+    int r = blk_req[j];
+    bool first = true;
+    while (lo < hi && r >= 0 && r < p.B) {
+        const int c0 = req_start[r], c1 = req_start[r + 1];
+        if (c1 <= lo || c0 > lo) { ++r; continue; }          // never with a well-formed cut; keeps the walk inside the arrays
+        const int seg_hi = min(hi, c1);
+        TileInfo ti;
+        ti.req = r; ti.t0 = 0; ti.n_tok = 1; ti.q_len = 1; ti.kv_len = p.kv_len[r]; ti.q_base = p.q_start[r];
+        const int pos = ti.kv_len - 1;
+        const int k_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const int first_unit = k_lo / DEC_WT;
+        const int ns = p.nsplit ? min(max(p.nsplit[r], 1), p.max_split) : 1;
+        const int piece = j - req_first_blk[r];
+        const bool last = seg_hi >= hi;
+        if (piece >= 0 && piece < ns) {
+            if (!first) __syncthreads();       // the reduction of the run before this one has left the ring
+            decode_t_run<D, NW, ST, NBH>(p, ti, ns, piece, first_unit + (lo - c0), min(first_unit + (seg_hi - c0), pos / DEC_WT + 1),
+                                         pos, pos, kvh, chunk, first, last, ring);
+            first = false;
+        }
+        lo = seg_hi;
+        ++r;
     }
 }
 
@@ -1209,6 +1280,9 @@ MSGL_API int msgl_attention_decode_tile_tokens(int G) {
 }
 
 // how many blocks of the decode kernel fit one SM, for the host's choice of kv splits
+// 1 if the decode launch of this library can take an even cut (msgl_attention's `even`) for G q heads per kv head
+MSGL_API int msgl_attention_decode_even_ok(int G) { return (MSGL_HEAD_DIM % 32 == 0 && G <= 16) ? 1 : 0; }
+
 MSGL_API int msgl_attention_decode_blocks_per_sm(int G) {
     size_t smem;
     int reg_limit;
@@ -1239,13 +1313,15 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
                             const int* kv_len, const int* block_table, const int* nsplit, float* part_o,
                             float* part_ml, int B, int T_, int n_q, int n_kv, int d, int page_size, int bt_stride,
                             int window, int max_split, float scale, int qlen_min, int qlen_max, int uniform_decode,
-                            int variant, int grid_x, int dtype, const int* order, cudaStream_t stream) {
+                            int variant, int grid_x, int dtype, const int* order, const int* even, int even_nb,
+                            cudaStream_t stream) {
     if (grid_x <= 0 || B <= 0) return MSGL_OK;
     if (n_kv <= 0 || n_q % n_kv != 0 || d <= 0 || page_size <= 0 || max_split < 1) return MSGL_ERR_SIZE;
     if (max_split > 1 && (part_o == nullptr || part_ml == nullptr || nsplit == nullptr)) return MSGL_ERR_SIZE;
     AttnParams p;
     p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len;
-    p.block_table = block_table; p.nsplit = nsplit; p.order = order; p.part_o = part_o; p.part_ml = part_ml;
+    p.block_table = block_table; p.nsplit = nsplit; p.order = order; p.even = nullptr; p.even_nb = 0;
+    p.part_o = part_o; p.part_ml = part_ml;
     p.B = B; p.T = T_; p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.page_size = page_size; p.bt_stride = bt_stride;
     p.window = window; p.max_split = max_split;
     p.page_shift = -1;
@@ -1255,6 +1331,8 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
     const int R = variant == 1 ? 64 : 16;
     const int n_chunks = G <= R ? 1 : (G + R - 1) / R;
     dim3 grid(grid_x, n_kv * n_chunks, max_split);
+    // an even cut is read by the transposed decode kernel only (nsplit then counts a request's pieces, not equal splits)
+    if (even != nullptr && !(variant == 2 && MSGL_HEAD_DIM % 32 == 0 && G <= 16 && dtype == MSGL_BF16)) return MSGL_ERR_SIZE;
     if (variant == 0) {
         if (d > 512) return MSGL_ERR_SIZE;
         const size_t smem = simt_smem_bytes(d);
@@ -1302,7 +1380,18 @@ MSGL_API int msgl_attention(const void* q, void* out, const void* k_cache, const
             if (attr_set.due()) {
                 cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 cudaFuncSetAttribute(attn_decode_t_kernel<DT, NW, ST, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                cudaFuncSetAttribute(attn_decode_even_kernel<DT, NW, ST, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                cudaFuncSetAttribute(attn_decode_even_kernel<DT, NW, ST, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 attr_set.mark();
+            }
+            if (even != nullptr) {
+                // the keys of a decode step dealt out evenly over even_nb blocks per kv head
+                if (!uniform_decode || even_nb < 1 || T_ != B) return MSGL_ERR_SIZE;
+                p.even = even; p.even_nb = even_nb;
+                grid = dim3(even_nb, n_kv, 1);
+                if (C == 8) msgl_launch_pdl(attn_decode_even_kernel<DT, NW, ST, 1>, grid, dim3(NW * 32), smem, stream, p);
+                else msgl_launch_pdl(attn_decode_even_kernel<DT, NW, ST, 2>, grid, dim3(NW * 32), smem, stream, p);
+                return msgl_check_launch();
             }
             if (C == 8) msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 1>, grid, dim3(NW * 32), smem, stream, p);
             else msgl_launch_pdl(attn_decode_t_kernel<DT, NW, ST, 2>, grid, dim3(NW * 32), smem, stream, p);
@@ -1339,7 +1428,8 @@ MSGL_API int msgl_attention_tc(const void* q, void* out, const void* k_cache, co
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return MSGL_ERR_ALIGN;
     AttnParams p;
     p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len;
-    p.block_table = block_table; p.nsplit = nullptr; p.order = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
+    p.block_table = block_table; p.nsplit = nullptr; p.order = nullptr; p.even = nullptr; p.even_nb = 0;
+    p.part_o = nullptr; p.part_ml = nullptr;
     p.B = B; p.T = T_; p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.page_size = page_size; p.bt_stride = bt_stride;
     p.window = window; p.max_split = 1;
     p.page_shift = -1;

@@ -39,7 +39,7 @@ MSGL_API int msgl_attention_decode_noalloc(const void* q, void* out, const void*
     const int variant = (dtype == MSGL_BF16 && d == MSGL_HEAD_DIM) ? 2 : 0;
     int rc = msgl_attention(q, out, k_cache, v_cache, q_start, kv_len, block_table, nsplit, part_o, part_ml, B, B, n_q,
                             n_kv, d, page_size, bt_stride, window, max_split, scale, 1, 1, /*uniform_decode=*/1, variant,
-                            /*grid_x=*/B, dtype, /*order=*/nullptr, stream);
+                            /*grid_x=*/B, dtype, /*order=*/nullptr, /*even=*/nullptr, 0, stream);
     if (rc != MSGL_OK) return rc;
     return msgl_attention_combine(part_o, part_ml, /*token_req=*/nullptr, nsplit, out, B, n_q, d, max_split, dtype, stream);
 }

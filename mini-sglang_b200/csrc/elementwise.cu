@@ -69,8 +69,11 @@ __global__ void decode_meta_kernel(const int* __restrict__ id, const int* __rest
                                    int page_size, int mp, int common, int* __restrict__ input_ids, int* __restrict__ positions,
                                    int* __restrict__ token_req, int* __restrict__ q_start, int* __restrict__ kv_len,
                                    int* __restrict__ slots, int* __restrict__ out_loc, int* __restrict__ nsplit,
-                                   int* __restrict__ block_table, int window, int* __restrict__ order) {
+                                   int* __restrict__ block_table, int window, int* __restrict__ order,
+                                   const int* __restrict__ even_in, int* __restrict__ even_out, int n_even) {
     const int r = blockIdx.x;
+    // the even cut of the step's keys comes ready-made from the host: the blocks copy it between them
+    for (int i = r * blockDim.x + threadIdx.x; i < n_even; i += b * blockDim.x) even_out[i] = even_in[i];
     const bool live = r < B;
     const int sl = live ? slot[r] : 0, ps = live ? pos[r] : 0;
     const int* row = table + (size_t)sl * row_stride;
@@ -122,12 +125,13 @@ MSGL_API int msgl_table_delta(const int* deltas, int n_records, int* table, int 
 MSGL_API int msgl_decode_meta(const int* id, const int* slot, const int* pos, const int* nsplit_in, int B, int b, const int* table,
                               int row_stride, int page_size, int mp, int common, int* input_ids, int* positions, int* token_req,
                               int* q_start, int* kv_len, int* slots, int* out_loc, int* nsplit, int* block_table,
-                              int window, int* order, cudaStream_t stream) {
+                              int window, int* order, const int* even_in, int* even_out, int n_even, cudaStream_t stream) {
     if (b <= 0) return MSGL_OK;
     if (B < 0 || B > b || page_size < 1 || mp < 1 || row_stride < 1 || order == nullptr) return MSGL_ERR_SIZE;
+    if (n_even < 0 || (n_even > 0 && (even_in == nullptr || even_out == nullptr))) return MSGL_ERR_SIZE;
     decode_meta_kernel<<<b, 128, 0, stream>>>(id, slot, pos, nsplit_in, B, b, table, row_stride, page_size, mp, common, input_ids,
                                              positions, token_req, q_start, kv_len, slots, out_loc, nsplit, block_table,
-                                             window, order);
+                                             window, order, even_in, even_out, n_even);
     return msgl_check_launch();
 }
 

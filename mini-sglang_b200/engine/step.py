@@ -36,6 +36,10 @@ MAX_KV_SPLIT = 32                 # more than MANY_SPLITS pieces only where they
 MANY_SPLITS, MANY_SPLITS_MIN_KEYS = 16, 512      # one request of 32k keys: 16 pieces 4.54, 32 pieces 4.29 ms a step; of 4k keys: 3.37 / 3.44
 MIN_KEYS_PER_SPLIT = 128          # 64 / 128 / 256 / 512 measured at 1 to 8 requests of 1k to 4k keys: 128 best or level (batch 1, 4,096 keys: 3.46 against 3.54 ms with 256)
 MIN_KEYS_PER_PIECE = 256          # shortest piece when a single long request is cut up among many short ones
+EVEN_MIN_UNITS = 16               # an even cut gives no block fewer than this many units of 16 keys (256 keys, as the pieces above)
+EVEN_SNAP_UNITS = 4               # a cut this close to a request's edge moves onto it: a run of a few units costs more than it evens out
+EVEN_FROM_UNITS = 64              # a decode step takes the even cut from this many units (1,024 keys) a request on in the mean ...
+EVEN_UNEVEN = 1.25                # ... if its longest request has this many times the mean or more
 LONG_REQUEST_FACTOR = 1.5         # a request beyond this many times the mean load per block is cut up (1.0, 1.25, 1.5 measured: 1.5 best)
 BALANCE_MIN_KEYS = 6144           # mean keys a request from which halving every request to even out the SMs pays
 WIDE_KV_SPLIT = 8                 # cap of the decode graphs that are captured for batches with such requests
@@ -55,8 +59,9 @@ def _align4(n: int) -> int:
 class _Layout:
     """Offsets of the fields inside the int32 staging buffer of a step."""
 
-    def __init__(self, T: int, B: int, W: int, max_pages: Sequence[int]):
+    def __init__(self, T: int, B: int, W: int, max_pages: Sequence[int], even_nb: Optional[Sequence[int]] = None):
         self.T, self.B, self.W, self.max_pages = T, B, W, list(max_pages)
+        self.even_nb = list(even_nb) if even_nb is not None else [0] * len(self.max_pages)      # 0: no even cut for the group
         off = 0
 
         def take(n):
@@ -67,11 +72,12 @@ class _Layout:
 
         self.input_ids, self.positions, self.token_req = take(T), take(T), take(T)
         self.q_start, self.kv_len, self.slots, self.want = take(B + 1), take(B), take(B), take(W)
-        self.out_loc, self.nsplit, self.order, self.table = [], [], [], []
-        for mp in max_pages:
+        self.out_loc, self.nsplit, self.order, self.even, self.table = [], [], [], [], []
+        for mp, nb in zip(max_pages, self.even_nb):
             self.out_loc.append(take(T))
             self.nsplit.append(take(B))
             self.order.append(take(B))
+            self.even.append(take(ops.even_cut_size(B, nb) if nb else 0))
             self.table.append(take(B * mp))
         self.size = off
 
@@ -185,6 +191,62 @@ def plan_kv_splits(q_lens: Sequence[int], kv_lens: Sequence[int], *, n_kv: int, 
     return out
 
 
+def plan_even_cut(kv_lens: Sequence[int], window: Optional[int], n_blocks: int, max_pieces: int):
+    """The keys of a decode step (one new token a request) dealt out evenly over the blocks of one kv head.
+
+    The requests' units of DECODE_UNIT_KEYS keys (from the first unit a window still reaches to the unit of the newest
+    key) are laid end to end and cut into at most `n_blocks` runs of equal length; a cut that falls within
+    EVEN_SNAP_UNITS of a request's edge moves onto it.  No run is shorter than EVEN_MIN_UNITS unless the whole step is,
+    and no request lies in more than `max_pieces` runs (fewer blocks are used if it would).
+
+    -> (blocks in use n, start unit of every block [n + 1], first request of every block [n], first unit of every
+    request [B + 1], first block of every request [B], pieces of every request [B]); int32 arrays."""
+    pos = np.asarray(kv_lens, dtype=np.int64) - 1
+    k_lo = np.maximum(pos - window + 1, 0) if window else np.zeros_like(pos)
+    units = pos // DECODE_UNIT_KEYS - k_lo // DECODE_UNIT_KEYS + 1
+    B = len(units)
+    cum = np.zeros(B + 1, dtype=np.int64)
+    np.cumsum(units, out=cum[1:])
+    U = int(cum[-1])
+    n = max(1, min(n_blocks, U // EVEN_MIN_UNITS))
+    while True:
+        raw = (np.arange(n + 1, dtype=np.int64) * U) // n
+        snap = min(EVEN_SNAP_UNITS, (U // n) // 4)
+        idx = np.clip(np.searchsorted(cum, raw, side="right") - 1, 0, B - 1)          # the request a cut falls into
+        below, above = raw - cum[idx], cum[idx + 1] - raw
+        start = np.where(below <= snap, cum[idx], np.where(above <= snap, cum[idx + 1], raw))
+        start[0], start[n] = 0, U
+        first_blk = np.searchsorted(start, cum[:-1], side="right") - 1                  # the run that holds a request's first unit
+        last_blk = np.searchsorted(start, cum[1:], side="left") - 1                     # ... and its last
+        pieces = last_blk - first_blk + 1
+        most = int(pieces.max())
+        if most <= max_pieces or n == 1:
+            break
+        n = max(1, min(n - 1, n * max_pieces // most))
+    blk_req = np.searchsorted(cum, start[:-1], side="right") - 1
+    i32 = lambda a: np.asarray(a, dtype=np.int32)
+    return n, i32(start), i32(blk_req), i32(cum), i32(first_blk), i32(pieces)
+
+
+def pack_even_cut(cut, B: int, n_blocks: int) -> np.ndarray:
+    """The result of plan_even_cut as the words the attention launch reads (ops.even_cut_size(B, n_blocks) of them): B
+    and n_blocks are the sizes the launch was captured with, at least the cut's own."""
+    n, start, blk_req, cum, first_blk, _ = cut
+    out = np.zeros(ops.even_cut_size(B, n_blocks), dtype=np.int32)
+    out[0] = n
+    o = 1
+    out[o:o + n + 1] = start
+    out[o + n + 1:o + n_blocks + 1] = start[n]
+    o += n_blocks + 1
+    out[o:o + n] = blk_req
+    o += n_blocks
+    out[o:o + len(cum)] = cum
+    out[o + len(cum):o + B + 1] = cum[-1]
+    o += B + 1
+    out[o:o + len(first_blk)] = first_blk
+    return out
+
+
 def decode_order(kv_lens, nsplits, window: Optional[int], b: int) -> np.ndarray:
     """The rows of a decode batch in the order in which the attention launch takes them: by falling number of keys
     per kv split (blocks go to the SMs in index order, so the longest start first and the shortest fill the end);
@@ -266,6 +328,16 @@ class ModelRunner:
             qt = ops.attention_tile_tokens(ops.VARIANT_MMA_DECODE, G, need.head_dim) if ops.mma_supported(need.head_dim, self.dtype) \
                 else ops.attention_tile_tokens(ops.VARIANT_SIMT, G)
             self._group_geom.append((need.n_kv_heads, G, ops.decode_blocks_per_sm(need.head_dim, self.dtype, G), qt))
+        # blocks per kv head of a decode launch with an even cut of the keys: what the SMs hold at once; empty unless the
+        # decode kernel of every group takes such a cut
+        self._even_nb: List[int] = []
+        if self.dtype == torch.bfloat16 and self.mgr.groups:
+            ok = True
+            for g, (n_kv, G, per_sm, _) in zip(self.mgr.groups, self._group_geom):
+                head_dim = needs[g.cache_ids[0]].head_dim
+                ok = ok and ops.decode_even_ok(head_dim, self.dtype, G) and self.sm_count * per_sm >= n_kv
+            if ok:
+                self._even_nb = [max(1, self.sm_count * per_sm // n_kv) for (n_kv, G, per_sm, _) in self._group_geom]
 
     # -- device ------------------------------------------------------------------------------
     def _init_device(self, device: str) -> torch.device:
@@ -334,7 +406,7 @@ class ModelRunner:
                               warps=warps)
 
     def _fill(self, host: np.ndarray, lay: _Layout, entries: Sequence[StepEntry], starts: Sequence[int],
-              want_rows: Sequence[int], nsplits: Sequence[Sequence[int]], pad_to: int = 0) -> None:
+              want_rows: Sequence[int], nsplits: Sequence[Sequence[int]], pad_to: int = 0, even_cuts=None) -> None:
         """Write every field of the staging buffer.  Rows beyond len(entries) (graph padding) are
         single tokens of a request of length 1 on the dump page."""
         T, B = lay.T, lay.B
@@ -358,6 +430,9 @@ class ModelRunner:
                 host[lay.out_loc[gi]: lay.out_loc[gi] + n_ent] = g.table[slots, pos // P].astype(np.int64) * P + pos % P
                 host[lay.nsplit[gi]: lay.nsplit[gi] + n_ent] = nsplits[gi]
                 host[lay.order[gi]: lay.order[gi] + B] = decode_order(pos + 1, nsplits[gi], g.window, B)
+                if lay.even_nb[gi] and even_cuts is not None:
+                    words = pack_even_cut(even_cuts[gi], B, lay.even_nb[gi])
+                    host[lay.even[gi]: lay.even[gi] + len(words)] = words
                 width = min(mp, g.table.shape[1])
                 host[lay.table[gi]: lay.table[gi] + n_ent * mp].reshape(n_ent, mp)[:, :width] = g.table[slots, :width]
             t = n_ent
@@ -401,7 +476,9 @@ class ModelRunner:
                                        nsplit=v(lay.nsplit[gi], lay.B) if max_splits[gi] > 1 else None,
                                        max_split=max_splits[gi], window=g.window,
                                        host_nsplit=nsplits[gi] if nsplits is not None else None,
-                                       order=v(lay.order[gi], lay.B) if uniform else None))
+                                       order=v(lay.order[gi], lay.B) if uniform else None,
+                                       even=v(lay.even[gi], ops.even_cut_size(lay.B, lay.even_nb[gi])) if uniform and lay.even_nb[gi] else None,
+                                       even_nb=lay.even_nb[gi] if uniform else 0))
         return StepContext(T=lay.T, B=lay.B, page_size=self.page_size, input_ids=v(lay.input_ids, lay.T),
                            positions=v(lay.positions, lay.T), q_start=v(lay.q_start, lay.B + 1),
                            kv_len=v(lay.kv_len, lay.B), token_req=v(lay.token_req, lay.T), slots=v(lay.slots, lay.B),
@@ -536,23 +613,36 @@ class ModelRunner:
         room = [self._graph_max_split(gi, b) for gi in range(len(self.mgr.groups))]
         narrow = [min(c, MANY_SPLITS) for c in room]
         fused = self._fused_blocks(b)
-        nsplits = [self._plan_splits(gi, q_lens, kv_lens, room[gi], max(narrow[gi], WIDE_KV_SPLIT), fused_blocks=fused)
-                   for gi in range(len(self.mgr.groups))]
-        # blocks of pieces that a request does not have leave at once, but they are launched: a graph with the split
-        # dimension of long contexts (up to MAX_KV_SPLIT) is kept apart from the one that every other step replays
-        wide = any(max(ns) > cap for ns, cap in zip(nsplits, narrow))
-        key = (b, mp, wide)
-        gr = self._graphs.get(key)
-        if gr is None:
-            gr = self._capture(b, mp, [max(c, r, WIDE_KV_SPLIT) for c, r in zip(narrow, room)] if wide else narrow)
-            self._graphs[key] = gr
-        self.last_plan = {"graph_key": key, "nsplits": nsplits, "max_split": list(gr.max_split)}
+        even_cuts = None
+        if not fused and self._even_nb and self._wants_even_cut(kv_lens):
+            # long contexts: the keys of all requests dealt out evenly over as many blocks as the SMs hold at once
+            pieces = [min(MAX_KV_SPLIT, nb) for nb in self._even_nb]
+            even_cuts = [plan_even_cut(kv_lens, g.window, nb, mx) for g, nb, mx in zip(self.mgr.groups, self._even_nb, pieces)]
+            nsplits = [c[5].tolist() for c in even_cuts]
+            key = (b, mp, "even")
+            gr = self._graphs.get(key)
+            if gr is None:
+                gr = self._capture(b, mp, pieces, even_nb=self._even_nb)
+                self._graphs[key] = gr
+        else:
+            nsplits = [self._plan_splits(gi, q_lens, kv_lens, room[gi], max(narrow[gi], WIDE_KV_SPLIT), fused_blocks=fused)
+                       for gi in range(len(self.mgr.groups))]
+            # blocks of pieces that a request does not have leave at once, but they are launched: a graph with the split
+            # dimension of long contexts (up to MAX_KV_SPLIT) is kept apart from the one that every other step replays
+            wide = any(max(ns) > cap for ns, cap in zip(nsplits, narrow))
+            key = (b, mp, wide)
+            gr = self._graphs.get(key)
+            if gr is None:
+                gr = self._capture(b, mp, [max(c, r, WIDE_KV_SPLIT) for c, r in zip(narrow, room)] if wide else narrow)
+                self._graphs[key] = gr
+        self.last_plan = {"graph_key": key, "nsplits": nsplits, "max_split": list(gr.max_split),
+                          "even_blocks": [c[0] for c in even_cuts] if even_cuts else None}
         lay = gr.layout
         if self.device_meta:
-            self._meta_on_device(gr, entries, starts, nsplits, b)
+            self._meta_on_device(gr, entries, starts, nsplits, b, even_cuts)
         else:
             host, idx = self._pinned_buffer(lay.size)
-            self._fill(host.numpy(), lay, entries, starts, list(range(b)), nsplits)
+            self._fill(host.numpy(), lay, entries, starts, list(range(b)), nsplits, even_cuts=even_cuts)
             gr.dev.copy_(host[:lay.size], non_blocking=True)
             self._mark(idx)
             self.last_h2d_bytes = 4 * lay.size
@@ -562,7 +652,22 @@ class ModelRunner:
         ops.LAUNCHES += gr.n_kernels
         return gr.logits[:B]
 
-    def _meta_on_device(self, gr: "_Graph", entries, starts, nsplits, b: int) -> None:
+    def _wants_even_cut(self, kv_lens: Sequence[int]) -> bool:
+        """Whether a decode step deals its keys out evenly (plan_even_cut) instead of cutting every request by itself:
+        when the requests' lengths differ (the longest EVEN_UNEVEN times the mean or more) and a request has
+        EVEN_FROM_UNITS units or more in the mean.  Requests of like length fill the SMs as well cut one by one, with
+        fewer runs and pieces; below that mean a run of keys is so short that the fixed cost of the runs a block strings
+        together outweighs what the even load gains."""
+        if os.environ.get("MSGL_EVEN_CUT", "1") == "0":
+            return False
+        for g in self.mgr.groups:
+            units = [-(-(min(k, g.window + 1) if g.window else k) // DECODE_UNIT_KEYS) for k in kv_lens]
+            mean = sum(units) / len(units)
+            if mean >= EVEN_FROM_UNITS and max(units) >= EVEN_UNEVEN * mean:
+                return True
+        return False
+
+    def _meta_on_device(self, gr: "_Graph", entries, starts, nsplits, b: int, even_cuts=None) -> None:
         """The fields of a decode step that the captured graph reads, made on the device.  The host sends one small
         buffer: token id, slot and position of every request, its kv splits per cache group, and per group the table
         rows of the requests whose pages changed since the last such step (whole rows; a request gets a page every
@@ -570,7 +675,8 @@ class ModelRunner:
         lay, B, G = gr.layout, len(entries), len(self.mgr.groups)
         rows = [self.mgr.take_dirty_rows(gi) for gi in range(G)]
         n_delta = [1 + 3 * len(r) + sum(len(t) for _, t in r) for r in rows]
-        size = (3 + G) * B + sum(_align4(n) for n in n_delta)
+        n_even = [ops.even_cut_size(b, nb) if (nb and even_cuts is not None) else 0 for nb in lay.even_nb]
+        size = (3 + G) * B + sum(_align4(n) for n in n_delta) + sum(_align4(n) for n in n_even)
         host_t, idx = self._pinned_buffer(size)
         host = host_t.numpy()
         host[0:B] = [e.tokens[0] for e in entries]
@@ -593,6 +699,12 @@ class ModelRunner:
                 host[at:at + len(table_row)] = table_row
                 at += len(table_row)
             off += _align4(n_delta[gi])
+        e_off = []
+        for gi in range(G):
+            e_off.append(off)
+            if n_even[gi]:
+                host[off:off + n_even[gi]] = pack_even_cut(even_cuts[gi], b, lay.even_nb[gi])
+            off += _align4(n_even[gi])
         if self._dev_compact is None or self._dev_compact.numel() < size:
             self._dev_compact = torch.empty(max(size, 1 << 14), dtype=torch.int32, device=self.device)
         dev = self._dev_compact
@@ -609,11 +721,13 @@ class ModelRunner:
                             input_ids=g0[lay.input_ids:], positions=g0[lay.positions:], token_req=g0[lay.token_req:],
                             q_start=g0[lay.q_start:], kv_len=g0[lay.kv_len:], slots=g0[lay.slots:],
                             out_loc=g0[lay.out_loc[gi]:], nsplit=g0[lay.nsplit[gi]:], block_table=g0[lay.table[gi]:],
-                            order=g0[lay.order[gi]:], window=int(self.mgr.groups[gi].window or 0))
+                            order=g0[lay.order[gi]:], window=int(self.mgr.groups[gi].window or 0),
+                            even_in=dev[e_off[gi]: e_off[gi] + n_even[gi]] if n_even[gi] else None,
+                            even_out=g0[lay.even[gi]:] if n_even[gi] else None)
 
-    def _capture(self, b: int, mp: Tuple[int, ...], max_split: Sequence[int]) -> _Graph:
+    def _capture(self, b: int, mp: Tuple[int, ...], max_split: Sequence[int], even_nb: Optional[Sequence[int]] = None) -> _Graph:
         gr = _Graph()
-        lay = _Layout(b, b, b, mp)
+        lay = _Layout(b, b, b, mp, even_nb)
         gr.layout = lay
         gr.dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
         gr.max_split = list(max_split)

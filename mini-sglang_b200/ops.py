@@ -79,7 +79,8 @@ def _lib():
         lib.msgl_embedding.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.msgl_resolve_ids.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.msgl_table_delta.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p]
-        lib.msgl_decode_meta.argtypes = [c_void_p] * 4 + [c_int, c_int, c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 9 + [c_int, c_void_p, c_void_p]
+        lib.msgl_decode_meta.argtypes = [c_void_p] * 4 + [c_int, c_int, c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 9 + [c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                         c_void_p]
         lib.msgl_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p,
                                      c_int, c_int, c_int, c_void_p]
         lib.msgl_qknorm_rope_kvwrite.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -107,7 +108,7 @@ def _attn_lib(head_dim: int):
     lib = _attn.get(hd)
     if lib is None:
         lib = _build.attention_library(hd)
-        lib.msgl_attention.argtypes = [c_void_p] * 10 + [c_int] * 9 + [c_float] + [c_int] * 6 + [c_void_p, c_void_p]
+        lib.msgl_attention.argtypes = [c_void_p] * 10 + [c_int] * 9 + [c_float] + [c_int] * 6 + [c_void_p, c_void_p, c_int, c_void_p]
         lib.msgl_attention_combine.argtypes = [c_void_p] * 5 + [c_int] * 5 + [c_void_p]
         lib.msgl_attention_tc.argtypes = [c_void_p] * 7 + [c_int] * 8 + [c_float] + [c_int] * 5 + [c_void_p, c_void_p]
         lib.msgl_attention_head_dim.restype = c_int
@@ -152,15 +153,17 @@ def table_delta(deltas: torch.Tensor, n_records: int, table: torch.Tensor) -> No
 
 def decode_meta(ids: torch.Tensor, slots_in: torch.Tensor, pos: torch.Tensor, nsplit_in: torch.Tensor, B: int, b: int,
                 table: torch.Tensor, page_size: int, mp: int, common: bool, *, input_ids, positions, token_req, q_start, kv_len,
-                slots, out_loc, nsplit, block_table, order, window: int = 0) -> None:
+                slots, out_loc, nsplit, block_table, order, window: int = 0, even_in: Optional[torch.Tensor] = None,
+                even_out: Optional[torch.Tensor] = None) -> None:
     """The step fields of a decode batch of B requests (captured size b) written on the device from (token id, slot,
     position) per request and the device copy of the block tables; see csrc/elementwise.cu.  `order` receives the rows
-    by falling number of keys per kv split (what the attention launch walks first)."""
+    by falling number of keys per kv split (what the attention launch walks first); `even_in` (the even cut of the step's
+    keys, made by the host) is copied to `even_out` as it is."""
     _need_cuda(ids, slots_in, pos, nsplit_in, table, input_ids, block_table)
     code = _lib().msgl_decode_meta(_ptr(ids), _ptr(slots_in), _ptr(pos), _ptr(nsplit_in), B, b, _ptr(table), table.shape[1], page_size,
                                    mp, int(common), _ptr(input_ids), _ptr(positions), _ptr(token_req), _ptr(q_start), _ptr(kv_len),
                                    _ptr(slots), _ptr(out_loc), _ptr(nsplit), _ptr(block_table), int(window), _ptr(order),
-                                   _stream())
+                                   _ptr(even_in), _ptr(even_out), even_in.numel() if even_in is not None else 0, _stream())
     _check(code, "decode_meta")
 
 
@@ -411,6 +414,22 @@ def decode_blocks_per_sm(head_dim: int, dtype: torch.dtype, group: int = 1) -> i
     return int(lib.msgl_attention_decode_blocks_per_sm(int(group)))
 
 
+def even_cut_size(B: int, n_blocks: int) -> int:
+    """int32 words of the even cut of a decode step of B requests over n_blocks blocks per kv head: blocks in use, start
+    unit of every block [n_blocks + 1], first request of every block [n_blocks], first unit of every request [B + 1], first
+    block of every request [B]."""
+    return 1 + (n_blocks + 1) + n_blocks + (B + 1) + B
+
+
+def decode_even_ok(head_dim: int, dtype: torch.dtype, group: int = 1) -> bool:
+    """Whether the decode attention launch for this head size takes an even cut of the keys (`attention(even=...)`)."""
+    if not mma_supported(head_dim, dtype):
+        return False
+    lib = _attn_lib(head_dim)
+    lib.msgl_attention_decode_even_ok.restype = c_int
+    return bool(lib.msgl_attention_decode_even_ok(int(group)))
+
+
 def mma_supported(head_dim: int, dtype: torch.dtype) -> bool:
     return dtype == torch.bfloat16 and head_dim in _build.MMA_HEAD_DIMS
 
@@ -419,23 +438,27 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
               q_start: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor,
               nsplit: Optional[torch.Tensor], part_o: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
               n_kv: int, page_size: int, window: int, max_split: int, scale: float, qlen_min: int, qlen_max: int,
-              uniform_decode: bool, variant: int, grid_x: int, order: Optional[torch.Tensor] = None) -> None:
+              uniform_decode: bool, variant: int, grid_x: int, order: Optional[torch.Tensor] = None,
+              even: Optional[torch.Tensor] = None, even_nb: int = 0) -> None:
     """One launch of the paged attention kernel over the requests whose q_len lies in
     [qlen_min, qlen_max]; see csrc/attention.cu for the meaning of every argument.  `order` (uniform decode only):
-    int32 [B], a permutation of the requests; the launch's i-th block along x takes request order[i]."""
-    _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table, nsplit, part_o, part_ml, order)
+    int32 [B], a permutation of the requests; the launch's i-th block along x takes request order[i].  `even`: the even cut
+    of a decode step's keys over `even_nb` blocks per kv head (engine/step.py: plan_even_cut) in place of `grid_x` blocks."""
+    _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table, nsplit, part_o, part_ml, order, even)
     T, n_q, d = q.shape
     B = kv_len.numel()
     assert q.is_contiguous() and out.is_contiguous() and block_table.dim() == 2 and block_table.stride(1) == 1
     assert q_start.numel() == B + 1 and block_table.shape[0] == B and out.shape == q.shape
     assert nsplit is None or nsplit.numel() == B
     assert order is None or (uniform_decode and order.numel() == B and order.dtype == torch.int32)
+    assert even is None or (uniform_decode and variant == VARIANT_MMA_DECODE and even.dtype == torch.int32 and
+                            even.numel() >= even_cut_size(B, even_nb) and even_nb >= 1)
     if max_split > 1:
         assert part_o.numel() >= max_split * T * n_q * d and part_ml.numel() >= max_split * T * n_q * 2
     code = _attn_lib(d).msgl_attention(
         _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table),
         _ptr(nsplit), _ptr(part_o), _ptr(part_ml), B, T, n_q, n_kv, d, page_size, block_table.stride(0), window,
-        max_split, float(scale), qlen_min, qlen_max, int(uniform_decode), variant, grid_x, _dt(q), _ptr(order), _stream())
+        max_split, float(scale), qlen_min, qlen_max, int(uniform_decode), variant, grid_x, _dt(q), _ptr(order), _ptr(even), int(even_nb), _stream())
     _check(code, f"attention (head size {d}, variant {variant})")
 
 

@@ -123,7 +123,7 @@ class PagedAttention(Mixer):
             qt_row = ops.attention_tile_tokens(ops.VARIANT_MMA_ROWS, G)
             if ctx.uniform_decode:
                 ops.attention(q, out, cache.k, cache.v, qlen_min=1, qlen_max=1, variant=ops.VARIANT_MMA_DECODE,
-                              grid_x=ctx.B, **common)
+                              grid_x=ctx.B, even=g.even, even_nb=g.even_nb, **common)
             else:
                 n_dec = sum(1 for n in ctx.host_q_lens if n <= qt_dec)
                 n_row = sum(-(-n // qt_row) for n in ctx.host_q_lens if n > qt_dec)

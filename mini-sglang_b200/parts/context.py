@@ -23,6 +23,8 @@ class GroupContext:
     window: Optional[int]
     host_nsplit: Optional[Sequence[int]] = None     # the host's copy of nsplit (None: not known here)
     order: Optional[torch.Tensor] = None            # [B] int32, uniform decode only: the requests by falling number of keys
+    even: Optional[torch.Tensor] = None             # int32, uniform decode only: the keys dealt out evenly over even_nb blocks
+    even_nb: int = 0                                # per kv head (ops.even_cut_size words; nsplit then holds the pieces a request)
 
 
 @dataclasses.dataclass

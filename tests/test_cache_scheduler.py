@@ -494,6 +494,56 @@ def test_kv_split_plan():
     assert plan_kv_splits([1] * 16, [8192] * 16, cap=16, **wide) == [slots // (16 * 2 * 2)] * 16
 
 
+def walk_even_cut(cut, n_req):
+    """The runs of keys that the blocks of an even cut take, found the way the kernel finds them: per request the list of
+    (piece, first unit, end unit) in units of the request."""
+    n, start, blk_req, cum, first_blk, pieces = cut
+    runs = [[] for _ in range(n_req)]
+    for j in range(n):
+        lo, hi, r = int(start[j]), int(start[j + 1]), int(blk_req[j])
+        while lo < hi:
+            c0, c1 = int(cum[r]), int(cum[r + 1])
+            assert c0 <= lo < c1
+            end = min(hi, c1)
+            runs[r].append((j - int(first_blk[r]), lo - c0, end - c0))
+            lo, r = end, r + 1
+    return runs
+
+
+def test_even_cut_of_a_decode_step():
+    """Every unit of every request lies in exactly one run, the runs of a request are its pieces 0, 1, ... in order, no
+    request has more pieces than allowed, and the blocks' loads differ by little."""
+    from mini_sglang_b200.engine.step import EVEN_MIN_UNITS, EVEN_SNAP_UNITS, pack_even_cut, plan_even_cut
+    n, start, blk_req, cum, first_blk, pieces = plan_even_cut([4096] * 8, None, 74, 32)
+    assert n == 74 and cum[-1] == 8 * 256 and pieces.tolist() == [10] * 8
+    assert max(np.diff(start)) - min(np.diff(start)) <= 2 * EVEN_SNAP_UNITS + 1
+    n, start, *_ , pieces = plan_even_cut([32768], None, 74, 32)              # one request: as many pieces as allowed
+    assert n == 32 and pieces.tolist() == [32] and set(np.diff(start).tolist()) == {64}
+    n, *_, pieces = plan_even_cut([4096], None, 74, 32)                       # no run below EVEN_MIN_UNITS
+    assert n == 256 // EVEN_MIN_UNITS and pieces.tolist() == [n]
+    n, *_, pieces = plan_even_cut([5, 1, 30], None, 74, 32)                   # a step smaller than one run
+    assert n == 1 and pieces.tolist() == [1, 1, 1]
+    # a window bounds the units that count: 16 + 1 keys end in at most two units
+    n, start, blk_req, cum, *_ = plan_even_cut([1000, 5000], 17, 74, 32)
+    assert cum.tolist() == [0, 2, 4]
+    words = pack_even_cut(plan_even_cut([700, 4096, 50], None, 5, 8), 4, 8)   # captured for 4 requests and 8 blocks
+    assert words[0] == 5 and len(words) == 1 + 9 + 8 + 5 + 4 and words[1 + 5] == words[1 + 8] == 44 + 256 + 4
+    rnd = np.random.RandomState(5)
+    for _ in range(300):
+        B = int(rnd.randint(1, 130))
+        lens = rnd.randint(1, int(rnd.choice([40, 700, 5000, 40000])), B)
+        window = None if rnd.rand() < 0.7 else int(rnd.randint(1, 3000))
+        blocks, most = int(rnd.choice([1, 3, 18, 37, 74, 148])), int(rnd.choice([1, 2, 8, 32]))
+        cut = plan_even_cut(lens, window, blocks, most)
+        n, start, blk_req, cum, first_blk, pieces = cut
+        assert 1 <= n <= blocks and start[0] == 0 and start[n] == cum[-1] and (np.diff(start) > 0).all()
+        assert pieces.max() <= most or n == 1
+        for r, runs in enumerate(walk_even_cut(cut, B)):
+            assert [p for p, _, _ in runs] == list(range(int(pieces[r])))
+            assert runs[0][1] == 0 and runs[-1][2] == cum[r + 1] - cum[r]
+            assert all(a[2] == b[1] for a, b in zip(runs, runs[1:]))
+
+
 def test_order_of_a_decode_batch():
     """The attention launch of a decode step takes the requests by falling number of keys per kv split; rows of equal
     load keep their order, padding rows of a captured batch size come last."""

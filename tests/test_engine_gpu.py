@@ -197,6 +197,7 @@ def test_step_fields_made_on_the_device_equal_the_hosts(monkeypatch):
     a kernel that reads a device copy of the block tables, kept up to date by deltas.  Requests come, grow over page edges,
     end and are replaced, with so few pages that they are used again; before every replay the graph's buffer must hold
     exactly what the host's own filling of the same step gives."""
+    from mini_sglang_b200 import ops
     from mini_sglang_b200.engine.step import StepEntry
     name = "B"
     cfg = CONFIGS[name]
@@ -205,11 +206,11 @@ def test_step_fields_made_on_the_device_equal_the_hosts(monkeypatch):
     checked = []
     inner = runner._meta_on_device
 
-    def checking(gr, entries, starts, nsplits, b):
-        inner(gr, entries, starts, nsplits, b)
+    def checking(gr, entries, starts, nsplits, b, even_cuts=None):
+        inner(gr, entries, starts, nsplits, b, even_cuts)
         lay = gr.layout
         want = np.zeros(lay.size, dtype=np.int32)
-        runner._fill(want, lay, entries, starts, list(range(b)), nsplits, pad_to=b)
+        runner._fill(want, lay, entries, starts, list(range(b)), nsplits, pad_to=b, even_cuts=even_cuts)
         got = gr.dev.cpu().numpy()
         B = len(entries)
         for field, off, n in [("input_ids", lay.input_ids, b), ("positions", lay.positions, b), ("token_req", lay.token_req, b),
@@ -222,6 +223,8 @@ def test_step_fields_made_on_the_device_equal_the_hosts(monkeypatch):
             order = got[lay.order[gi]: lay.order[gi] + b]
             assert (order == want[lay.order[gi]: lay.order[gi] + b]).all(), (order, want[lay.order[gi]: lay.order[gi] + b])
             assert sorted(order.tolist()) == list(range(b))
+            n_even = ops.even_cut_size(b, lay.even_nb[gi]) if lay.even_nb[gi] else 0
+            assert (got[lay.even[gi]: lay.even[gi] + n_even] == want[lay.even[gi]: lay.even[gi] + n_even]).all()
             tg, tw = got[lay.table[gi]: lay.table[gi] + b * mp].reshape(b, mp), want[lay.table[gi]: lay.table[gi] + b * mp].reshape(b, mp)
             for r, e in enumerate(entries):                 # the pages a request holds; what lies beyond them is never read
                 n = int(g.n_pages[e.slot])
@@ -251,3 +254,80 @@ def test_step_fields_made_on_the_device_equal_the_hosts(monkeypatch):
     assert len(checked) > 25 and len(set(checked)) >= 3
     for s in live:
         runner.close(s)
+
+
+def test_even_cut_of_requests_of_mixed_lengths(monkeypatch):
+    """Decode steps whose requests hold 1,030 to 3,000 keys: the keys of all of them are dealt out evenly over the blocks
+    that the SMs hold (a block takes the end of one request and the start of the next; a request is merged from up to
+    32 pieces).  Requests end and others join, pages are used again, the fields of every step are made on the device and
+    compared with the host's.  bfloat16, two layers of a small width, every decoded row against the plain implementation."""
+    import plain_qwen3 as P
+    from helpers import assert_row_close
+    from mini_sglang_b200 import ops
+    from mini_sglang_b200.config import Qwen3Config
+    from mini_sglang_b200.config.qwen3 import build_qwen3_spec
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    from mini_sglang_b200.parts import expected_tensors
+    from mini_sglang_b200.weights import RandomSource
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 96,
+           "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 32, "intermediate_size": 160, "vocab_size": 411,
+           "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 4096,
+           "hidden_act": "silu", "attention_bias": False, "torch_dtype": "bfloat16"}
+    spec = build_qwen3_spec(Qwen3Config.from_dict(cfg))
+    src = RandomSource(expected_tensors(spec), 5, torch.bfloat16, "cuda")
+    weights = {n: src.draw(n) for n in expected_tensors(spec) if src.has(n)}
+    lens = {"a": 1100, "b": 2300, "c": 3000, "d": 1500, "e": 1030, "f": 2048}
+    n_dec = 6
+    seqs = {r: random_tokens(n + n_dec, cfg["vocab_size"], 900 + i) for i, (r, n) in enumerate(lens.items())}
+    pages = sum(-(-(lens[r] + n_dec) // 16) for r in "abcd") + 2          # room for four of them at a time
+    runner = ModelRunner.from_random(spec, 5, dtype="bfloat16", page_size=16, num_pages=pages, max_reqs=4)
+    assert runner.device_meta and runner._even_nb
+    slots, fed, got, plans = {}, {}, {}, []
+    inner = runner._meta_on_device
+
+    def checking(gr, entries, starts, nsplits, b, even_cuts=None):
+        inner(gr, entries, starts, nsplits, b, even_cuts)
+        lay = gr.layout
+        want = np.zeros(lay.size, dtype=np.int32)
+        runner._fill(want, lay, entries, starts, list(range(b)), nsplits, pad_to=b, even_cuts=even_cuts)
+        have = gr.dev.cpu().numpy()
+        n_even = ops.even_cut_size(b, lay.even_nb[0])
+        for off, n in [(lay.even[0], n_even), (lay.nsplit[0], b), (lay.kv_len, b), (lay.out_loc[0], b)]:
+            assert (have[off:off + n] == want[off:off + n]).all(), (have[off:off + n], want[off:off + n])
+
+    monkeypatch.setattr(runner, "_meta_on_device", checking)
+
+    def feed(r):
+        slots[r], fed[r] = runner.open(), lens[r]
+        runner.step([StepEntry(slots[r], seqs[r][:lens[r]], [])])
+
+    def decode(rs):
+        out = runner.step([StepEntry(slots[r], [seqs[r][fed[r]]], [0]) for r in rs]).float().cpu()
+        assert runner.last_step_used_graph and runner.last_plan["graph_key"][2] == "even", runner.last_plan
+        plans.append(runner.last_plan)
+        for r, row in zip(rs, out):
+            got[(r, fed[r])] = row
+            fed[r] += 1
+
+    for r in "abcd":
+        feed(r)
+    decode("abcd")
+    decode("abcd")
+    runner.close(slots.pop("b"))
+    decode("acd")
+    feed("e")                                   # takes pages that b held
+    decode("acde")
+    runner.close(slots.pop("c"))
+    feed("f")
+    decode("adef")
+    decode("fa")
+    assert max(max(p["nsplits"][0]) for p in plans) > 4 and min(min(p["nsplits"][0]) for p in plans) >= 1
+    for r in lens:
+        rows = sorted(pos for (rr, pos) in got if rr == r)
+        with torch.no_grad():
+            ref = P.forward_sequence(cfg, weights, seqs[r], device="cuda", rows=rows).cpu()
+        for pos, want in zip(rows, ref):
+            try:
+                assert_row_close(got[(r, pos)], want, "bfloat16")
+            except AssertionError as e:
+                raise AssertionError(f"request {r}, position {pos}: {e}") from None

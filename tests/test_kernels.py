@@ -314,7 +314,7 @@ def attention_reference(q, K, V, q_lens, kv_lens, scale, window):
 
 
 def run_attention_case(dtype, n_q, n_kv, d, P, q_lens, kv_lens, window=None, force_split=None, seed=0,
-                       spike=False, order=None):
+                       spike=False, order=None, even_blocks=None, max_pieces=8):
     from mini_sglang_b200.config import PartSpec
     from mini_sglang_b200.parts import BuildEnv, GroupContext, KVCacheView, StepContext, Workspace
     from mini_sglang_b200.parts.attention import PagedAttention
@@ -364,8 +364,14 @@ def run_attention_case(dtype, n_q, n_kv, d, P, q_lens, kv_lens, window=None, for
     nsplit, max_split = None, 1
     if force_split:
         nsplit, max_split = i32([force_split] * B), force_split
+    even = None
+    if even_blocks:          # the keys dealt out evenly over even_blocks blocks per kv head (decode only)
+        from mini_sglang_b200.engine.step import pack_even_cut, plan_even_cut
+        cut = plan_even_cut(kv_lens, window, even_blocks, max_pieces)
+        nsplit, max_split = i32(cut[5].tolist()), max_pieces
+        even = torch.from_numpy(pack_even_cut(cut, B, even_blocks)).to(DEV)
     grp = GroupContext(block_table=bt.to(DEV), out_loc=i32([0] * T), nsplit=nsplit, max_split=max_split, window=window,
-                       order=i32(list(order)) if order is not None else None)
+                       order=i32(list(order)) if order is not None else None, even=even, even_nb=even_blocks or 0)
     uniform = all(n == 1 for n in q_lens)
     ctx = StepContext(T=T, B=B, page_size=P, input_ids=i32([0] * T), positions=i32([0] * T), q_start=i32(q_start),
                       kv_len=i32(kv_lens), token_req=i32(token_req), slots=i32([0] * B), groups=[grp],
@@ -408,6 +414,24 @@ def test_attention_decode_batch_with_splits(dtype, force_split, order):
     out, ref = run_attention_case(dtype, 32, 8, 128, 16, [1] * len(kv_lens), kv_lens, force_split=force_split,
                                   seed=7, spike=True, order=order)
     torch.testing.assert_close(out, ref.to(dtype).float(), **ATT_TOL[dtype])
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,P", [(32, 8, 128, 16), (8, 2, 64, 8), (16, 1, 32, 4), (6, 2, 96, 16)])
+@pytest.mark.parametrize("blocks,max_pieces", [(1, 1), (3, 8), (7, 8), (74, 32), (7, 2)])
+@pytest.mark.parametrize("window", [None, 600])
+def test_attention_decode_even_cut(n_q, n_kv, d, P, blocks, max_pieces, window):
+    """Single decoded tokens of requests of very different lengths with the keys of all of them dealt out evenly over
+    a fixed number of blocks: a block takes the end of one request, whole short ones and the start of the next; requests
+    in several blocks are merged from their pieces.  A far key stands out in every long request (it must be read once)."""
+    from mini_sglang_b200.engine.step import plan_even_cut
+    kv_lens = [1, 63, 64, 65, 700, 1500, 300, 129, 16, 17, 1025]
+    if d not in (32, 64, 96, 128):
+        pytest.skip("no transposed decode kernel for this head size")
+    cut = plan_even_cut(kv_lens, window, blocks, max_pieces)
+    assert cut[5].max() <= max_pieces and (window is not None or blocks == 1 or max_pieces == 1 or cut[5].max() > 1)
+    out, ref = run_attention_case(torch.bfloat16, n_q, n_kv, d, P, [1] * len(kv_lens), kv_lens, window=window, seed=11,
+                                  spike=window is None, even_blocks=blocks, max_pieces=max_pieces)
+    torch.testing.assert_close(out, ref.to(torch.bfloat16).float(), **ATT_TOL[torch.bfloat16])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
