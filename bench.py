@@ -165,6 +165,43 @@ def sanity_check(cfg, page):
     return out
 
 
+def parse_lengths(spec, batch):
+    """'lo:hi' -> `batch` lengths spread evenly from lo to hi; 'a,bxN,c' -> the list itself (x: repeated)."""
+    if ":" in spec:
+        lo, hi = (int(x) for x in spec.split(":"))
+        return [lo + (hi - lo) * i // max(batch - 1, 1) for i in range(batch)]
+    out = []
+    for part in spec.split(","):
+        n, _, rep = part.partition("x")
+        out += [int(n)] * (int(rep) if rep else 1)
+    return out
+
+
+def profile_kernels(step, n_steps, captures=lambda: 0):
+    """-> {kernel name: [launches a step, mean microseconds]} of the twelve kernels that `n_steps` calls of step() spend the
+    most time in, from the CUDA profiler's trace (kernels inside a replayed graph included).  `captures()` counts the CUDA
+    graphs made so far: a trace during which one was captured (its warm-up runs are in it) is taken again."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    for _ in range(4):
+        before = captures()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(n_steps):
+                step()
+            torch.cuda.synchronize()
+        if captures() == before:
+            break
+    acc = {}
+    for e in prof.events():
+        if e.device_type == torch.autograd.DeviceType.CUDA:
+            name = e.name.split("(")[0][:60]
+            a = acc.setdefault(name, [0, 0.0])
+            a[0] += 1
+            a[1] += e.time_range.end - e.time_range.start
+    top = sorted(acc.items(), key=lambda kv: -kv[1][1])[:12]
+    return {k: [round(v[0] / n_steps, 1), round(v[1] / v[0], 1)] for k, v in top}
+
+
 def _unavailable(why):
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
@@ -507,6 +544,12 @@ def main():
     ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep"],
                     help="headline: the line the contract names; the others: further workloads, one JSON line each")
     ap.add_argument("--skip-sanity", action="store_true", help="no comparison with the plain implementation before timing")
+    ap.add_argument("--model", default="8b", choices=["8b", "32b", "0.6b"], help="layer sizes for --only decode / prefill")
+    ap.add_argument("--lengths", default=None,
+                    help="--only decode: context lengths of the requests instead of --batch x --context: 'lo:hi' spreads --batch "
+                         "requests evenly from lo to hi, '30000,1000x15' lists them (x: repeated)")
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="--only decode: three more steps under the CUDA profiler; the line gets the kernels' mean times")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures the single-GPU engine; --gpus {args.gpus} is not supported (this engine has no multi-GPU path)")
@@ -529,6 +572,13 @@ def main():
     B, CTX, PAGE, PREFILL = args.batch, args.context, 16, 2048
     SETTLE = 0 if args.only != "all" else 25
     cfg = dict(QWEN3_8B)
+    lengths = None
+    if args.only != "all":
+        cfg = dict({"8b": QWEN3_8B, "32b": QWEN3_32B, "0.6b": QWEN3_0_6B}[args.model])
+        if args.lengths:
+            lengths = parse_lengths(args.lengths, B)
+            B, CTX = len(lengths), max(lengths)
+        cfg["max_position_embeddings"] = max(cfg.get("max_position_embeddings", 0), CTX + 64)
     cfg["num_hidden_layers"] = args.layers
     pk = peaks()
     tmp = tempfile.mkdtemp(prefix="msgl_bench_")
@@ -538,6 +588,8 @@ def main():
         args.skip_points = True
     max_b = B if args.skip_points else max(B, 64)
     pages = max_b * (CTX // PAGE + 2) + 256
+    if lengths:
+        pages = sum(n // PAGE + 2 for n in lengths) + 256
     eng = Engine(EngineArgs(model=tmp, dummy_load=True, random_seed=0, page_size=PAGE, num_pages=pages,
                             max_num_reqs=max_b + 2, max_context_len=CTX + 64, max_prefill_tokens=8192, chunk_size=2048,
                             disable_radix_cache=True, schedule_policy="fcfs", log_level="WARNING",
@@ -566,9 +618,10 @@ def main():
         if prompt_len is None:
             prompt_len = CTX - (warm + steps) - 1
         slots = [runner.open() for _ in range(batch)]
-        for s in slots:                                           # prompts in portions of 2,048
-            toks = rand_tokens(prompt_len)
-            for i in range(0, prompt_len, 2048):
+        for r, s in enumerate(slots):                             # prompts in portions of 2,048
+            n = max(lengths[r] - (warm + steps) - 1, 1) if lengths else prompt_len
+            toks = rand_tokens(n)
+            for i in range(0, n, 2048):
                 runner.step([StepEntry(s, toks[i:i + 2048], [])])
         feed = [[rand_tokens(1) for _ in slots] for _ in range(warm + steps)]
         for i in range(warm):
@@ -589,9 +642,14 @@ def main():
         ms = e0.elapsed_time(e1) / steps
         launches = ops.LAUNCHES - l0
         c1 = clocks.mark()
+        if args.kernel_times and args.only == "decode":
+            kernel_times.update(profile_kernels(lambda: runner.step([StepEntry(s, rand_tokens(1), [0]) for s in slots]), 3,
+                                                captures=lambda: len(runner._graphs)))
         for s in slots:
             runner.close(s)
         return ms, launches, (c0, c1)
+
+    kernel_times = {}
 
     if args.only == "prefill":
         s = runner.open()
@@ -618,8 +676,13 @@ def main():
     ms_step, launches, (c0, c1) = timed_decode(B, K, W)
     if args.only == "decode":
         clocks.stop()
-        print(json.dumps({"only": "decode", "layers": L, "batch": B, "context": CTX, "ms_per_step": round(ms_step, 4),
-                          "launches": launches}))
+        line = {"only": "decode", "model": args.model, "layers": L, "batch": B, "context": CTX, "ms_per_step": round(ms_step, 4),
+                "launches": launches, "plan": {k: (v if k != "nsplits" else [max(ns) for ns in v]) for k, v in runner.last_plan.items()}}
+        if lengths:
+            line["lengths"] = args.lengths
+        if kernel_times:
+            line["kernels"] = kernel_times
+        print(json.dumps(line))
         return 0
     value = B / (ms_step * 1e-3)
     step_bytes = weight_bytes + B * (CTX - K // 2) * kv_bytes_per_token
