@@ -1,6 +1,7 @@
 """Cache manager, prefix tree and scheduler on the CPU: no page lost, held twice or freed twice
 under random orders of requests; what the scheduler decides when pages run out."""
 
+import os
 import random
 
 import numpy as np
@@ -542,6 +543,25 @@ def test_even_cut_of_a_decode_step():
             assert [p for p, _, _ in runs] == list(range(int(pieces[r])))
             assert runs[0][1] == 0 and runs[-1][2] == cum[r + 1] - cum[r]
             assert all(a[2] == b[1] for a, b in zip(runs, runs[1:]))
+
+
+def test_which_decode_steps_take_the_even_cut():
+    """Requests of like length, short requests and a switched-off cut keep the cut per request; long requests of
+    different lengths take the even cut; a window bounds the keys that count."""
+    from types import SimpleNamespace
+    from mini_sglang_b200.engine.step import ModelRunner
+    def wants(lens, window=None):
+        stub = SimpleNamespace(mgr=SimpleNamespace(groups=[SimpleNamespace(window=window)]))
+        return ModelRunner._wants_even_cut(stub, lens)
+    assert not wants([4096] * 8) and not wants([4096 + 3 * i for i in range(64)]) and not wants([32768])
+    assert wants([1000 + 1000 * i for i in range(16)]) and wants([30000] + [1000] * 15) and wants([8000] * 4 + [500] * 28)
+    assert not wants([64 + 10 * i for i in range(128)])              # 64...1,334 keys: 44 units in the mean
+    assert not wants([30000] + [1000] * 15, window=1000)             # every request within its window: alike
+    os.environ["MSGL_EVEN_CUT"] = "0"
+    try:
+        assert not wants([30000] + [1000] * 15)
+    finally:
+        del os.environ["MSGL_EVEN_CUT"]
 
 
 def test_order_of_a_decode_batch():
