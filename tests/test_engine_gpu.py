@@ -259,7 +259,7 @@ def test_step_fields_made_on_the_device_equal_the_hosts(monkeypatch):
 def test_even_cut_of_requests_of_mixed_lengths(monkeypatch):
     """Decode steps whose requests hold 1,030 to 3,000 keys: the keys of all of them are dealt out evenly over the blocks
     that the SMs hold (a block takes the end of one request and the start of the next; a request is merged from up to
-    32 pieces).  Requests end and others join, pages are used again, the fields of every step are made on the device and
+    48 pieces).  Requests end and others join, pages are used again, the fields of every step are made on the device and
     compared with the host's.  bfloat16, two layers of a small width, every decoded row against the plain implementation."""
     import plain_qwen3 as P
     from helpers import assert_row_close
