@@ -1,5 +1,5 @@
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block, BuildEnv,
-                   FeedForward, Mixer, Norm, Part, PositionEncoding, register_block, register_embedding,
+                   FeedForward, Mixer, Norm, Part, PositionEncoding, build_part, register_block, register_embedding,
                    register_feed_forward, register_head, register_mixer, register_norm, register_position_encoding)
 from .context import GroupContext, KVCacheView, StateCacheView, StepContext, Workspace
 from . import attention, block, embedding, mlp, norm, rope  # noqa: F401  (register the built-in parts)

@@ -546,3 +546,180 @@ def test_scheduler_runs_a_toy_model_with_two_cache_groups_under_a_small_pool():
                 toks.append(t)
     finally:
         ARCHITECTURES.pop("ToyRoutedLM", None)
+
+
+# ---------------------------------------------------------------------------------------
+# a third toy architecture, defined here as well: a norm of another kind (mean-centred, with a bias)
+# and another arrangement of a block (one norm, mixer and feed-forward side by side on its output)
+# ---------------------------------------------------------------------------------------
+def _register_parallel_toy():
+    from mini_sglang_b200.config import LayerSpec, ModelSpec, PartSpec, Run, register_architecture
+    from mini_sglang_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, Norm, build_part
+    from mini_sglang_b200.parts import register_block, register_norm
+    from mini_sglang_b200.weights import TensorDecl
+
+    if "toy_centred_norm" not in NORMS:
+        @register_norm("toy_centred_norm")
+        class CentredNorm(Norm):
+            """v = residual + x; y = (v - mean(v)) * rsqrt(var(v) + eps) * weight + bias, in float32.  The sum goes to
+            `residual_out`; `rows` picks the rows that are normed."""
+
+            def __init__(self, spec, prefix, env):
+                super().__init__(spec, prefix, env)
+                self.size, self.eps = spec["size"], spec["eps"]
+                self.w_name, self.b_name = spec.get("name", self.name("weight")), spec.get("bias_name", self.name("bias"))
+
+            def tensors(self):
+                return {self.w_name: TensorDecl((self.size,), kind="vector", init="norm"),
+                        self.b_name: TensorDecl((self.size,), kind="vector")}
+
+            def load(self, src):
+                self.weight, self.bias = src.fetch(self.w_name).float(), src.fetch(self.b_name).float()
+
+            def forward(self, x=None, residual=None, residual_out=None, rows=None):
+                v = residual if x is None else (x.float() if residual is None else residual + x.float())
+                if residual_out is not None and x is not None:
+                    residual_out.copy_(v)
+                if rows is not None:
+                    v = v[rows.long()]
+                c = v - v.mean(-1, keepdim=True)
+                y = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight + self.bias
+                return y.to(self.env.dtype)
+
+    if "toy_side_by_side" not in BLOCKS:
+        @register_block("toy_side_by_side")
+        class SideBySideBlock(Block):
+            """res += delta_in; y = norm(res); delta_out = mixer(y) + feed_forward(y): one norm a layer, both branches
+            read its output.  The engine asks a block for `mixer` (cache need, graph safety) and `ffn` (graph safety)."""
+
+            def __init__(self, layer_spec, env):
+                super().__init__(None, layer_spec.prefix, env)
+                at = layer_spec.part_prefix
+                self.position = env.shared(layer_spec.position, lambda: build_part(
+                    POSITION_ENCODINGS, "position encoding", layer_spec.position, layer_spec.prefix, env))
+                self.norm = build_part(NORMS, "norm", layer_spec.norms["input"], at("input"), env)
+                self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, at("mixer"), env, position=self.position)
+                self.ffn = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward, at("feed_forward"), env)
+
+            def tensors(self):
+                out = {}
+                for part in (self.position, self.norm, self.mixer, self.ffn):
+                    out.update(part.tensors())
+                return out
+
+            def load(self, src):
+                for part in (self.position, self.norm, self.mixer, self.ffn):
+                    part.load(src)
+
+            def forward(self, delta, residual, ctx, cache, writes_cache=True):
+                y = self.norm.forward(x=delta, residual=residual, residual_out=residual if delta is not None else None)
+                return self.mixer.forward(y, ctx, cache, writes_cache) + self.ffn.forward(y, ctx), residual
+
+    class Cfg:
+        def __init__(self, raw):
+            self.raw = raw
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw)
+
+    def build(cfg):
+        r = cfg.raw
+        H, V = r["width"], r["vocab"]
+        norm = PartSpec("toy_centred_norm", {"size": H, "eps": r["eps"]})
+        pos = PartSpec("rope_neox", {"head_dim": 32, "rotary_dim": 16, "theta": 500.0, "max_positions": 256})
+        att = PartSpec("paged_attention", {"hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 32, "qk_norm": False})
+        ffn = PartSpec("swiglu_mlp", {"hidden_size": H, "intermediate_size": r["ffn"]})
+        layers = [LayerSpec(f"toy.h.{i}", att, ffn, {"input": norm}, position=pos, block="toy_side_by_side",
+                            names={"input": "ln", "mixer": "attn", "feed_forward": "mlp"}) for i in range(2)]
+        return ModelSpec("ToySideBySideLM", H, V, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "name": "toy.wte.weight"}),
+                         PartSpec("toy_centred_norm", {"size": H, "eps": r["eps"], "name": "toy.ln_f.weight", "bias_name": "toy.ln_f.bias"}),
+                         PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": True, "name": "toy.head.weight", "tied_to": "toy.wte.weight"}),
+                         layers, [Run(0, cache=0), Run(1, cache=1)], max_context_len=256)
+
+    register_architecture("ToySideBySideLM", Cfg, build)
+    return build, Cfg
+
+
+def side_by_side_plain(w, tokens, eps):
+    f = {k: v.float() for k, v in w.items()}
+    S = len(tokens)
+    res = f["toy.wte.weight"][torch.tensor(tokens)]
+    inv = 1.0 / (500.0 ** (torch.arange(0, 16, 2, dtype=torch.float32) / 16))
+    ang = torch.arange(S, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+    def norm(v, p):
+        c = v - v.mean(-1, keepdim=True)
+        return c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * f[p + "weight"] + f[p + "bias"]
+
+    def rotate(x):                                   # the first 16 of a head's 32 elements, in halves of 8
+        a, b, rest = x[..., :8], x[..., 8:16], x[..., 16:]
+        return torch.cat((a * cos - b * sin, b * cos + a * sin, rest), -1)
+
+    for i in range(2):
+        p = f"toy.h.{i}."
+        y = norm(res, p + "ln.")
+        q = rotate((y @ f[p + "attn.q_proj.weight"].T).reshape(S, 4, 32))
+        k = rotate((y @ f[p + "attn.k_proj.weight"].T).reshape(S, 2, 32)).repeat_interleave(2, 1)
+        v = (y @ f[p + "attn.v_proj.weight"].T).reshape(S, 2, 32).repeat_interleave(2, 1)
+        s = torch.einsum("qhd,khd->hqk", q, k) * 32 ** -0.5
+        s = s.masked_fill(~(torch.arange(S)[None, :] <= torch.arange(S)[:, None]), float("-inf"))
+        a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(S, 128) @ f[p + "attn.o_proj.weight"].T
+        res = res + a + P.mlp_block(y, f, p + "mlp.")
+    return norm(res, "toy.ln_f.") @ f["toy.wte.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_a_norm_and_a_block_arrangement_of_its_own(dtype):
+    """Registered, built and stepped without a change to the framework's files: a mean-centred norm with a bias (also
+    as the model's final norm, on the wanted rows only) and a block with one norm whose output the mixer and the
+    feed-forward read side by side.  A prompt whole, another in portions, then both decoded token by token through the
+    CUDA graph; every row against the toy's plain restatement."""
+    from mini_sglang_b200.config import ARCHITECTURES
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    from mini_sglang_b200.weights import RandomSource
+
+    build, Cfg = _register_parallel_toy()
+    try:
+        spec = build(Cfg({"width": 72, "vocab": 131, "ffn": 88, "eps": 1e-5}))
+        spec.validate()
+        holder = {}
+
+        def factory(expected, dt, dev):
+            src = RandomSource(expected, 31, dt, dev, std=0.12)
+            holder["w"] = {n: src.draw(n).cpu() for n in expected if src.has(n)}
+            return src
+
+        runner = ModelRunner(spec, factory, dtype=dtype, page_size=8, num_pages=24, max_reqs=2, max_step_tokens=64)
+        assert runner.use_cuda_graph and len(runner.mgr.groups) == 1
+        g = torch.Generator().manual_seed(12)
+        a = torch.randint(0, 131, (45,), generator=g).tolist()
+        b = torch.randint(0, 131, (38,), generator=g).tolist()
+        sa, sb = runner.open(), runner.open()
+        got = {}
+
+        def step(parts):                             # parts: [(name, slot, tokens, first position)]
+            out = runner.step([StepEntry(s, t, list(range(len(t)))) for _, s, t, _ in parts]).float().cpu()
+            i = 0
+            for name, _, t, p0 in parts:
+                for k in range(len(t)):
+                    got[(name, p0 + k)] = out[i]
+                    i += 1
+
+        step([("a", sa, a[:40], 0)])
+        step([("b", sb, b[:9], 0)])
+        step([("b", sb, b[9:11], 9)])
+        step([("b", sb, b[11:33], 11)])
+        for k in range(5):
+            step([("a", sa, a[40 + k:41 + k], 40 + k), ("b", sb, b[33 + k:34 + k], 33 + k)])
+            assert runner.last_step_used_graph
+        ref = {"a": side_by_side_plain(holder["w"], a, 1e-5), "b": side_by_side_plain(holder["w"], b, 1e-5)}
+        assert len(got) == 45 + 38
+        for (name, pos), row in got.items():
+            try:
+                assert_row_close(row, ref[name][pos], dtype)
+            except AssertionError as e:
+                raise AssertionError(f"request {name}, position {pos}: {e}") from None
+    finally:
+        ARCHITECTURES.pop("ToySideBySideLM", None)
