@@ -12,7 +12,8 @@ from .base import Part, register_embedding, register_head
 @register_embedding("token_embedding")
 class TokenEmbedding(Part):
     """h = E[ids], no scaling (mini_sglang/layers/embed_head.py:49); the result opens the float32
-    residual stream.  params: vocab_size, hidden_size, name."""
+    residual stream.  params: vocab_size, hidden_size, name.  An embedding part gets the step's context too
+    (`ctx.positions` for one that adds a position's own vector); this one does not need it."""
 
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
@@ -26,7 +27,7 @@ class TokenEmbedding(Part):
     def load(self, src) -> None:
         self.weight = src.fetch(self.tensor_name).contiguous()
 
-    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+    def forward(self, ids: torch.Tensor, ctx=None) -> torch.Tensor:
         return ops.embedding(ids, self.weight)
 
     def fused_decode_fields(self):

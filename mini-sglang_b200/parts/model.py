@@ -75,7 +75,7 @@ class DecoderModel:
             return self.fused_decode.forward(ctx, caches)       # the whole step in one persistent kernel
         if NVTX_RANGES:
             return self._forward_marked(ctx, caches, want_rows)
-        residual = self.embedding.forward(ctx.input_ids)
+        residual = self.embedding.forward(ctx.input_ids, ctx)
         delta = None
         for run in self.schedule:
             cache = caches.get(run.cache) if run.cache is not None else None
@@ -88,7 +88,7 @@ class DecoderModel:
         that show them on the timeline."""
         nvtx = torch.cuda.nvtx
         nvtx.range_push("embedding")
-        residual = self.embedding.forward(ctx.input_ids)
+        residual = self.embedding.forward(ctx.input_ids, ctx)
         nvtx.range_pop()
         delta = None
         for i, run in enumerate(self.schedule):

@@ -554,9 +554,29 @@ def test_scheduler_runs_a_toy_model_with_two_cache_groups_under_a_small_pool():
 # ---------------------------------------------------------------------------------------
 def _register_parallel_toy():
     from mini_sglang_b200.config import LayerSpec, ModelSpec, PartSpec, Run, register_architecture
-    from mini_sglang_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, Norm, build_part
-    from mini_sglang_b200.parts import register_block, register_norm
+    from mini_sglang_b200.parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, Norm, Part, build_part
+    from mini_sglang_b200.parts import register_block, register_embedding, register_norm
     from mini_sglang_b200.weights import TensorDecl
+
+    if "toy_token_and_place" not in EMBEDDINGS:
+        @register_embedding("toy_token_and_place")
+        class TokenAndPlace(Part):
+            """h = E[id] + A[position]: a position encoding that is added to the hidden state (a learned vector for every
+            place) belongs to the embedding part, which gets the step's context for it."""
+
+            def __init__(self, spec, prefix, env):
+                super().__init__(spec, prefix, env)
+                self.V, self.H, self.places = spec["vocab_size"], spec["hidden_size"], spec["places"]
+                self.tensor_name, self.place_name = spec["name"], spec["place_name"]
+
+            def tensors(self):
+                return {self.tensor_name: TensorDecl((self.V, self.H)), self.place_name: TensorDecl((self.places, self.H))}
+
+            def load(self, src):
+                self.weight, self.place = src.fetch(self.tensor_name).contiguous(), src.fetch(self.place_name).contiguous()
+
+            def forward(self, ids, ctx=None):
+                return self.weight[ids.long()].float() + self.place[ctx.positions.long()].float()
 
     if "toy_centred_norm" not in NORMS:
         @register_norm("toy_centred_norm")
@@ -595,20 +615,25 @@ def _register_parallel_toy():
             def __init__(self, layer_spec, env):
                 super().__init__(None, layer_spec.prefix, env)
                 at = layer_spec.part_prefix
-                self.position = env.shared(layer_spec.position, lambda: build_part(
-                    POSITION_ENCODINGS, "position encoding", layer_spec.position, layer_spec.prefix, env))
+                self.position = None
+                if layer_spec.position is not None:
+                    self.position = env.shared(layer_spec.position, lambda: build_part(
+                        POSITION_ENCODINGS, "position encoding", layer_spec.position, layer_spec.prefix, env))
                 self.norm = build_part(NORMS, "norm", layer_spec.norms["input"], at("input"), env)
                 self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, at("mixer"), env, position=self.position)
                 self.ffn = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward, at("feed_forward"), env)
 
+            def parts(self):
+                return [p for p in (self.position, self.norm, self.mixer, self.ffn) if p is not None]
+
             def tensors(self):
                 out = {}
-                for part in (self.position, self.norm, self.mixer, self.ffn):
+                for part in self.parts():
                     out.update(part.tensors())
                 return out
 
             def load(self, src):
-                for part in (self.position, self.norm, self.mixer, self.ffn):
+                for part in self.parts():
                     part.load(src)
 
             def forward(self, delta, residual, ctx, cache, writes_cache=True):
@@ -630,9 +655,12 @@ def _register_parallel_toy():
         pos = PartSpec("rope_neox", {"head_dim": 32, "rotary_dim": 16, "theta": 500.0, "max_positions": 256})
         att = PartSpec("paged_attention", {"hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 32, "qk_norm": False})
         ffn = PartSpec("swiglu_mlp", {"hidden_size": H, "intermediate_size": r["ffn"]})
-        layers = [LayerSpec(f"toy.h.{i}", att, ffn, {"input": norm}, position=pos, block="toy_side_by_side",
+        # layer 0 rotates q and k, layer 1 has no position encoding of its own (the places are in the stream already)
+        layers = [LayerSpec(f"toy.h.{i}", att, ffn, {"input": norm}, position=pos if i == 0 else None, block="toy_side_by_side",
                             names={"input": "ln", "mixer": "attn", "feed_forward": "mlp"}) for i in range(2)]
-        return ModelSpec("ToySideBySideLM", H, V, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "name": "toy.wte.weight"}),
+        return ModelSpec("ToySideBySideLM", H, V,
+                         PartSpec("toy_token_and_place", {"vocab_size": V, "hidden_size": H, "places": 256, "name": "toy.wte.weight",
+                                                          "place_name": "toy.wpe.weight"}),
                          PartSpec("toy_centred_norm", {"size": H, "eps": r["eps"], "name": "toy.ln_f.weight", "bias_name": "toy.ln_f.bias"}),
                          PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": True, "name": "toy.head.weight", "tied_to": "toy.wte.weight"}),
                          layers, [Run(0, cache=0), Run(1, cache=1)], max_context_len=256)
@@ -644,7 +672,7 @@ def _register_parallel_toy():
 def side_by_side_plain(w, tokens, eps):
     f = {k: v.float() for k, v in w.items()}
     S = len(tokens)
-    res = f["toy.wte.weight"][torch.tensor(tokens)]
+    res = f["toy.wte.weight"][torch.tensor(tokens)] + f["toy.wpe.weight"][:S]
     inv = 1.0 / (500.0 ** (torch.arange(0, 16, 2, dtype=torch.float32) / 16))
     ang = torch.arange(S, dtype=torch.float32)[:, None] * inv[None, :]
     cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
@@ -660,8 +688,11 @@ def side_by_side_plain(w, tokens, eps):
     for i in range(2):
         p = f"toy.h.{i}."
         y = norm(res, p + "ln.")
-        q = rotate((y @ f[p + "attn.q_proj.weight"].T).reshape(S, 4, 32))
-        k = rotate((y @ f[p + "attn.k_proj.weight"].T).reshape(S, 2, 32)).repeat_interleave(2, 1)
+        q = (y @ f[p + "attn.q_proj.weight"].T).reshape(S, 4, 32)
+        k = (y @ f[p + "attn.k_proj.weight"].T).reshape(S, 2, 32)
+        if i == 0:
+            q, k = rotate(q), rotate(k)
+        k = k.repeat_interleave(2, 1)
         v = (y @ f[p + "attn.v_proj.weight"].T).reshape(S, 2, 32).repeat_interleave(2, 1)
         s = torch.einsum("qhd,khd->hqk", q, k) * 32 ** -0.5
         s = s.masked_fill(~(torch.arange(S)[None, :] <= torch.arange(S)[:, None]), float("-inf"))
@@ -672,9 +703,10 @@ def side_by_side_plain(w, tokens, eps):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_toy_architecture_with_a_norm_and_a_block_arrangement_of_its_own(dtype):
-    """Registered, built and stepped without a change to the framework's files: a mean-centred norm with a bias (also
-    as the model's final norm, on the wanted rows only) and a block with one norm whose output the mixer and the
-    feed-forward read side by side.  A prompt whole, another in portions, then both decoded token by token through the
+    """Registered, built and stepped without a change to the framework's files: an embedding that adds a learned vector
+    for every place, a mean-centred norm with a bias (also as the model's final norm, on the wanted rows only) and a block
+    with one norm whose output the mixer and the feed-forward read side by side; one layer rotates q and k, the other has
+    no position encoding.  A prompt whole, another in portions, then both decoded token by token through the
     CUDA graph; every row against the toy's plain restatement."""
     from mini_sglang_b200.config import ARCHITECTURES
     from mini_sglang_b200.engine.step import ModelRunner, StepEntry
