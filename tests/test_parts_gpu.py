@@ -554,8 +554,8 @@ def test_scheduler_runs_a_toy_model_with_two_cache_groups_under_a_small_pool():
 # ---------------------------------------------------------------------------------------
 def _register_parallel_toy():
     from mini_sglang_b200.config import LayerSpec, ModelSpec, PartSpec, Run, register_architecture
-    from mini_sglang_b200.parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, Norm, Part, build_part
-    from mini_sglang_b200.parts import register_block, register_embedding, register_norm
+    from mini_sglang_b200.parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block, Norm, Part, build_part
+    from mini_sglang_b200.parts import register_block, register_embedding, register_head, register_norm
     from mini_sglang_b200.weights import TensorDecl
 
     if "toy_token_and_place" not in EMBEDDINGS:
@@ -577,6 +577,25 @@ def _register_parallel_toy():
 
             def forward(self, ids, ctx=None):
                 return self.weight[ids.long()].float() + self.place[ctx.positions.long()].float()
+
+    if "toy_capped_head" not in HEADS:
+        @register_head("toy_capped_head")
+        class CappedHead(Part):
+            """logits = cap * tanh((h W^T + bias) / cap), float32: an output head with a bias and a soft cap."""
+
+            def __init__(self, spec, prefix, env):
+                super().__init__(spec, prefix, env)
+                self.V, self.H, self.cap = spec["vocab_size"], spec["hidden_size"], spec["cap"]
+
+            def tensors(self):
+                return {"toy.head.weight": TensorDecl((self.V, self.H)), "toy.head.bias": TensorDecl((self.V,), kind="vector")}
+
+            def load(self, src, embedding=None):
+                self.weight, self.bias = src.fetch("toy.head.weight").contiguous(), src.fetch("toy.head.bias").float()
+
+            def forward(self, h):
+                from mini_sglang_b200 import ops
+                return self.cap * torch.tanh((ops.linear(h, self.weight, out_dtype=torch.float32) + self.bias) / self.cap)
 
     if "toy_centred_norm" not in NORMS:
         @register_norm("toy_centred_norm")
@@ -662,7 +681,7 @@ def _register_parallel_toy():
                          PartSpec("toy_token_and_place", {"vocab_size": V, "hidden_size": H, "places": 256, "name": "toy.wte.weight",
                                                           "place_name": "toy.wpe.weight"}),
                          PartSpec("toy_centred_norm", {"size": H, "eps": r["eps"], "name": "toy.ln_f.weight", "bias_name": "toy.ln_f.bias"}),
-                         PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": True, "name": "toy.head.weight", "tied_to": "toy.wte.weight"}),
+                         PartSpec("toy_capped_head", {"vocab_size": V, "hidden_size": H, "cap": 2.0}),
                          layers, [Run(0, cache=0), Run(1, cache=1)], max_context_len=256)
 
     register_architecture("ToySideBySideLM", Cfg, build)
@@ -698,15 +717,15 @@ def side_by_side_plain(w, tokens, eps):
         s = s.masked_fill(~(torch.arange(S)[None, :] <= torch.arange(S)[:, None]), float("-inf"))
         a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(S, 128) @ f[p + "attn.o_proj.weight"].T
         res = res + a + P.mlp_block(y, f, p + "mlp.")
-    return norm(res, "toy.ln_f.") @ f["toy.wte.weight"].T
+    return 2.0 * torch.tanh((norm(res, "toy.ln_f.") @ f["toy.head.weight"].T + f["toy.head.bias"]) / 2.0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_toy_architecture_with_a_norm_and_a_block_arrangement_of_its_own(dtype):
     """Registered, built and stepped without a change to the framework's files: an embedding that adds a learned vector
-    for every place, a mean-centred norm with a bias (also as the model's final norm, on the wanted rows only) and a block
-    with one norm whose output the mixer and the feed-forward read side by side; one layer rotates q and k, the other has
-    no position encoding.  A prompt whole, another in portions, then both decoded token by token through the
+    for every place, a mean-centred norm with a bias (also as the model's final norm, on the wanted rows only), a block
+    with one norm whose output the mixer and the feed-forward read side by side, and an output head with a bias and a soft
+    cap; one layer rotates q and k, the other has no position encoding.  A prompt whole, another in portions, then both decoded token by token through the
     CUDA graph; every row against the toy's plain restatement."""
     from mini_sglang_b200.config import ARCHITECTURES
     from mini_sglang_b200.engine.step import ModelRunner, StepEntry
