@@ -35,6 +35,7 @@ class EngineArgs:
     schedule_conservativeness: float = 1.0
     max_prefill_tokens: int = 16384
     dummy_load: bool = False
+    attention_backend: Optional[str] = None  # the reference chooses between library kernels here; this engine has its own kernels only
     # this engine's own
     dtype: str = "bfloat16"                  # "bfloat16" | "float32" (true 32-bit everywhere)
     num_pages: Optional[int] = None          # size of the cache in pages instead of a memory fraction
@@ -72,6 +73,8 @@ class EngineArgs:
         d = EngineArgs
         parser.add_argument("--model", type=str, required=True, help="Model folder: config.json and *.safetensors (and a tokenizer, for text prompts).")
         parser.add_argument("--page_size", type=int, default=d.page_size, help="Tokens per page of the key/value cache (a power of two from 8 on suits the TMA kernels; 1 is allowed).")
+        parser.add_argument("--attention_backend", type=str, default=None,
+                            help="Accepted so that the reference's command lines keep working; this engine has one attention backend, its own kernels.")
         parser.add_argument("--tp_size", type=int, default=1, help="Number of GPUs the model is split over; this engine takes 1 only.")
         parser.add_argument("--device", type=str, default="cuda", help="Where the model runs; a CUDA device, nothing else.")
         parser.add_argument("--gpu_memory_utilization", type=float, default=d.gpu_memory_utilization,

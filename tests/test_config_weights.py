@@ -151,3 +151,35 @@ def test_safetensors_reader_rejects_garbage(tmp_path):
     p.write_bytes(b"\x00\x01")
     with pytest.raises(SafetensorsError):
         SafetensorsFile(str(p))
+
+
+def test_engine_options_keep_the_references_names_and_defaults(tmp_path):
+    """Every option of the reference's command line that concerns one GPU without a server (mini_sglang/managers/
+    server_args.py:62-183) parses here under the same name, and the defaults it has there are the defaults here, page_size
+    apart (1 there, 16 here; 1 is accepted).  What the engine cannot do is refused in words."""
+    import argparse
+
+    from mini_sglang_b200.engine.args import EngineArgs, ServerArgs
+    ap = argparse.ArgumentParser()
+    EngineArgs.add_cli_args(ap)
+    d = str(tmp_path)
+    ns = ap.parse_args(["--model", d, "--page_size", "1", "--attention_backend", "fa3", "--tp_size", "1", "--device", "cuda",
+                        "--gpu_memory_utilization", "0.8", "--max_num_reqs", "64", "--schedule_policy", "fcfs", "--log_level", "WARNING",
+                        "--random_seed", "7", "--profile", "--disable_radix_cache", "--disable_cuda_graph", "--max_capture_bs", "32",
+                        "--schedule-conservativeness", "0.5", "--max_prefill_tokens", "4096", "--dummy_load"])
+    a = EngineArgs.from_cli_args(ns)
+    assert (a.page_size, a.max_num_reqs, a.schedule_policy, a.random_seed, a.max_capture_bs) == (1, 64, "fcfs", 7, 32)
+    assert a.profile and a.disable_radix_cache and a.disable_cuda_graph and a.dummy_load
+    assert (a.gpu_memory_utilization, a.schedule_conservativeness, a.max_prefill_tokens) == (0.8, 0.5, 4096)
+    b = EngineArgs.from_cli_args(ap.parse_args(["--model", d]))
+    assert (b.max_num_reqs, b.max_capture_bs, b.schedule_policy, b.tp_size, b.device) == (1024, 128, "lpm", 1, "cuda")
+    assert (b.gpu_memory_utilization, b.log_level, b.schedule_conservativeness, b.max_prefill_tokens) == (0.9, "INFO", 1.0, 16384)
+    assert not (b.profile or b.disable_radix_cache or b.disable_cuda_graph or b.dummy_load) and isinstance(b.random_seed, int)
+    assert ServerArgs is EngineArgs
+    for bad, words in [(dict(tp_size=2), "one GPU"), (dict(device="cpu"), "CUDA"), (dict(schedule_policy="lifo"), "policy"),
+                       (dict(schedule_policy="lpm", disable_radix_cache=True), "radix"), (dict(dtype="float16"), "dtype"),
+                       (dict(page_size=0), "page_size")]:
+        with pytest.raises(ValueError, match=words):
+            EngineArgs(model=d, **bad)
+    with pytest.raises(ValueError, match="not a folder"):
+        EngineArgs(model=str(tmp_path / "nothing here"))
