@@ -260,3 +260,58 @@ def test_profile_records_log_lines_and_async_generate(tmp_path, caplog):
     eng.scheduler.check_idle_invariants()
     from mini_sglang_b200.parts import model as _model
     _model.NVTX_RANGES = False
+
+
+def _folder_with_a_tokenizer(tmp_path, name):
+    """A copy of a tiny model's folder with a word-level tokenizer beside it: the word "w<i>" is token i."""
+    import shutil
+
+    from tokenizers import Tokenizer
+    from tokenizers.models import WordLevel
+    from tokenizers.pre_tokenizers import WhitespaceSplit
+    d = str(tmp_path / "model")
+    shutil.copytree(model_dir(name), d)
+    tok = Tokenizer(WordLevel({f"w{i}": i for i in range(CONFIGS[name]["vocab_size"])}, unk_token="w0"))
+    tok.pre_tokenizer = WhitespaceSplit()
+    tok.save(os.path.join(d, "tokenizer.json"))
+    with open(os.path.join(d, "tokenizer_config.json"), "w") as f:
+        json.dump({"tokenizer_class": "PreTrainedTokenizerFast"}, f)
+    return d
+
+
+def test_text_prompts_through_the_entry_point_and_the_command_line(tmp_path):
+    """With a tokenizer in the model folder a prompt may be text: it is encoded on the way in and the new tokens are
+    decoded on the way out; the tokens are those of the same request given as ids, a list of texts runs as a batch, and
+    the command line takes --prompt and lines of text in --prompt_file.  Without a tokenizer a text prompt is refused."""
+    from mini_sglang_b200 import Engine, EngineArgs
+    name, cfg = "A", CONFIGS["A"]
+    d = _folder_with_a_tokenizer(tmp_path, name)
+    ids = random_tokens(7, cfg["vocab_size"], 1700)
+    other = random_tokens(4, cfg["vocab_size"], 1701)
+    text, other_text = " ".join(f"w{t}" for t in ids), " ".join(f"w{t}" for t in other)
+    sp = {"max_new_tokens": 5, "ignore_eos": True}
+    want = P.greedy_generate(cfg, weights(name), ids, 5, device="cpu")
+    want_other = P.greedy_generate(cfg, weights(name), other, 5, device="cpu")
+    eng = Engine(EngineArgs(model=d, dtype="float32", page_size=PAGE[name], num_pages=128, max_num_reqs=4, random_seed=0,
+                            log_level="ERROR"))
+    out = eng.generate(prompt=text, sampling_params=sp)
+    assert out["token_ids"] == want and out["text"] == " ".join(f"w{t}" for t in want) and out["meta_info"]["prompt_tokens"] == 7
+    both = eng.generate(prompt=[other_text, text], sampling_params=sp)
+    assert [o["token_ids"] for o in both] == [want_other, want]
+    last = None
+    for last in eng.generate(prompt=text, sampling_params=sp, stream=True):
+        pass
+    assert last["token_ids"] == want and last["text"].split() == [f"w{t}" for t in want]
+    plain_eng = make_engine(name, "float32")
+    with pytest.raises(ValueError, match="no tokenizer"):
+        plain_eng.generate(prompt=text, sampling_params=sp)
+    lines = tmp_path / "prompts.txt"
+    lines.write_text(other_text + "\n" + json.dumps(ids) + "\n")
+    proc = subprocess.run([sys.executable, "-m", "mini_sglang_b200.engine.cli", "--model", d, "--dtype", "float32",
+                           "--page_size", "1", "--num_pages", "128", "--max_num_reqs", "4", "--log_level", "ERROR",
+                           "--prompt", text, "--prompt_file", str(lines), "--max_new_tokens", "5", "--ignore_eos"],
+                          capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    outs = [json.loads(l) for l in proc.stdout.strip().split("\n")[-3:]]
+    assert [o["token_ids"] for o in outs] == [want, want_other, want]
+    assert outs[0]["text"] == " ".join(f"w{t}" for t in want)
