@@ -256,11 +256,13 @@ def test_step_fields_made_on_the_device_equal_the_hosts(monkeypatch):
         runner.close(s)
 
 
-def test_even_cut_of_requests_of_mixed_lengths(monkeypatch):
+@pytest.mark.parametrize("fields_on_device", [True, False])
+def test_even_cut_of_requests_of_mixed_lengths(monkeypatch, fields_on_device):
     """Decode steps whose requests hold 1,030 to 3,000 keys: the keys of all of them are dealt out evenly over the blocks
     that the SMs hold (a block takes the end of one request and the start of the next; a request is merged from up to
     48 pieces).  Requests end and others join, pages are used again, the fields of every step are made on the device and
-    compared with the host's.  bfloat16, two layers of a small width, every decoded row against the plain implementation."""
+    compared with the host's (or, second run, written by the host and copied).  bfloat16, two layers of a small width,
+    every decoded row against the plain implementation."""
     import plain_qwen3 as P
     from helpers import assert_row_close
     from mini_sglang_b200 import ops
@@ -295,7 +297,10 @@ def test_even_cut_of_requests_of_mixed_lengths(monkeypatch):
         for off, n in [(lay.even[0], n_even), (lay.nsplit[0], b), (lay.kv_len, b), (lay.out_loc[0], b)]:
             assert (have[off:off + n] == want[off:off + n]).all(), (have[off:off + n], want[off:off + n])
 
-    monkeypatch.setattr(runner, "_meta_on_device", checking)
+    if fields_on_device:
+        monkeypatch.setattr(runner, "_meta_on_device", checking)
+    else:
+        runner.device_meta = False              # the host writes every field of the step and copies them (the other way to a replay)
 
     def feed(r):
         slots[r], fed[r] = runner.open(), lens[r]
