@@ -458,6 +458,10 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_mma_kernel(const AttnParams 
 // the merge at the end, so loads stay in flight while other warps compute.
 // ---------------------------------------------------------------------------------------
 constexpr int DEC_WT = 16;        // keys per warp unit
+#ifndef MSGL_DEC_LAZY
+#define MSGL_DEC_LAZY 8
+#endif
+constexpr float DEC_LAZY = (float)MSGL_DEC_LAZY;   // log2 of how far a score may lie above its column's reference before the reference moves (decode_t_run)
 
 template <int D, int NW, int ST>
 __global__ void __launch_bounds__(NW * 32) attn_decode_kernel(const AttnParams p) {
@@ -882,42 +886,42 @@ __device__ __forceinline__ void decode_t_run(const AttnParams& p, const TileInfo
         const int key0 = (u_begin + warp + i * NW) * DEC_WT;
         const bool need_mask = (key0 + DEC_WT - 1 > p_min) || (p.window > 0 && key0 <= p_max - p.window);
         unsigned pb0[NBH], pb1[NBH];
-        float alpha[NBH][2];
-        bool rescale = false;
+        float v[NBH][4];
+        bool behind = false;              // a score lies further above its column's reference than DEC_LAZY allows
 #pragma unroll
-        for (int nb = 0; nb < NBH; ++nb) {
-            float v[4];
+        for (int nb = 0; nb < NBH; ++nb)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                v[e] = (s[nb][e] + s2[nb][e]) * sc;
+                v[nb][e] = (s[nb][e] + s2[nb][e]) * sc;
                 if (need_mask) {
                     const int key = key0 + g + ((e & 2) ? 8 : 0);
                     const int pos = pos_c[nb][e & 1];
                     bool ok = key <= pos;
                     if (p.window > 0) ok = ok && (key > pos - p.window);
-                    if (!ok) v[e] = -INFINITY;
+                    if (!ok) v[nb][e] = -INFINITY;
                 }
+                behind = behind || v[nb][e] > m_c[nb][e & 1] + DEC_LAZY;
             }
+        // The reference m of a column's exponentials need not be the maximum so far: any m that keeps 2^(s - m) within
+        // the range of bfloat16 and float32 gives the same softmax.  So the maximum over the unit's keys (three shuffles
+        // a column) is only looked for when some score of the warp lies more than DEC_LAZY above its reference (always
+        // for a column's first finite score); then the references move and the sums and accumulators are scaled.
+        if (__any_sync(0xffffffffu, behind)) {
+            float alpha[NBH][2];
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                float mx = fmaxf(v[e], v[e + 2]);
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                const float mn = fmaxf(m_c[nb][e], mx);
-                const float mu = (mn == -INFINITY) ? 0.f : mn;
-                alpha[nb][e] = fast_exp2(m_c[nb][e] - mu);
-                m_c[nb][e] = mn;
-                v[e] = fast_exp2(v[e] - mu);
-                v[e + 2] = fast_exp2(v[e + 2] - mu);
-                l_c[nb][e] = l_c[nb][e] * alpha[nb][e] + v[e] + v[e + 2];
-                rescale = rescale || alpha[nb][e] != 1.f;
-            }
-            // accumulator layout (key g | g+8 ; columns 2t, 2t+1) -> B operand layout (keys 2t, 2t+1 ; column g)
-            pb0[nb] = movmatrix_trans(pack_bf16(v[0], v[1]));
-            pb1[nb] = movmatrix_trans(pack_bf16(v[2], v[3]));
-        }
-        if (__any_sync(0xffffffffu, rescale)) {
+            for (int nb = 0; nb < NBH; ++nb)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    float mx = fmaxf(v[nb][e], v[nb][e + 2]);
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    const float mn = fmaxf(m_c[nb][e], mx);
+                    const float mu = (mn == -INFINITY) ? 0.f : mn;
+                    alpha[nb][e] = fast_exp2(m_c[nb][e] - mu);
+                    m_c[nb][e] = mn;
+                    l_c[nb][e] *= alpha[nb][e];
+                }
 #pragma unroll
             for (int nb = 0; nb < NBH; ++nb)
 #pragma unroll
@@ -925,6 +929,19 @@ __device__ __forceinline__ void decode_t_run(const AttnParams& p, const TileInfo
                     o[nb][mt][0] *= alpha[nb][0]; o[nb][mt][1] *= alpha[nb][1];
                     o[nb][mt][2] *= alpha[nb][0]; o[nb][mt][3] *= alpha[nb][1];
                 }
+        }
+#pragma unroll
+        for (int nb = 0; nb < NBH; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float mu = (m_c[nb][e] == -INFINITY) ? 0.f : m_c[nb][e];
+                v[nb][e] = fast_exp2(v[nb][e] - mu);
+                v[nb][e + 2] = fast_exp2(v[nb][e + 2] - mu);
+                l_c[nb][e] += v[nb][e] + v[nb][e + 2];
+            }
+            // accumulator layout (key g | g+8 ; columns 2t, 2t+1) -> B operand layout (keys 2t, 2t+1 ; column g)
+            pb0[nb] = movmatrix_trans(pack_bf16(v[nb][0], v[nb][1]));
+            pb1[nb] = movmatrix_trans(pack_bf16(v[nb][2], v[nb][3]));
         }
         // ---- O^T += V^T P^T
         cp_async_wait<ST - 1>();
