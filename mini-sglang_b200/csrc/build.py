@@ -152,7 +152,7 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     kernel takes any head size up to 512."""
     hd = head_dim if head_dim in MMA_HEAD_DIMS else 128
     defines = {"MSGL_HEAD_DIM": hd}
-    for knob in ("MSGL_DEC_WARPS", "MSGL_DEC_STAGES", "MSGL_DEC_PFK", "MSGL_DEC_PFV", "MSGL_TC_PROFILE", "MSGL_PDL_MODE", "MSGL_PDL_SMALL"):          # tuning knobs / phase timers
+    for knob in ("MSGL_DEC_WARPS", "MSGL_DEC_STAGES", "MSGL_DEC_PFK", "MSGL_DEC_PFV", "MSGL_DEC_LAZY", "MSGL_TC_PROFILE", "MSGL_PDL_MODE", "MSGL_PDL_SMALL"):          # tuning knobs / phase timers
         if os.environ.get(knob):
             defines[knob] = int(os.environ[knob])
     return load_library(f"attention_d{hd}", ATTENTION_SOURCES, defines)
