@@ -22,11 +22,14 @@
 //                               m16n8k16, 64 rows per block, each warp owns 16 rows and walks all keys of a tile
 //   attn_decode_t_kernel<D,...> bfloat16, short query runs (decode), head sizes in steps of 32: keys on the M
 //                               dimension of the mma, K straight from global memory into registers, kv splits
+//   attn_decode_even_kernel<D,...> the same arithmetic for a decode step whose keys the host has dealt out evenly over
+//                               a fixed number of blocks per kv head (requests of very different lengths)
 //   attn_decode_kernel<D,...>   the same for head sizes 16 mod 32: heads on the M dimension
 //   attn_simt_kernel<T>         any head size up to 512, float32 arithmetic throughout; this is
 //                               the true 32-bit path and the fallback for odd head sizes
 //   attn_combine_kernel<T>      merge of the kv splits
-// Scores, softmax and the accumulation are float32 in all of them.
+// Scores, softmax and the accumulation are float32 in all of them.  In a step of single tokens the blocks take the
+// requests in the order the step gives (`order`: longest first), the kv heads of one request in adjacent blocks.
 #include "common.cuh"
 #include <math.h>
 
