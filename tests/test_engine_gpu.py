@@ -336,3 +336,64 @@ def test_even_cut_of_requests_of_mixed_lengths(monkeypatch, fields_on_device):
                 assert_row_close(got[(r, pos)], want, "bfloat16")
             except AssertionError as e:
                 raise AssertionError(f"request {r}, position {pos}: {e}") from None
+
+
+@pytest.mark.parametrize("head_dim,seed", [(64, 0), (128, 3)])
+def test_random_requests_of_mixed_lengths_come_and_go(head_dim, seed):
+    """A random run: up to 12 live requests, short prompts (20...300 tokens) beside long ones (900...5,000), requests join
+    and leave at random, every step decodes one token of every live request through a CUDA graph (the even cut of the keys
+    in most steps, the cut per request in the others).  bfloat16, two layers of a small width; every decoded row against the
+    plain implementation."""
+    import plain_qwen3 as P
+    from helpers import assert_row_close
+    from mini_sglang_b200.config import Qwen3Config
+    from mini_sglang_b200.config.qwen3 import build_qwen3_spec
+    from mini_sglang_b200.engine.step import ModelRunner, StepEntry
+    from mini_sglang_b200.parts import expected_tensors
+    from mini_sglang_b200.weights import RandomSource
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 128,
+           "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": head_dim, "intermediate_size": 192, "vocab_size": 503,
+           "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 8192,
+           "hidden_act": "silu", "attention_bias": False, "torch_dtype": "bfloat16"}
+    spec = build_qwen3_spec(Qwen3Config.from_dict(cfg))
+    src = RandomSource(expected_tensors(spec), 5, torch.bfloat16, "cuda")
+    weights = {n: src.draw(n) for n in expected_tensors(spec) if src.has(n)}
+    rnd = np.random.RandomState(seed)
+    most, n_dec = 12, 60
+    runner = ModelRunner.from_random(spec, 5, dtype="bfloat16", page_size=16, num_pages=most * 330 + 8, max_reqs=most)
+    live, seqs, fed, got, modes = {}, {}, {}, {}, {}
+    for it in range(n_dec):
+        if len(live) < most and (len(live) < 3 or rnd.rand() < 0.3):
+            n = int(rnd.choice([rnd.randint(20, 300), rnd.randint(900, 5000)]))
+            rid = len(seqs)
+            seqs[rid] = random_tokens(n + n_dec, cfg["vocab_size"], 7000 + 100 * seed + rid)
+            live[rid], fed[rid] = runner.open(), n
+            for i in range(0, n, 2048):
+                runner.step([StepEntry(live[rid], seqs[rid][i:min(i + 2048, n)], [])])
+        if live and rnd.rand() < 0.1:
+            runner.close(live.pop(list(live)[rnd.randint(len(live))]))
+        rs = list(live)
+        if not rs:
+            continue
+        out = runner.step([StepEntry(live[r], [seqs[r][fed[r]]], [0]) for r in rs]).float().cpu()
+        assert runner.last_step_used_graph
+        mode = str(runner.last_plan["graph_key"][2])
+        modes[mode] = modes.get(mode, 0) + 1
+        for r, row in zip(rs, out):
+            got[(r, fed[r])] = row
+            fed[r] += 1
+    assert modes.get("even", 0) >= n_dec // 3 and len(got) > 4 * n_dec, (modes, len(got))
+    for rid in seqs:
+        rows = sorted(p for (r, p) in got if r == rid)
+        if not rows:
+            continue
+        with torch.no_grad():
+            ref = P.forward_sequence(cfg, weights, seqs[rid][:rows[-1] + 1], device="cuda", rows=rows).cpu()
+        for p, want in zip(rows, ref):
+            try:
+                assert_row_close(got[(rid, p)], want, "bfloat16")
+            except AssertionError as e:
+                raise AssertionError(f"head size {head_dim}, request {rid}, position {p}: {e}") from None
+    for s in live.values():
+        runner.close(s)
+    runner.mgr.check_idle()
