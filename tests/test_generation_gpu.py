@@ -315,3 +315,43 @@ def test_text_prompts_through_the_entry_point_and_the_command_line(tmp_path):
     outs = [json.loads(l) for l in proc.stdout.strip().split("\n")[-3:]]
     assert [o["token_ids"] for o in outs] == [want, want_other, want]
     assert outs[0]["text"] == " ".join(f"w{t}" for t in want)
+
+
+def test_long_prompts_under_a_small_pool_twice_the_same(tmp_path):
+    """Forty requests with prompts of 20...4,000 tokens (a third of them behind a shared prefix of 400) and 20...90 new tokens
+    each, through the scheduler with 16 slots, portions of 512 tokens and a pool that holds a fraction of them (requests wait,
+    are retracted and come back; decode steps take the even cut of the keys or the cut per request as the lengths ask).  In
+    bfloat16 two runs give the same tokens, request by request; the float32 run of the same requests gives the same first
+    five tokens everywhere (later ones may part by rounding); nothing is left allocated."""
+    from mini_sglang_b200 import Engine, EngineArgs
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 128,
+           "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 192, "vocab_size": 503,
+           "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 8192,
+           "hidden_act": "silu", "attention_bias": False, "torch_dtype": "bfloat16"}
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(cfg, f)
+    g = torch.Generator().manual_seed(4)
+    draw = lambda lo, hi: int(torch.randint(lo, hi, (1,), generator=g))       # noqa: E731
+    shared = torch.randint(0, 503, (400,), generator=g).tolist()
+    prompts, params = [], []
+    for i in range(40):
+        n = draw(20, 300) if draw(0, 2) else draw(900, 4000)
+        body = torch.randint(0, 503, (n,), generator=g).tolist()
+        prompts.append(shared + body if i % 3 == 0 else body)
+        params.append({"temperature": 0.0, "max_new_tokens": draw(20, 90), "ignore_eos": True})
+
+    def run(dtype):
+        eng = Engine(EngineArgs(model=str(tmp_path), dummy_load=True, random_seed=1, dtype=dtype, page_size=16, num_pages=700,
+                                max_num_reqs=16, max_prefill_tokens=2048, chunk_size=512, log_level="ERROR", max_context_len=6000))
+        outs = eng.generate(input_ids=prompts, sampling_params=params)
+        eng.scheduler.check_idle_invariants()
+        return [o["token_ids"] for o in outs], [o["meta_info"]["cached_tokens"] for o in outs], dict(eng.scheduler.stats)
+
+    a, cached, stats = run("bfloat16")
+    b, _, _ = run("bfloat16")
+    assert a == b
+    assert stats["retractions"] + stats.get("evicted_pages", 0) > 0, stats          # the pool was too small for what was live
+    assert [len(x) for x in a] == [p["max_new_tokens"] for p in params]
+    assert sum(1 for c in cached if c >= 400 - 16) >= 5          # the shared prefix came from the cache for most who have it
+    f, _, _ = run("float32")
+    assert [x[:5] for x in a] == [y[:5] for y in f]
