@@ -40,7 +40,6 @@ stand-ins on the CPU.
 from __future__ import annotations
 
 import dataclasses
-import itertools
 import logging
 import random
 import time
@@ -70,8 +69,6 @@ class FinishReason:
 
 
 class Req:
-    _keys = itertools.count(1)
-
     def __init__(self, rid: str, prompt: Sequence[int], params: SamplingParams, eos_ids: Sequence[int] = ()):
         if len(prompt) == 0:
             raise ValueError("a request needs at least one prompt token")
@@ -85,7 +82,10 @@ class Req:
         self.cached_tokens = 0                # prompt tokens taken from the prefix cache at first admission
         self.finish_reason: Optional[FinishReason] = None
         self.to_abort: Optional[str] = None
-        self.rng_key = params.seed if params.seed is not None else next(Req._keys)
+        # what the random draws of this request are keyed by, beside the engine's seed and the step: the request's own
+        # seed, or else its number among the requests that its scheduler was given (set there), so that an engine with
+        # the same seed and the same requests in the same order draws the same numbers whatever else ran in the process
+        self.rng_key: Optional[int] = params.seed
         self.retractions = 0
         self.t_arrive = time.time()
         self.t_first_token: Optional[float] = None
@@ -171,6 +171,7 @@ class Scheduler:
         self._inflight: Optional[_InFlight] = None
         self._host_ids = [None, None]         # two pinned buffers for the tokens on their way to the host
         self._host_flip = 0
+        self._n_added = 0                      # requests given to add_request so far
         self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "cached_tokens": 0, "retractions": 0,
                       "evicted_pages": 0, "aborted": 0, "finished": 0}
         self.last_step: Dict[str, object] = {}     # what the last launched step held (for logs and profiles)
@@ -180,6 +181,9 @@ class Scheduler:
 
     # -- requests --------------------------------------------------------------------------
     def add_request(self, req: Req) -> None:
+        self._n_added += 1
+        if req.rng_key is None:
+            req.rng_key = self._n_added
         limit = self.mgr.max_context_len
         if req.params.eos_token_id == -1 and not req.eos_ids:
             req.eos_ids = set(self.eos_ids)          # the model's own end tokens

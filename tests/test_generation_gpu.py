@@ -355,3 +355,28 @@ def test_long_prompts_under_a_small_pool_twice_the_same(tmp_path):
     assert sum(1 for c in cached if c >= 400 - 16) >= 5          # the shared prefix came from the cache for most who have it
     f, _, _ = run("float32")
     assert [x[:5] for x in a] == [y[:5] for y in f]
+
+
+def test_temperature_sampling_does_not_depend_on_the_pool_or_on_other_engines():
+    """A request's random draws are keyed by the engine's seed, the request's number among those given to its engine and
+    the step.  So a second engine in the same process with the same seed gives the same tokens, and so does one whose pool is
+    so small that a request is retracted and fed again, with the overlapped decode or without.  float32."""
+    from mini_sglang_b200 import Engine, EngineArgs
+    name, cfg = "B", CONFIGS["B"]
+    prompts = [random_tokens(n, cfg["vocab_size"], 4000 + i) for i, n in enumerate([30, 9, 55, 17, 41, 23, 60, 12, 35, 48])]
+    sps = [{"temperature": 0.8, "max_new_tokens": 40, "ignore_eos": True} for _ in prompts]
+
+    def run(pages, **kw):
+        eng = Engine(EngineArgs(model=model_dir(name), dtype="float32", page_size=PAGE[name], num_pages=pages, max_num_reqs=8,
+                                random_seed=5, log_level="ERROR", **kw))
+        outs = eng.generate(input_ids=prompts, sampling_params=sps)
+        eng.scheduler.check_idle_invariants()
+        return [o["token_ids"] for o in outs], eng.scheduler.stats["retractions"]
+
+    roomy, r0 = run(400)
+    again, _ = run(400)
+    tight, r1 = run(60)
+    tight_no_overlap, r2 = run(60, disable_overlap=True)
+    assert r0 == 0 and r1 > 0 and r2 > 0
+    assert roomy == again == tight == tight_no_overlap
+    assert len({tuple(t) for t in roomy}) == len(roomy)              # and the requests do not all draw alike
