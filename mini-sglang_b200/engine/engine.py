@@ -88,10 +88,15 @@ class Engine:
             if self.tokenizer is None:
                 raise ValueError("the model folder has no tokenizer; pass input_ids")
             input_ids = self.tokenizer.encode(prompt)
+        input_ids = [int(t) for t in input_ids]
+        vocab = self.spec.vocab_size
+        bad = [t for t in input_ids if not 0 <= t < vocab]
+        if bad:       # refused here: inside a step it would stop every other request of the batch as well
+            raise ValueError(f"token id {bad[0]} is outside the model's vocabulary [0, {vocab})")
         import dataclasses as _dc
         params = (_dc.replace(sampling_params) if isinstance(sampling_params, SamplingParams)
                   else SamplingParams.init_from_dict(sampling_params))
-        return Req(uuid.uuid4().hex, list(input_ids), params, self.spec.eos_token_ids)
+        return Req(uuid.uuid4().hex, input_ids, params, self.spec.eos_token_ids)
 
     def add_request(self, prompt=None, sampling_params=None, input_ids=None) -> Req:
         req = self._make_req(prompt, input_ids, sampling_params)

@@ -380,3 +380,48 @@ def test_temperature_sampling_does_not_depend_on_the_pool_or_on_other_engines():
     assert r0 == 0 and r1 > 0 and r2 > 0
     assert roomy == again == tight == tight_no_overlap
     assert len({tuple(t) for t in roomy}) == len(roomy)              # and the requests do not all draw alike
+
+
+def test_edges_of_the_entry_point():
+    """More requests than the largest captured batch; the context's end; a prompt that does not fit; requests aborted while
+    others run; a one-token prompt; and what is refused before it reaches a step (no prompt, no new tokens, a token id outside
+    the vocabulary), after which the engine goes on as before.  float32, greedy, against the plain implementation."""
+    from mini_sglang_b200 import Engine, EngineArgs
+    name, cfg = "B", CONFIGS["B"]
+    prompts = [random_tokens(n, cfg["vocab_size"], 5000 + i) for i, n in enumerate([30, 9, 55, 17, 41])]
+    plain = lambda p, n: P.greedy_generate(cfg, weights(name), p, n, device="cpu")      # noqa: E731
+    sp = {"max_new_tokens": 12, "ignore_eos": True}
+    eng = make_engine(name, "float32", max_capture_bs=2)
+    assert [o["token_ids"] for o in eng.generate(input_ids=prompts, sampling_params=sp)] == [plain(p, 12) for p in prompts]
+
+    eng = make_engine(name, "float32", max_context_len=40)
+    out = eng.generate(input_ids=prompts[0], sampling_params={"max_new_tokens": 100, "ignore_eos": True})
+    assert out["meta_info"]["finish_reason"] == {"type": "length", "length": 11} and out["token_ids"] == plain(prompts[0], 11)
+    out = eng.generate(input_ids=prompts[2], sampling_params=sp)
+    assert out["meta_info"]["finish_reason"]["type"] == "abort" and "does not fit" in out["meta_info"]["finish_reason"]["message"]
+    assert out["token_ids"] == []
+
+    eng = make_engine(name, "float32")
+    reqs = [eng.add_request(input_ids=p, sampling_params={"max_new_tokens": 30, "ignore_eos": True}) for p in prompts]
+    for _ in range(6):
+        eng.step()
+    eng.scheduler.abort(reqs[1].rid)
+    eng.scheduler.abort(reqs[3].rid)
+    while not eng.scheduler.idle:
+        eng.step()
+    eng.scheduler.check_idle_invariants()
+    assert [r.finish_reason.to_json()["type"] for r in reqs] == ["length", "abort", "length", "abort", "length"]
+    assert all(len(reqs[i].output) == 30 for i in (0, 2, 4)) and all(0 < len(reqs[i].output) < 30 for i in (1, 3))
+    assert all(r.output == plain(p, len(r.output)) for r, p in zip(reqs, prompts))
+
+    assert eng.generate(input_ids=[7], sampling_params={"max_new_tokens": 1, "ignore_eos": True})["token_ids"] == plain([7], 1)
+    for bad, words in [(dict(input_ids=[7], sampling_params={"max_new_tokens": 0}), "max_new_tokens"),
+                       (dict(input_ids=[], sampling_params=sp), "at least one prompt token"),
+                       (dict(input_ids=[3, cfg["vocab_size"] + 5], sampling_params=sp), "vocabulary"),
+                       (dict(input_ids=[-1], sampling_params=sp), "vocabulary"),
+                       (dict(sampling_params=sp), "prompt or input_ids")]:
+        with pytest.raises(ValueError, match=words):
+            eng.generate(**bad)
+    assert eng.scheduler.idle
+    assert eng.generate(input_ids=prompts[1], sampling_params=sp)["token_ids"] == plain(prompts[1], 12)
+    eng.scheduler.check_idle_invariants()
